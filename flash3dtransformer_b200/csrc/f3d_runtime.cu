@@ -1,0 +1,92 @@
+// Process-wide runtime state of the library: last-error string, sync flag, RNG seed, scratch workspaces.
+// Stands in for the reference's DeviceManagerSingleton (src/common/device_manager.cu:32-119): the
+// sync_stream debug flag is kept; the per-device cuRAND state array is replaced by a stateless
+// counter-based generator, so only a 64-bit seed lives here (default 3407 as in device_manager.cu:58-67).
+#include "f3d_common.cuh"
+#include "../../include/f3d_b200.h"
+#include <mutex>
+#include <map>
+#include <atomic>
+
+namespace f3d {
+
+static thread_local char g_err[512] = "";
+static std::atomic<int> g_sync{0};
+static std::atomic<uint64_t> g_seed{3407ull};
+
+char *err_buf() { return g_err; }
+
+int set_error(int code, const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+bool sync_flag() { return g_sync.load() != 0; }
+uint64_t seed() { return g_seed.load(); }
+
+struct Slot { void *ptr = nullptr; size_t bytes = 0; };
+static std::mutex g_ws_mu;
+static std::map<std::pair<int, int>, Slot> g_ws;
+
+int workspace(int device, int slot, size_t bytes, void **out) {
+  std::lock_guard<std::mutex> lk(g_ws_mu);
+  Slot &s = g_ws[{device, slot}];
+  if (s.bytes < bytes) {
+    // round up so that slowly growing requests do not reallocate every call
+    size_t want = bytes + bytes / 4 + 4096;
+    if (s.ptr) {
+      // the old block may still be in use by kernels queued earlier: wait for the device first
+      F3D_CUDA_TRY(cudaDeviceSynchronize());
+      F3D_CUDA_TRY(cudaFree(s.ptr));
+      s.ptr = nullptr; s.bytes = 0;
+    }
+    F3D_CUDA_TRY(cudaMalloc(&s.ptr, want));
+    s.bytes = want;
+  }
+  *out = s.ptr;
+  return F3D_OK;
+}
+
+void workspace_release_all() {
+  std::lock_guard<std::mutex> lk(g_ws_mu);
+  for (auto &kv : g_ws) {
+    if (kv.second.ptr) { cudaSetDevice(kv.first.first); cudaFree(kv.second.ptr); }
+  }
+  g_ws.clear();
+}
+
+}  // namespace f3d
+
+extern "C" {
+
+const char *f3d_last_error(void) { return f3d::err_buf(); }
+
+int f3d_version(void) { return 100; }
+
+int f3d_set_sync(int on) {
+  int old = f3d::g_sync.exchange(on ? 1 : 0);
+  return old;
+}
+
+int f3d_get_sync(void) { return f3d::g_sync.load(); }
+
+int f3d_set_seed(uint64_t seed) { f3d::g_seed.store(seed); return F3D_OK; }
+
+uint64_t f3d_get_seed(void) { return f3d::g_seed.load(); }
+
+int f3d_init_device(int device) {
+  int n = 0;
+  F3D_CUDA_TRY(cudaGetDeviceCount(&n));
+  if (device < 0 || device >= n) return f3d::set_error(F3D_ERR_ARG, "device %d out of range [0,%d)", device, n);
+  cudaDeviceProp p;
+  F3D_CUDA_TRY(cudaGetDeviceProperties(&p, device));
+  if (p.major != 10) return f3d::set_error(F3D_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library holds sm_100a code only", device, p.major, p.minor);
+  return F3D_OK;
+}
+
+int f3d_release_workspaces(void) { f3d::workspace_release_all(); return F3D_OK; }
+
+}  // extern "C"

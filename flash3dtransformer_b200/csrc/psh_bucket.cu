@@ -1,0 +1,727 @@
+// Batched perfect-spatial-hash bucketing and scatter for sm_100a.
+//
+// Replaces the reference's three kernels
+//   batch_psh_bucketing_balancing_ker     src/psh/batch_psh_bucket.cuh:42-257
+//   batch_psh_distribute_recycle_ker      src/psh/batch_psh_bucket.cuh:259-382
+//   batch_psh_cumsum_scatter_postpad_ker  src/psh/batch_psh_bucket.cuh:493-614
+// and their host driver batch_psh_scatter_pad_hash (src/psh/batch_psh_bucket_dispatcher.cu:221-326).
+//
+// The reference decides in-bucket offsets by atomicInc arrival order and rebalances with racy reads, so its
+// output differs from run to run.  Here every offset is a *stable rank by input index*, which is one of the
+// outcomes the reference can produce for points that do not overflow, and the rebalance is defined as three
+// deterministic rounds (scene-local, input order = index order inside the scene):
+//
+//   round A  bucket b = first_hash(vox).  rank_A = number of earlier points of the scene with the same b.
+//            A point keeps (b, rank_A) if b is the recycle bucket 0 or rank_A < bucket_size.
+//            kept[b] = count[b] for b == 0, min(count[b], bucket_size) otherwise.
+//   round B  every other point makes one attempt, as in the reference (one attempt per point because the
+//            segment commit test at batch_psh_bucket.cuh:218 only fires on the last probe): it walks the 128
+//            probes in table order and takes the first perturbed-hash bucket t that is neither its own bucket
+//            nor bucket 0 and has kept[t] < bucket_size.  Attempts on t are ranked by input index; the first
+//            bucket_size - kept[t] are accepted at offset kept[t] + rank_B.  The rest, and points with no
+//            admissible probe, go to the recycle bucket at offset count[0] + (rejected of lower t) + (rank_B -
+//            free[t]); points without a probe are ordered last.
+//   round C  recycle-bucket points at offset >= bucket_size are redistributed as in the recycle kernel: one
+//            random probe, perturbed hash, a random non-zero bucket if that hashes to 0, no capacity check.
+//            Arrivals on bucket c are ranked by input index and appended after round B's content of c.
+//
+// Each round is "tile histogram -> per-scene scan over tiles -> tile rank", so a point's rank needs no atomics
+// on global memory and no inter-CTA waiting.  Warps own contiguous index ranges; equal keys inside a warp are
+// merged with match_any (warp-aggregated counting), per-warp counters live in shared memory, and coordinates
+// are staged into shared memory with 128-bit loads.
+#include "f3d_common.cuh"
+#include "psh_device.cuh"
+#include "../../include/f3d_b200.h"
+
+namespace f3d {
+
+uint64_t seed();
+
+constexpr int kPshThreads = 256;
+constexpr int kPshWarps = kPshThreads / 32;
+constexpr uint32_t kGroup = 256;            // points one warp stages at a time
+constexpr uint32_t kStageHalves = kGroup * 3 + 16;   // staged halves + room for the 16-byte alignment skew
+constexpr uint32_t kMaxTile = 16384;
+
+struct PshArgs {
+  const __half *coord; uint16_t *bucket_id; uint32_t *bucket_counter; uint32_t *bucket_offset;
+  const uint32_t *batch_sep; uint32_t *cumsum_counter; __half *scatter_coord;
+  const __half *bbox_min; const __half *bbox_max; const int16_t *probe;
+  uint32_t total_N, batch, nb, nbp, divisor, cap, num_vox, hash_type, pad_to;
+  uint32_t tile, tiles_max;
+  uint16_t pad_bits; uint16_t coord_aligned;
+  RngKey key;
+  // scratch
+  uint32_t *tabP, *tabQ;           // [batch*tiles_max][nbp] tile histograms / tile prefixes
+  uint32_t *count0, *kept, *freeB, *rejpre, *cntB, *cntF;   // [batch][nbp]
+  uint32_t *tile_pending, *tile_movers;                     // [batch*tiles_max]
+};
+
+// ---------------------------------------------------------------------------------------------------------
+// shared-memory plan of the tile kernels
+struct TileSmem {
+  uint16_t *stage;     // [kPshWarps][kStageHalves]
+  uint16_t *whist;     // [kPshWarps][nbp]   per-warp counts, then per-warp running ranks (tile-relative)
+  uint32_t *tbase;     // [nbp]              rank of the tile's first element of each key
+  uint32_t *aux;       // [nbp]              block histogram of the next round / cached per-scene table
+  uint16_t *keys;      // [tile]             key cache between the counting and the ranking sweep
+};
+
+__host__ __device__ inline size_t tile_smem_bytes(uint32_t nbp, uint32_t tile) {
+  size_t b = 0;
+  b += (size_t)kPshWarps * kStageHalves * 2;
+  b += ((size_t)kPshWarps * nbp * 2 + 15) / 16 * 16;
+  b += (size_t)nbp * 4 * 2;
+  b += (size_t)tile * 2;
+  return b + 64;
+}
+
+__device__ __forceinline__ TileSmem carve(unsigned char *base, uint32_t nbp, uint32_t tile) {
+  TileSmem s;
+  s.stage = reinterpret_cast<uint16_t *>(base);
+  base += (size_t)kPshWarps * kStageHalves * 2;          // multiple of 16
+  s.whist = reinterpret_cast<uint16_t *>(base);
+  base += ((size_t)kPshWarps * nbp * 2 + 15) / 16 * 16;
+  s.tbase = reinterpret_cast<uint32_t *>(base);
+  base += (size_t)nbp * 4;
+  s.aux = reinterpret_cast<uint32_t *>(base);
+  base += (size_t)nbp * 4;
+  s.keys = reinterpret_cast<uint16_t *>(base);
+  return s;
+}
+
+// Stage points [g, g+cnt) of the flat [N,3] fp16 array into the warp's shared buffer with 128-bit loads.
+// Returns the offset (in halves) of point g inside the buffer.
+__device__ __forceinline__ uint32_t warp_stage(const PshArgs &a, uint32_t g, uint32_t cnt, uint16_t *dst, int lane) {
+  const uint16_t *src = reinterpret_cast<const uint16_t *>(a.coord);
+  const uint64_t total_h = (uint64_t)a.total_N * 3ull;
+  uint64_t h0 = (uint64_t)g * 3ull, h1 = h0 + (uint64_t)cnt * 3ull;
+  __syncwarp();
+  if (a.coord_aligned) {
+    uint64_t a0 = h0 & ~7ull;                       // 8 halves = 16 bytes
+    uint32_t nvec = (uint32_t)((h1 - a0 + 7ull) / 8ull);
+    for (uint32_t v = lane; v < nvec; v += 32) {
+      uint64_t off = a0 + (uint64_t)v * 8ull;
+      if (off + 8ull <= total_h) {
+        uint4 w = __ldg(reinterpret_cast<const uint4 *>(src + off));
+        *reinterpret_cast<uint4 *>(dst + v * 8u) = w;
+      } else {
+        for (uint32_t e = 0; e < 8 && off + e < total_h; ++e) dst[v * 8u + e] = src[off + e];
+      }
+    }
+    __syncwarp();
+    return (uint32_t)(h0 - a0);
+  }
+  for (uint32_t e = lane; e < cnt * 3u; e += 32) dst[e] = src[h0 + e];
+  __syncwarp();
+  return 0u;
+}
+
+__device__ __forceinline__ void load_vox(const PshArgs &a, const uint16_t *st, uint32_t skew, uint32_t k,
+                                         const float (&lo)[3], const float (&hi)[3], uint32_t (&vox)[3]) {
+#pragma unroll
+  for (int d = 0; d < 3; ++d) {
+    float c = __half2float(__ushort_as_half(st[skew + 3u * k + d]));
+    vox[d] = vox_axis(c, lo[d], hi[d], a.num_vox);
+  }
+}
+
+__device__ __forceinline__ void load_bbox(const PshArgs &a, float (&lo)[3], float (&hi)[3]) {
+#pragma unroll
+  for (int d = 0; d < 3; ++d) { lo[d] = __half2float(a.bbox_min[d]); hi[d] = __half2float(a.bbox_max[d]); }
+}
+
+struct TileInfo { uint32_t scene, tile, start, n, t0, cnt, row; bool live; };
+
+__device__ __forceinline__ TileInfo tile_info(const PshArgs &a) {
+  TileInfo t;
+  t.scene = blockIdx.y; t.tile = blockIdx.x;
+  t.start = t.scene ? a.batch_sep[t.scene - 1] : 0u;
+  uint32_t end = a.batch_sep[t.scene];
+  if (end > a.total_N) end = a.total_N;
+  t.n = end > t.start ? end - t.start : 0u;
+  t.t0 = t.tile * a.tile;
+  t.live = t.t0 < t.n;
+  t.cnt = t.live ? min(a.tile, t.n - t.t0) : 0u;
+  t.row = t.scene * a.tiles_max + t.tile;
+  return t;
+}
+
+// warp-aggregated counting of one key per lane (all 32 lanes call)
+__device__ __forceinline__ void warp_count(uint16_t *wh, uint32_t key, bool valid, int lane) {
+  uint32_t peers = __match_any_sync(0xFFFFFFFFu, valid ? key : 0xFFFFFFFFu);
+  if (valid && (__ffs(peers) - 1) == lane) wh[key] = (uint16_t)(wh[key] + __popc(peers));
+  __syncwarp();
+}
+
+// stable rank of one key per lane; wh holds the warp's running tile-relative rank of every key
+__device__ __forceinline__ uint32_t warp_rank(uint16_t *wh, const uint32_t *tbase, uint32_t key, bool valid, int lane) {
+  uint32_t peers = __match_any_sync(0xFFFFFFFFu, valid ? key : 0xFFFFFFFFu);
+  uint32_t base = valid ? wh[key] : 0u;
+  __syncwarp();
+  if (valid && (__ffs(peers) - 1) == lane) wh[key] = (uint16_t)(base + __popc(peers));
+  __syncwarp();
+  uint32_t lower = __popc(peers & ((1u << lane) - 1u));
+  return valid ? tbase[key] + base + lower : 0u;
+}
+
+__device__ __forceinline__ void zero_whist(const TileSmem &s, uint32_t nbp) {
+  for (uint32_t i = threadIdx.x; i < kPshWarps * nbp; i += kPshThreads) s.whist[i] = 0;
+}
+
+// per-warp counts -> per-warp exclusive prefix (tile-relative); tbase[key] = row[key] (+ add[key])
+__device__ __forceinline__ void warp_prefix(const TileSmem &s, uint32_t nbp, const uint32_t *row, const uint32_t *add) {
+  for (uint32_t b = threadIdx.x; b < nbp; b += kPshThreads) {
+    uint32_t run = 0;
+#pragma unroll
+    for (int w = 0; w < kPshWarps; ++w) {
+      uint32_t c = s.whist[w * nbp + b];
+      s.whist[w * nbp + b] = (uint16_t)run;
+      run += c;
+    }
+    s.tbase[b] = row[b] + (add ? add[b] : 0u);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// K1: first-hash histogram of every tile
+__global__ void __launch_bounds__(kPshThreads) psh_hist_kernel(PshArgs a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  TileSmem s = carve(smem_raw, a.nbp, 0);
+  TileInfo t = tile_info(a);
+  if (!t.live) return;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (uint32_t b = threadIdx.x; b < a.nbp; b += kPshThreads) s.aux[b] = 0;
+  __syncthreads();
+  float lo[3], hi[3];
+  load_bbox(a, lo, hi);
+  const uint32_t wt = a.tile / kPshWarps;
+  const uint32_t w0 = warp * wt, w1 = min(w0 + wt, t.cnt);
+  uint16_t *st = s.stage + warp * kStageHalves;
+  for (uint32_t g = w0; g < w1; g += kGroup) {
+    uint32_t gc = min(kGroup, w1 - g);
+    uint32_t skew = warp_stage(a, t.start + t.t0 + g, gc, st, lane);
+    for (uint32_t it = 0; it < gc; it += 32) {
+      uint32_t k = it + lane;
+      bool valid = k < gc;
+      uint32_t key = 0;
+      if (valid) {
+        uint32_t vox[3];
+        load_vox(a, st, skew, k, lo, hi, vox);
+        key = first_hash(a.hash_type, vox[0], vox[1], vox[2], a.divisor, a.nb);
+      }
+      uint32_t peers = __match_any_sync(0xFFFFFFFFu, valid ? key : 0xFFFFFFFFu);
+      if (valid && (__ffs(peers) - 1) == lane) atomicAdd(&s.aux[key], (uint32_t)__popc(peers));
+    }
+  }
+  __syncthreads();
+  uint32_t *row = a.tabP + (size_t)t.row * a.nbp;
+  for (uint32_t b = threadIdx.x; b < a.nbp; b += kPshThreads) row[b] = s.aux[b];
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// per-scene scans (one CTA per scene).  Column scan over tiles: table[tile][col] -> exclusive prefix.
+__device__ __forceinline__ uint32_t column_scan(uint32_t *tab, uint32_t tiles, uint32_t nbp, uint32_t col) {
+  uint32_t run = 0;
+  uint32_t t = 0;
+  for (; t + 8 <= tiles; t += 8) {
+    uint32_t v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = tab[(size_t)(t + j) * nbp + col];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { tab[(size_t)(t + j) * nbp + col] = run; run += v[j]; }
+  }
+  for (; t < tiles; ++t) { uint32_t v = tab[(size_t)t * nbp + col]; tab[(size_t)t * nbp + col] = run; run += v; }
+  return run;
+}
+
+// block-wide exclusive scan of one value per thread (kPshThreads threads); returns exclusive prefix, total in *tot
+__device__ __forceinline__ uint32_t block_excl_scan(uint32_t v, uint32_t *wsum /*[kPshWarps+1]*/, uint32_t *tot) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint32_t inc = v;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    uint32_t o = __shfl_up_sync(0xFFFFFFFFu, inc, d);
+    if (lane >= d) inc += o;
+  }
+  if (lane == 31) wsum[warp] = inc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t run = 0;
+    for (int w = 0; w < kPshWarps; ++w) { uint32_t c = wsum[w]; wsum[w] = run; run += c; }
+    wsum[kPshWarps] = run;
+  }
+  __syncthreads();
+  uint32_t ex = wsum[warp] + inc - v;
+  *tot = wsum[kPshWarps];
+  __syncthreads();
+  return ex;
+}
+
+__device__ __forceinline__ uint32_t scene_tiles(const PshArgs &a, uint32_t scene) {
+  uint32_t start = scene ? a.batch_sep[scene - 1] : 0u;
+  uint32_t end = min(a.batch_sep[scene], a.total_N);
+  uint32_t n = end > start ? end - start : 0u;
+  return (n + a.tile - 1) / a.tile;
+}
+
+// K2: round A totals
+__global__ void __launch_bounds__(kPshThreads) psh_scanA_kernel(PshArgs a) {
+  const uint32_t scene = blockIdx.x;
+  const uint32_t tiles = scene_tiles(a, scene);
+  uint32_t *tab = a.tabP + (size_t)scene * a.tiles_max * a.nbp;
+  for (uint32_t b = threadIdx.x; b < a.nbp; b += kPshThreads) {
+    uint32_t tot = column_scan(tab, tiles, a.nbp, b);
+    a.count0[scene * a.nbp + b] = tot;
+    a.kept[scene * a.nbp + b] = (b == kRecycleBucket) ? tot : min(tot, a.cap);
+  }
+}
+
+// K4: round B totals -> free capacity, rejected prefix, counts after round B
+__global__ void __launch_bounds__(kPshThreads) psh_scanB_kernel(PshArgs a) {
+  __shared__ uint32_t wsum[kPshWarps + 1];
+  const uint32_t scene = blockIdx.x;
+  const uint32_t tiles = scene_tiles(a, scene);
+  uint32_t *tab = a.tabQ + (size_t)scene * a.tiles_max * a.nbp;
+  const uint32_t so = scene * a.nbp;
+  uint32_t carry = 0;
+  for (uint32_t b0 = 0; b0 < a.nbp; b0 += kPshThreads) {
+    uint32_t b = b0 + threadIdx.x;
+    uint32_t rej = 0;
+    if (b < a.nbp) {
+      uint32_t att = column_scan(tab, tiles, a.nbp, b);
+      uint32_t kept = a.kept[so + b];
+      uint32_t fr = (b != kRecycleBucket && b < a.nb && kept < a.cap) ? a.cap - kept : 0u;
+      uint32_t acc = min(att, fr);
+      rej = att - acc;
+      a.freeB[so + b] = fr;
+      a.cntB[so + b] = kept + acc;      // bucket 0 is fixed up below
+    }
+    uint32_t tot;
+    uint32_t ex = block_excl_scan(rej, wsum, &tot);
+    if (b < a.nbp) a.rejpre[so + b] = carry + ex;
+    carry += tot;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) a.cntB[so + kRecycleBucket] = a.count0[so + kRecycleBucket] + carry;
+}
+
+// K6: round C totals -> final counts and inclusive cumsum
+__global__ void __launch_bounds__(kPshThreads) psh_scanC_kernel(PshArgs a) {
+  __shared__ uint32_t wsum[kPshWarps + 1];
+  const uint32_t scene = blockIdx.x;
+  const uint32_t tiles = scene_tiles(a, scene);
+  uint32_t *tab = a.tabP + (size_t)scene * a.tiles_max * a.nbp;
+  const uint32_t so = scene * a.nbp;
+  uint32_t carry = 0;
+  for (uint32_t b0 = 0; b0 < a.nbp; b0 += kPshThreads) {
+    uint32_t b = b0 + threadIdx.x;
+    uint32_t fin = 0;
+    if (b < a.nbp) {
+      uint32_t mv = column_scan(tab, tiles, a.nbp, b);
+      uint32_t cb = a.cntB[so + b];
+      if (b == kRecycleBucket) fin = (a.nb > 1) ? min(cb, a.cap) : cb;
+      else if (b < a.nb) fin = cb + mv;
+      a.cntF[so + b] = fin;
+    }
+    uint32_t tot;
+    uint32_t ex = block_excl_scan(fin, wsum, &tot);
+    if (b < a.nb) {
+      a.bucket_counter[scene * a.nb + b] = fin;
+      a.cumsum_counter[scene * a.nb + b] = carry + ex + fin;
+    }
+    carry += tot;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// K3: round A ranks, overflow detection, probe walk, round B histogram
+__global__ void __launch_bounds__(kPshThreads) psh_rankA_kernel(PshArgs a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ uint32_t pending_cnt;
+  TileSmem s = carve(smem_raw, a.nbp, a.tile);
+  TileInfo t = tile_info(a);
+  if (!t.live) return;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  zero_whist(s, a.nbp);
+  if (threadIdx.x == 0) pending_cnt = 0;
+  __syncthreads();
+  float lo[3], hi[3];
+  load_bbox(a, lo, hi);
+  const uint32_t wt = a.tile / kPshWarps;
+  const uint32_t w0 = warp * wt, w1 = min(w0 + wt, t.cnt);
+  uint16_t *st = s.stage + warp * kStageHalves;
+  uint16_t *wh = s.whist + warp * a.nbp;
+  // sweep 1: keys and per-warp counts
+  for (uint32_t g = w0; g < w1; g += kGroup) {
+    uint32_t gc = min(kGroup, w1 - g);
+    uint32_t skew = warp_stage(a, t.start + t.t0 + g, gc, st, lane);
+    for (uint32_t it = 0; it < gc; it += 32) {
+      uint32_t k = it + lane;
+      bool valid = k < gc;
+      uint32_t key = 0;
+      if (valid) {
+        uint32_t vox[3];
+        load_vox(a, st, skew, k, lo, hi, vox);
+        key = first_hash(a.hash_type, vox[0], vox[1], vox[2], a.divisor, a.nb);
+        s.keys[g + k] = (uint16_t)key;
+      }
+      warp_count(wh, key, valid, lane);
+    }
+  }
+  __syncthreads();
+  warp_prefix(s, a.nbp, a.tabP + (size_t)t.row * a.nbp, nullptr);
+  const uint32_t so = t.scene * a.nbp;
+  for (uint32_t b = threadIdx.x; b < a.nbp; b += kPshThreads) s.aux[b] = a.kept[so + b];
+  __syncthreads();
+  // sweep 2: ranks; overflowing points choose their attempt bucket and are counted into the round B table,
+  // whose row is accumulated with global atomics (rare path) after being zeroed by the host memset.
+  uint32_t *rowB = a.tabQ + (size_t)t.row * a.nbp;
+  uint32_t my_pending = 0;
+  for (uint32_t g = w0; g < w1; g += kGroup) {
+    uint32_t gc = min(kGroup, w1 - g);
+    bool need_coords = false;
+    // ranks first (cheap), then stage coordinates only if some lane of the group overflows
+    for (uint32_t it = 0; it < gc; it += 32) {
+      uint32_t k = it + lane;
+      bool valid = k < gc;
+      uint32_t key = valid ? s.keys[g + k] : 0u;
+      uint32_t rank = warp_rank(wh, s.tbase, key, valid, lane);
+      uint32_t gi = t.start + t.t0 + g + k;
+      bool over = valid && key != kRecycleBucket && rank >= a.cap;
+      if (valid && !over) {
+        a.bucket_id[gi] = (uint16_t)key;
+        a.bucket_offset[gi] = rank;
+        if (key == kRecycleBucket && rank >= a.cap && a.nb > 1) ++my_pending;
+      }
+      if (valid && over) s.keys[g + k] = (uint16_t)(0x8000u | key);   // mark for the walk below
+      need_coords |= (__any_sync(0xFFFFFFFFu, over) != 0);
+    }
+    if (!need_coords) continue;
+    uint32_t skew = warp_stage(a, t.start + t.t0 + g, gc, st, lane);
+    for (uint32_t it = 0; it < gc; it += 32) {
+      uint32_t k = it + lane;
+      bool valid = k < gc;
+      uint32_t mk = valid ? s.keys[g + k] : 0u;
+      if (valid && (mk & 0x8000u)) {
+        uint32_t init = mk & 0x7FFFu;
+        uint32_t vox[3], nvox[3], r[4];
+        load_vox(a, st, skew, k, lo, hi, vox);
+        uint32_t pt = t.t0 + g + k;
+        uint32_t target = a.nb;                       // "no admissible probe" column
+        for (uint32_t p = 0; p < kNumProbes; ++p) {
+          psh_rand(a.key, t.scene, pt, p, r);
+          perturb_vox(r, a.num_vox, a.divisor, a.probe + 3u * p, vox, nvox);
+          uint32_t c = first_hash(a.hash_type, nvox[0], nvox[1], nvox[2], a.divisor, a.nb);
+          if (c != init && c != kRecycleBucket && s.aux[c] < a.cap) { target = c; break; }
+        }
+        uint32_t gi = t.start + pt;
+        a.bucket_id[gi] = (uint16_t)target;
+        a.bucket_offset[gi] = kPending;
+        atomicAdd(&rowB[target], 1u);
+        ++my_pending;
+      }
+    }
+  }
+  if (my_pending) atomicAdd(&pending_cnt, my_pending);
+  __syncthreads();
+  if (threadIdx.x == 0) a.tile_pending[t.row] = pending_cnt;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// K5: resolve round B, choose round C targets, round C histogram
+__global__ void __launch_bounds__(kPshThreads) psh_resolveB_kernel(PshArgs a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ uint32_t mover_cnt;
+  TileSmem s = carve(smem_raw, a.nbp, a.tile);
+  TileInfo t = tile_info(a);
+  if (!t.live) return;
+  if (a.tile_pending[t.row] == 0) {
+    if (threadIdx.x == 0) a.tile_movers[t.row] = 0;
+    return;                       // the round C row stays zero (host memset)
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  zero_whist(s, a.nbp);
+  if (threadIdx.x == 0) mover_cnt = 0;
+  __syncthreads();
+  const uint32_t wt = a.tile / kPshWarps;
+  const uint32_t w0 = warp * wt, w1 = min(w0 + wt, t.cnt);
+  uint16_t *wh = s.whist + warp * a.nbp;
+  const uint32_t gbase = t.start + t.t0;
+  for (uint32_t it = w0; it < w1; it += 32) {
+    uint32_t k = it + lane;
+    bool inb = k < w1;
+    bool valid = false;
+    uint32_t key = 0;
+    if (inb) {
+      uint32_t off = a.bucket_offset[gbase + k];
+      key = a.bucket_id[gbase + k];
+      valid = (off == kPending);
+      s.keys[k] = valid ? (uint16_t)key : (uint16_t)0xFFFFu;
+    }
+    warp_count(wh, key, valid, lane);
+  }
+  __syncthreads();
+  warp_prefix(s, a.nbp, a.tabQ + (size_t)t.row * a.nbp, nullptr);
+  __syncthreads();
+  float lo[3], hi[3];
+  load_bbox(a, lo, hi);
+  const uint32_t so = t.scene * a.nbp;
+  uint32_t *rowC = a.tabP + (size_t)t.row * a.nbp;
+  const uint32_t count0_recycle = a.count0[so + kRecycleBucket];
+  uint32_t my_movers = 0;
+  for (uint32_t it = w0; it < w1; it += 32) {
+    uint32_t k = it + lane;
+    bool inb = k < w1;
+    uint32_t kk = inb ? s.keys[k] : 0xFFFFu;
+    bool valid = inb && kk != 0xFFFFu;
+    uint32_t q = warp_rank(wh, s.tbase, kk, valid, lane);
+    if (!inb) continue;
+    uint32_t gi = gbase + k;
+    bool mover = false;
+    uint32_t recycle_off = 0;
+    if (valid) {
+      uint32_t fr = a.freeB[so + kk];
+      if (q < fr) {
+        a.bucket_id[gi] = (uint16_t)kk;
+        a.bucket_offset[gi] = a.kept[so + kk] + q;
+      } else {
+        recycle_off = count0_recycle + a.rejpre[so + kk] + (q - fr);
+        if (recycle_off < a.cap || a.nb <= 1) {
+          a.bucket_id[gi] = (uint16_t)kRecycleBucket;
+          a.bucket_offset[gi] = recycle_off;
+        } else {
+          mover = true;
+        }
+      }
+    } else {
+      uint32_t off = a.bucket_offset[gi];
+      mover = (a.bucket_id[gi] == kRecycleBucket) && off >= a.cap && a.nb > 1;
+    }
+    if (mover) {
+      uint32_t pt = t.t0 + k;
+      uint32_t vox[3], nvox[3], r[4];
+#pragma unroll
+      for (int d = 0; d < 3; ++d) vox[d] = vox_axis(__half2float(a.coord[(size_t)gi * 3 + d]), lo[d], hi[d], a.num_vox);
+      psh_rand(a.key, t.scene, pt, 128u, r);
+      uint32_t p = r[0] % kNumProbes;
+      psh_rand(a.key, t.scene, pt, 129u, r);
+      perturb_vox(r, a.num_vox, a.divisor, a.probe + 3u * p, vox, nvox);
+      uint32_t c = first_hash(a.hash_type, nvox[0], nvox[1], nvox[2], a.divisor, a.nb);
+      if (c == kRecycleBucket) {
+        psh_rand(a.key, t.scene, pt, 130u, r);
+        c = 1u + r[0] % (a.nb - 1u);
+      }
+      a.bucket_id[gi] = (uint16_t)c;
+      a.bucket_offset[gi] = kPending;
+      atomicAdd(&rowC[c], 1u);
+      ++my_movers;
+    }
+  }
+  if (my_movers) atomicAdd(&mover_cnt, my_movers);
+  __syncthreads();
+  if (threadIdx.x == 0) a.tile_movers[t.row] = mover_cnt;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// K7: round C ranks, final (id, offset), scatter of the coordinates, tail padding (grid row y == batch)
+__global__ void __launch_bounds__(kPshThreads) psh_scatter_kernel(PshArgs a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  if (blockIdx.y == a.batch) {
+    // tail rows [total_N, pad_to) take the pad value (src/psh/batch_psh_bucket.cuh:538-547)
+    uint64_t h0 = (uint64_t)a.total_N * 3ull, h1 = (uint64_t)a.pad_to * 3ull;
+    uint64_t per = (uint64_t)a.tile * 3ull;
+    uint64_t b0 = h0 + (uint64_t)blockIdx.x * per;
+    uint64_t b1 = min(b0 + per, h1);
+    uint16_t *dst = reinterpret_cast<uint16_t *>(a.scatter_coord);
+    for (uint64_t e = b0 + threadIdx.x; e < b1; e += kPshThreads) dst[e] = a.pad_bits;
+    return;
+  }
+  TileSmem s = carve(smem_raw, a.nbp, a.tile);
+  TileInfo t = tile_info(a);
+  if (!t.live) return;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t so = t.scene * a.nbp;
+  const bool movers = a.tile_movers[t.row] != 0;
+  const uint32_t wt = a.tile / kPshWarps;
+  const uint32_t w0 = warp * wt, w1 = min(w0 + wt, t.cnt);
+  uint16_t *wh = s.whist + warp * a.nbp;
+  uint16_t *st = s.stage + warp * kStageHalves;
+  const uint32_t gbase = t.start + t.t0;
+  // aux = exclusive bucket start inside the scene
+  for (uint32_t b = threadIdx.x; b < a.nb; b += kPshThreads)
+    s.aux[b] = a.cumsum_counter[t.scene * a.nb + b] - a.cntF[so + b];
+  if (movers) {
+    zero_whist(s, a.nbp);
+    __syncthreads();
+    for (uint32_t it = w0; it < w1; it += 32) {
+      uint32_t k = it + lane;
+      bool inb = k < w1;
+      bool valid = false;
+      uint32_t key = 0;
+      if (inb) {
+        key = a.bucket_id[gbase + k];
+        valid = a.bucket_offset[gbase + k] == kPending;
+      }
+      warp_count(wh, key, valid, lane);
+    }
+    __syncthreads();
+    warp_prefix(s, a.nbp, a.tabP + (size_t)t.row * a.nbp, a.cntB + so);
+  }
+  __syncthreads();
+  uint16_t *dst = reinterpret_cast<uint16_t *>(a.scatter_coord);
+  for (uint32_t g = w0; g < w1; g += kGroup) {
+    uint32_t gc = min(kGroup, w1 - g);
+    uint32_t skew = warp_stage(a, gbase + g, gc, st, lane);
+    for (uint32_t it = 0; it < gc; it += 32) {
+      uint32_t k = it + lane;
+      bool inb = k < gc;
+      uint32_t gi = gbase + g + k;
+      uint32_t id = 0, off = 0;
+      if (inb) { id = a.bucket_id[gi]; off = a.bucket_offset[gi]; }
+      if (movers) {
+        bool valid = inb && off == kPending;
+        uint32_t r = warp_rank(wh, s.tbase, id, valid, lane);
+        if (valid) { off = r; a.bucket_offset[gi] = off; }
+      }
+      if (inb) {
+        uint64_t row = (uint64_t)t.start + s.aux[id] + off;
+        if (row < a.pad_to) {
+          uint16_t *d3 = dst + row * 3ull;
+          const uint16_t *s3 = st + skew + 3u * k;
+          d3[0] = s3[0]; d3[1] = s3[1]; d3[2] = s3[2];
+        }
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+static int psh_validate(uint32_t total_N, uint32_t batch, uint32_t num_bucket, uint32_t divisor, uint32_t cap,
+                        uint32_t num_vox, uint32_t pad_to, uint32_t hash_type) {
+  if (batch == 0) return set_error(F3D_ERR_ARG, "batch_sep is empty");
+  if (divisor == 0 || num_bucket == 0 || cap == 0 || num_vox == 0)
+    return set_error(F3D_ERR_ARG, "num_bucket, bucket_divisor, bucket_size and num_vox must be positive");
+  if (num_vox / divisor > num_bucket) return set_error(F3D_ERR_ARG, "bucket divisor too small");
+  if (pad_to < total_N)
+    return set_error(F3D_ERR_ARG, "Output coord buffer length(%u) is smaller than the input length(%u).", pad_to, total_N);
+  if (hash_type < 1 || hash_type > 4)
+    return set_error(F3D_ERR_ARG, "Currently only four types of hash modes are supported. Requested hash_type=%u is unsupported.", hash_type);
+  if (num_bucket > 0x7FFEu) return set_error(F3D_ERR_ARG, "num_bucket=%u exceeds the supported 32766", num_bucket);
+  if (num_vox > 0x10000u) return set_error(F3D_ERR_ARG, "num_vox=%u exceeds the 16-bit voxel range", num_vox);
+  return F3D_OK;
+}
+
+struct PshPlan { uint32_t tile, tiles_max, nbp; size_t scratch_words; size_t smem_hist, smem_rank; };
+
+static PshPlan psh_plan(uint32_t batch, uint32_t max_n, uint32_t nb) {
+  PshPlan p;
+  p.nbp = nb + 1;
+  uint32_t want = (max_n + 63) / 64;                 // aim for at most 64 tiles per scene
+  uint32_t tile = ((want + 2047) / 2048) * 2048;
+  if (tile < 2048) tile = 2048;
+  if (tile > kMaxTile) tile = kMaxTile;
+  p.tile = tile;
+  p.tiles_max = max_n ? (max_n + tile - 1) / tile : 1;
+  if (p.tiles_max == 0) p.tiles_max = 1;
+  size_t rows = (size_t)batch * p.tiles_max;
+  p.scratch_words = 2 * rows * p.nbp + 6 * (size_t)batch * p.nbp + 2 * rows;
+  p.smem_hist = tile_smem_bytes(p.nbp, 0);
+  p.smem_rank = tile_smem_bytes(p.nbp, tile);
+  return p;
+}
+
+static int psh_run(PshArgs a, const PshPlan &p, uint32_t *scratch, uint32_t max_n, cudaStream_t st) {
+  size_t rows = (size_t)a.batch * p.tiles_max;
+  uint32_t *w = scratch;
+  a.tabP = w; w += rows * p.nbp;
+  a.tabQ = w; w += rows * p.nbp;
+  a.count0 = w; w += (size_t)a.batch * p.nbp;
+  a.kept = w; w += (size_t)a.batch * p.nbp;
+  a.freeB = w; w += (size_t)a.batch * p.nbp;
+  a.rejpre = w; w += (size_t)a.batch * p.nbp;
+  a.cntB = w; w += (size_t)a.batch * p.nbp;
+  a.cntF = w; w += (size_t)a.batch * p.nbp;
+  a.tile_pending = w; w += rows;
+  a.tile_movers = w; w += rows;
+  a.tile = p.tile; a.tiles_max = p.tiles_max; a.nbp = p.nbp;
+
+  static bool attr_done[16] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 16 && !attr_done[dev]) {
+    // opt in once per device to the large dynamic shared memory the rank kernels may ask for
+    F3D_CUDA_TRY(cudaFuncSetAttribute(psh_hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    F3D_CUDA_TRY(cudaFuncSetAttribute(psh_rankA_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    F3D_CUDA_TRY(cudaFuncSetAttribute(psh_resolveB_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    F3D_CUDA_TRY(cudaFuncSetAttribute(psh_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    attr_done[dev] = true;
+  }
+  if (p.smem_rank > 200 * 1024) return set_error(F3D_ERR_UNSUPPORTED, "num_bucket=%u needs %zu bytes of shared memory", a.nb, p.smem_rank);
+
+  dim3 grid(p.tiles_max, a.batch);
+  // tabP is fully rewritten by K1 for live tiles; tabQ (round B) and the later tabP (round C) rows are
+  // accumulated with atomics and must start at zero.
+  F3D_CUDA_TRY(cudaMemsetAsync(a.tabQ, 0, rows * p.nbp * sizeof(uint32_t), st));
+  if (max_n > 0) {
+    psh_hist_kernel<<<grid, kPshThreads, p.smem_hist, st>>>(a);
+    psh_scanA_kernel<<<a.batch, kPshThreads, 0, st>>>(a);
+    psh_rankA_kernel<<<grid, kPshThreads, p.smem_rank, st>>>(a);
+    psh_scanB_kernel<<<a.batch, kPshThreads, 0, st>>>(a);
+    F3D_CUDA_TRY(cudaMemsetAsync(a.tabP, 0, rows * p.nbp * sizeof(uint32_t), st));
+    psh_resolveB_kernel<<<grid, kPshThreads, p.smem_rank, st>>>(a);
+    psh_scanC_kernel<<<a.batch, kPshThreads, 0, st>>>(a);
+  } else {
+    F3D_CUDA_TRY(cudaMemsetAsync(a.bucket_counter, 0, (size_t)a.batch * a.nb * 4, st));
+    F3D_CUDA_TRY(cudaMemsetAsync(a.cumsum_counter, 0, (size_t)a.batch * a.nb * 4, st));
+  }
+  uint32_t pad_rows = a.pad_to - a.total_N;
+  uint32_t gx = max_n ? p.tiles_max : 0;
+  uint32_t pad_blocks = (pad_rows + p.tile - 1) / p.tile;
+  if (pad_blocks > gx) gx = pad_blocks;
+  if (gx > 0) {
+    dim3 grid2(gx, a.batch + 1);
+    a.tiles_max = p.tiles_max;
+    psh_scatter_kernel<<<grid2, kPshThreads, p.smem_rank, st>>>(a);
+  }
+  return check_launch("psh kernels");
+}
+
+}  // namespace f3d
+
+using namespace f3d;
+
+extern "C" int f3d_batch_psh_scatter_pad_hash(
+    const void *coord, void *bucket_id, void *bucket_counter, void *bucket_offset, const void *batch_sep,
+    uint32_t total_N, uint32_t batch_size, uint32_t instance_max_N, uint32_t num_bucket, uint32_t bucket_divisor,
+    uint32_t bucket_size, uint32_t num_vox, const void *bbox_min, const void *bbox_max, const void *probe_offsets,
+    void *cumsum_counter, void *scatter_coord, uint32_t pad_to_N, float pad_num, uint32_t hash_type,
+    int device, void *stream) {
+  F3D_TRY(psh_validate(total_N, batch_size, num_bucket, bucket_divisor, bucket_size, num_vox, pad_to_N, hash_type));
+  DeviceGuard guard(device);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (instance_max_N > total_N) instance_max_N = total_N;
+  PshPlan p = psh_plan(batch_size, instance_max_N, num_bucket);
+  void *scratch = nullptr;
+  F3D_TRY(workspace(device, 0, p.scratch_words * sizeof(uint32_t), &scratch));
+  PshArgs a{};
+  a.coord = static_cast<const __half *>(coord);
+  a.bucket_id = static_cast<uint16_t *>(bucket_id);
+  a.bucket_counter = static_cast<uint32_t *>(bucket_counter);
+  a.bucket_offset = static_cast<uint32_t *>(bucket_offset);
+  a.batch_sep = static_cast<const uint32_t *>(batch_sep);
+  a.cumsum_counter = static_cast<uint32_t *>(cumsum_counter);
+  a.scatter_coord = static_cast<__half *>(scatter_coord);
+  a.bbox_min = static_cast<const __half *>(bbox_min);
+  a.bbox_max = static_cast<const __half *>(bbox_max);
+  a.probe = static_cast<const int16_t *>(probe_offsets);
+  a.total_N = total_N; a.batch = batch_size; a.nb = num_bucket; a.divisor = bucket_divisor; a.cap = bucket_size;
+  a.num_vox = num_vox; a.hash_type = hash_type; a.pad_to = pad_to_N;
+  a.pad_bits = __half_as_ushort(__float2half_rn(pad_num));
+  a.coord_aligned = (reinterpret_cast<uintptr_t>(coord) % 16 == 0) ? 1 : 0;
+  uint64_t sd = f3d::seed();
+  a.key.k0 = (uint32_t)sd; a.key.k1 = (uint32_t)(sd >> 32);
+  F3D_TRY(maybe_sync(st, "batch_psh_scatter_pad_hash"));
+  F3D_TRY(psh_run(a, p, static_cast<uint32_t *>(scratch), instance_max_N, st));
+  return maybe_sync(st, "batch_psh_scatter_pad_hash");
+}

@@ -1,0 +1,60 @@
+"""ctypes loader of libf3d_b200.so and the prototypes of its C ABI (include/f3d_b200.h).
+
+There is no CPU fallback: if the shared library is missing or a call fails, a RuntimeError is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_char_p, c_float, c_int, c_uint32, c_uint64, c_void_p
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libf3d_b200.so"
+
+_u32, _vp, _int, _f32 = c_uint32, c_void_p, c_int, c_float
+
+# name -> (restype, argtypes); mirrors include/f3d_b200.h declaration by declaration
+PROTOTYPES = {
+    "f3d_last_error": (c_char_p, []),
+    "f3d_version": (_int, []),
+    "f3d_init_device": (_int, [_int]),
+    "f3d_set_sync": (_int, [_int]),
+    "f3d_get_sync": (_int, []),
+    "f3d_set_seed": (_int, [c_uint64]),
+    "f3d_get_seed": (c_uint64, []),
+    "f3d_release_workspaces": (_int, []),
+    "f3d_batch_psh_scatter_pad_hash": (_int, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _u32, _u32,
+                                              _vp, _vp, _vp, _vp, _vp, _u32, _f32, _u32, _int, _vp]),
+}
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load the library once; raise loudly when it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m flash3dtransformer_b200.build` "
+            "(there is no CPU or PyTorch fallback for these operators)")
+    lib = ctypes.CDLL(os.fspath(LIB_PATH))
+    for name, (res, args) in PROTOTYPES.items():
+        fn = getattr(lib, name)          # AttributeError if the symbol is not exported
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def last_error() -> str:
+    msg = load().f3d_last_error()
+    return msg.decode("utf-8", "replace") if msg else ""
+
+
+def check(status: int, what: str) -> None:
+    """Turn a negative status into the RuntimeError the reference's bindings raise (std::runtime_error in
+    src/common/runtime.h:36-86 surfaces as RuntimeError through pybind11)."""
+    if status != 0:
+        raise RuntimeError(f"{what}: {last_error()} (status {status})")

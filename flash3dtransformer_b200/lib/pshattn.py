@@ -1,0 +1,151 @@
+"""Operator module with the surface of the reference's pybind11 extension `flash3dxfmr.lib.pshattn`
+(src/f3d_frontend.cu:112-138): same function names, same positional arguments, outputs mutated in place, errors
+raised as RuntimeError.  Each function unpacks torch tensors into device pointers and calls the C ABI of
+libf3d_b200.so (include/f3d_b200.h) on the tensor's device and torch's current stream.
+
+The two attention entry points the reference's Python layer calls but whose bindings are commented out in its
+snapshot (src/f3d_frontend.cu:136-137; callers flash3dxfmr/layers/buck_swin.py:57,91) are provided here.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _cabi
+
+HASH_ZORDER_DIV, HASH_XORSUM_DIV, HASH_ZORDER_MOD, HASH_XORSUM_MOD = 1, 2, 3, 4
+RED_MEAN, RED_SUM, RED_MIN, RED_MAX = 0, 1, 2, 3
+
+_FEAT_DTYPES = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
+
+
+# ------------------------------------------------------------------------------------------------ helpers
+def _require(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _check_tensors(tensors, names) -> torch.device:
+    """assert_contiguous + assert_same_device of src/common/runtime.h:36-70."""
+    dev = None
+    for t, n in zip(tensors, names):
+        _require(isinstance(t, torch.Tensor), f"{n} must be a torch.Tensor")
+        _require(t.is_contiguous(), f"Tensor {n} is not contiguous")
+        _require(t.is_cuda, f"Tensor {n} is not on a CUDA device (there is no CPU path)")
+        if dev is None:
+            dev = t.device
+        _require(t.device == dev, f"Tensor {n} is on {t.device}, expected {dev}")
+    return dev
+
+
+def _check_dtype(tensors, names, dtype) -> None:
+    """assert_dtype of src/common/runtime.h:72-86."""
+    for t, n in zip(tensors, names):
+        _require(t.dtype == dtype, f"Tensor {n} has dtype {t.dtype}, expected {dtype}")
+
+
+def _ptr(t: torch.Tensor) -> ctypes.c_void_p:
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _stream(dev: torch.device) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+
+
+def _dev_index(dev: torch.device) -> int:
+    return dev.index if dev.index is not None else torch.cuda.current_device()
+
+
+# ------------------------------------------------------------------------------- DeviceManagerSingleton
+class DeviceManagerSingleton:
+    """Mirror of f3d::DeviceManagerSingleton (src/common/device_manager.cuh:25-64, bindings
+    src/f3d_frontend.cu:115-120).  The reference keeps per-device cuRAND states and kernel dispatch tables here;
+    this build needs neither (stateless RNG, compile-time kernel selection), so only the device check, the
+    sync_stream flag and the seed remain."""
+    _inst = None
+
+    @staticmethod
+    def instance() -> "DeviceManagerSingleton":
+        if DeviceManagerSingleton._inst is None:
+            DeviceManagerSingleton._inst = DeviceManagerSingleton()
+        return DeviceManagerSingleton._inst
+
+    def __init__(self) -> None:
+        self._initialised = set()
+
+    def init_dev_info(self, dev_id: int) -> None:
+        if dev_id in self._initialised:
+            return
+        _cabi.check(_cabi.load().f3d_init_device(int(dev_id)), "init_dev_info")
+        self._initialised.add(dev_id)
+
+    def init_dispatchers(self) -> None:
+        _cabi.load()
+
+    def set_sync_stream(self, flag: bool) -> bool:
+        return bool(_cabi.load().f3d_set_sync(1 if flag else 0))
+
+    def get_sync_stream(self) -> bool:
+        return bool(_cabi.load().f3d_get_sync())
+
+    # additions of this build
+    def set_seed(self, seed: int) -> None:
+        _cabi.check(_cabi.load().f3d_set_seed(int(seed) & 0xFFFFFFFFFFFFFFFF), "set_seed")
+
+    def get_seed(self) -> int:
+        return int(_cabi.load().f3d_get_seed())
+
+
+# ----------------------------------------------------------------------------------------------- PSH scatter
+def batch_psh_scatter_pad_hash(coord, bucket_id, bucket_counter, bucket_offset, batch_sep, instance_max_N,
+                               num_bucket, bucket_divisor, bucket_size, num_vox, bbox_min, bbox_max,
+                               probe_offsets, cumsum_counter, scatter_coord, pad_num, hash_type) -> None:
+    """f3d::batch_psh_scatter_pad_hash (src/psh/batch_psh_bucket_dispatcher.cu:221-326)."""
+    names = ["coord", "bucket_id", "bucket_counter", "bucket_offset", "batch_sep", "probe_offsets",
+             "cumsum_counter", "scatter_coord", "bbox_min", "bbox_max"]
+    tensors = [coord, bucket_id, bucket_counter, bucket_offset, batch_sep, probe_offsets, cumsum_counter,
+               scatter_coord, bbox_min, bbox_max]
+    dev = _check_tensors(tensors, names)
+    _check_dtype([coord, scatter_coord, bbox_min, bbox_max], ["coord", "scatter_coord", "bbox_min", "bbox_max"],
+                 torch.float16)
+    _check_dtype([bucket_counter, bucket_offset, batch_sep, cumsum_counter],
+                 ["bucket_counter", "bucket_offset", "batch_sep", "cumsum_counter"], torch.uint32)
+    _check_dtype([bucket_id], ["bucket_id"], torch.uint16)
+    _check_dtype([probe_offsets], ["probe_offsets"], torch.int16)
+    _require(coord.dim() == 2 and coord.shape[1] == 3, f"coord must be [N,3], got {tuple(coord.shape)}")
+    _require(scatter_coord.dim() == 2 and scatter_coord.shape[1] == 3, "scatter_coord must be [pad_to,3]")
+    total_n = coord.shape[0]
+    batch = batch_sep.shape[0]
+    _require(bucket_id.numel() >= total_n and bucket_offset.numel() >= total_n,
+             "bucket_id / bucket_offset are shorter than coord")
+    _require(bucket_counter.numel() == batch * num_bucket and cumsum_counter.numel() == batch * num_bucket,
+             f"bucket_counter / cumsum_counter must be [{batch},{num_bucket}]")
+    _require(probe_offsets.numel() == 128 * 3, "probe_offsets must be [128,3]")
+    _require(bbox_min.numel() == 3 and bbox_max.numel() == 3, "bbox_min / bbox_max must have 3 elements")
+    st = _cabi.load().f3d_batch_psh_scatter_pad_hash(
+        _ptr(coord), _ptr(bucket_id), _ptr(bucket_counter), _ptr(bucket_offset), _ptr(batch_sep),
+        total_n, batch, int(instance_max_N), int(num_bucket), int(bucket_divisor), int(bucket_size), int(num_vox),
+        _ptr(bbox_min), _ptr(bbox_max), _ptr(probe_offsets), _ptr(cumsum_counter), _ptr(scatter_coord),
+        scatter_coord.shape[0], float(pad_num), int(hash_type), _dev_index(dev), _stream(dev))
+    _cabi.check(st, "batch_psh_scatter_pad_hash")
+
+
+def batch_psh_scatter_pad(coord, bucket_id, bucket_counter, bucket_offset, batch_sep, instance_max_N, num_bucket,
+                          bucket_divisor, bucket_size, num_vox, bbox_min, bbox_max, probe_offsets, cumsum_counter,
+                          scatter_coord, pad_num) -> None:
+    """f3d::batch_psh_scatter_pad (src/psh/batch_psh_bucket_dispatcher.cu:123-219): Z-order-mod hash."""
+    batch_psh_scatter_pad_hash(coord, bucket_id, bucket_counter, bucket_offset, batch_sep, instance_max_N,
+                               num_bucket, bucket_divisor, bucket_size, num_vox, bbox_min, bbox_max, probe_offsets,
+                               cumsum_counter, scatter_coord, pad_num, HASH_ZORDER_MOD)
+
+
+def batch_psh_scatter(coord, bucket_id, bucket_counter, bucket_offset, batch_sep, instance_max_N, num_bucket,
+                      bucket_divisor, bucket_size, num_vox, bbox_min, bbox_max, probe_offsets, cumsum_counter,
+                      scatter_coord, hash_dtype=None, coord_dtype=None, block_size_N=1024) -> None:
+    """f3d::batch_psh_scatter (src/psh/batch_psh_bucket_dispatcher.cu:39-121): Z-order-mod hash, no tail padding
+    beyond what scatter_coord holds.  hash_dtype, coord_dtype and block_size_N are accepted and ignored, as the
+    dtypes are fixed (u16 / fp16) and the tile size is chosen by the library."""
+    batch_psh_scatter_pad_hash(coord, bucket_id, bucket_counter, bucket_offset, batch_sep, instance_max_N,
+                               num_bucket, bucket_divisor, bucket_size, num_vox, bbox_min, bbox_max, probe_offsets,
+                               cumsum_counter, scatter_coord, 0.0, HASH_ZORDER_MOD)

@@ -1,0 +1,74 @@
+/* C ABI of libf3d_b200.so: the sm_100a kernels behind the Flash3D operator module
+ * flash3dxfmr.lib.pshattn (reference bindings: src/f3d_frontend.cu:112-138).
+ *
+ * Conventions
+ *  - every tensor argument is a DEVICE pointer to a contiguous row-major buffer of the stated dtype/shape;
+ *    outputs are caller-allocated and written in place, exactly like the reference's at::Tensor& outputs;
+ *  - sizes the reference reads from tensor shapes are passed explicitly;
+ *  - `device` is the CUDA ordinal the buffers live on, `stream` a cudaStream_t (NULL = legacy default stream);
+ *    the reference uses c10::cuda::getCurrentCUDAStream of the tensor's device
+ *    (src/psh/batch_psh_bucket_dispatcher.cu:256);
+ *  - return value 0 = ok, < 0 = error; the message is available from f3d_last_error() on the calling thread.
+ *    The reference throws std::runtime_error for argument errors (src/common/runtime.h:36-86) and calls exit()
+ *    on CUDA errors (src/common/runtime.h:29-34); this library returns in both cases.
+ */
+#ifndef F3D_B200_H
+#define F3D_B200_H
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define F3D_STATUS_OK 0
+#define F3D_STATUS_BAD_ARGUMENT (-1)
+#define F3D_STATUS_CUDA_ERROR (-2)
+#define F3D_STATUS_UNSUPPORTED (-3)
+#define F3D_STATUS_DEVICE (-4)
+
+/* feature element types for the pooling / unpooling entry points */
+#define F3D_DTYPE_BF16 0
+#define F3D_DTYPE_FP16 1
+#define F3D_DTYPE_FP32 2
+
+/* ---- runtime state: replaces DeviceManagerSingleton (src/common/device_manager.cuh:25-64) ---- */
+const char *f3d_last_error(void);
+int f3d_version(void);
+/* DeviceManagerSingleton::init_dev_info (src/common/device_manager.cu:73-99): checks the device is sm_100 */
+int f3d_init_device(int device);
+/* DeviceManagerSingleton::set_sync_stream / get_sync_stream (src/common/device_manager.cu:113-119);
+ * returns the previous value */
+int f3d_set_sync(int on);
+int f3d_get_sync(void);
+/* seed of the counter-based generator that replaces the per-device cuRAND states
+ * (src/common/device_manager.cu:58-67, seed 3407) */
+int f3d_set_seed(uint64_t seed);
+uint64_t f3d_get_seed(void);
+/* frees the library's cached scratch buffers on every device */
+int f3d_release_workspaces(void);
+
+/* ---- PSH bucketing + scatter ----
+ * replaces f3d::batch_psh_scatter_pad_hash (src/psh/batch_psh_bucket_dispatcher.cu:221-326; binding
+ * src/f3d_frontend.cu:120).  batch_psh_scatter and batch_psh_scatter_pad (same file :39-121, :123-219) are the
+ * same call with hash_type = 3 (Z-order mod) and, for the former, pad_to_N = total_N.
+ *   coord          fp16 [total_N,3]        in
+ *   bucket_id      u16  [total_N]          out
+ *   bucket_counter u32  [batch,num_bucket] out (final per-scene bucket sizes)
+ *   bucket_offset  u32  [total_N]          out
+ *   batch_sep      u32  [batch]            in  (inclusive end row of each scene)
+ *   bbox_min/max   fp16 [3]                in
+ *   probe_offsets  i16  [128,3]            in
+ *   cumsum_counter u32  [batch,num_bucket] out (inclusive cumsum of bucket_counter)
+ *   scatter_coord  fp16 [pad_to_N,3]       out; rows [total_N,pad_to_N) are set to pad_num
+ */
+int f3d_batch_psh_scatter_pad_hash(
+    const void *coord, void *bucket_id, void *bucket_counter, void *bucket_offset, const void *batch_sep,
+    uint32_t total_N, uint32_t batch_size, uint32_t instance_max_N, uint32_t num_bucket, uint32_t bucket_divisor,
+    uint32_t bucket_size, uint32_t num_vox, const void *bbox_min, const void *bbox_max, const void *probe_offsets,
+    void *cumsum_counter, void *scatter_coord, uint32_t pad_to_N, float pad_num, uint32_t hash_type,
+    int device, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* F3D_B200_H */
