@@ -149,3 +149,108 @@ def batch_psh_scatter(coord, bucket_id, bucket_counter, bucket_offset, batch_sep
     batch_psh_scatter_pad_hash(coord, bucket_id, bucket_counter, bucket_offset, batch_sep, instance_max_N,
                                num_bucket, bucket_divisor, bucket_size, num_vox, bbox_min, bbox_max, probe_offsets,
                                cumsum_counter, scatter_coord, 0.0, HASH_ZORDER_MOD)
+
+
+# ------------------------------------------------------------------------------------- pooling / unpooling
+def _feat_code(t: torch.Tensor, name: str) -> int:
+    _require(t.dtype in _FEAT_DTYPES, f"Tensor {name} has dtype {t.dtype}; bfloat16, float16 and float32 are supported")
+    return _FEAT_DTYPES[t.dtype]
+
+
+def batch_subbuck_reduce(scattered_coord, scattered_feat, batch_sep, instance_max_N, subbuck_size, num_vox,
+                         bbox_min, bbox_max, subbuck_id, subbuck_off, reduced_batch_sep, reduced_coord,
+                         reduced_feat, unpool_ind, hash_type, red_op) -> None:
+    """f3d::batch_subbuck_reduce (src/psh/batch_subbuck_pooling_dispatcher.cu:35-144)."""
+    names = ["scattered_coord", "scattered_feat", "batch_sep", "subbuck_id", "subbuck_off", "reduced_batch_sep",
+             "reduced_coord", "reduced_feat", "unpool_ind", "bbox_min", "bbox_max"]
+    tensors = [scattered_coord, scattered_feat, batch_sep, subbuck_id, subbuck_off, reduced_batch_sep,
+               reduced_coord, reduced_feat, unpool_ind, bbox_min, bbox_max]
+    dev = _check_tensors(tensors, names)
+    code = _feat_code(scattered_feat, "scattered_feat")
+    _check_dtype([reduced_feat], ["reduced_feat"], scattered_feat.dtype)
+    _check_dtype([scattered_coord, reduced_coord, bbox_min, bbox_max],
+                 ["scattered_coord", "reduced_coord", "bbox_min", "bbox_max"], torch.float16)
+    _check_dtype([batch_sep, subbuck_id, reduced_batch_sep, unpool_ind],
+                 ["batch_sep", "subbuck_id", "reduced_batch_sep", "unpool_ind"], torch.uint32)
+    _check_dtype([subbuck_off], ["subbuck_off"], torch.uint16)
+    _require(scattered_feat.shape[1] == reduced_feat.shape[1],
+             f"Input feature dim({scattered_feat.shape[1]}) != output feature dim({reduced_feat.shape[1]}).")
+    _require(reduced_coord.shape[0] == reduced_feat.shape[0],
+             f"Reduced coordinate length({reduced_coord.shape[0]}) != reduced feature length({reduced_feat.shape[0]}).")
+    _require(scattered_coord.shape[1] == 3 and reduced_coord.shape[1] == 3,
+             f"Input coordinates dim({scattered_coord.shape[1]}) or reduced coordinates dim({reduced_coord.shape[1]}) "
+             "are NOT 3D.")
+    _require(0 <= int(red_op) <= 3, f"Unsupported reduction operation id-{red_op}")
+    _require(unpool_ind.dim() == 2 and unpool_ind.shape[1] == subbuck_size,
+             f"Unpool_ind last dimension({unpool_ind.shape[-1]}) != subbucket_size({subbuck_size})")
+    total_n = scattered_coord.shape[0]
+    _require(scattered_feat.shape[0] >= total_n, "scattered_feat has fewer rows than scattered_coord")
+    _require(subbuck_id.numel() >= total_n and subbuck_off.numel() >= total_n, "subbuck_id / subbuck_off too short")
+    _require(reduced_batch_sep.shape[0] == batch_sep.shape[0], "reduced_batch_sep and batch_sep differ in length")
+    st = _cabi.load().f3d_batch_subbuck_reduce(
+        _ptr(scattered_coord), _ptr(scattered_feat), _ptr(batch_sep), total_n, batch_sep.shape[0],
+        int(instance_max_N), int(subbuck_size), int(num_vox), _ptr(bbox_min), _ptr(bbox_max), _ptr(subbuck_id),
+        _ptr(subbuck_off), _ptr(reduced_batch_sep), _ptr(reduced_coord), _ptr(reduced_feat), _ptr(unpool_ind),
+        unpool_ind.shape[0], reduced_feat.shape[0], scattered_feat.shape[1], code, int(hash_type), int(red_op),
+        _dev_index(dev), _stream(dev))
+    _cabi.check(st, "batch_subbuck_reduce")
+
+
+def batch_subbuck_reduce_backward(grad_red_feat, input_feat, unpool_ind, grad_input_feat, subbuck_size,
+                                  reduction_op) -> None:
+    """f3d::batch_subbuck_reduce_backward (src/psh/batch_subbuck_pooling_bwd_dispatcher.cu:26-85)."""
+    dev = _check_tensors([grad_red_feat, input_feat, unpool_ind, grad_input_feat],
+                         ["grad_red_feat", "input_feat", "unpool_ind", "grad_input_feat"])
+    code = _feat_code(input_feat, "input_feat")
+    _check_dtype([grad_red_feat, grad_input_feat], ["grad_red_feat", "grad_input_feat"], input_feat.dtype)
+    _check_dtype([unpool_ind], ["unpool_ind"], torch.uint32)
+    _require(unpool_ind.dim() == 2 and unpool_ind.shape[1] == subbuck_size,
+             f"Unpool_ind last dimension({unpool_ind.shape[-1]}) != subbucket_size({subbuck_size})")
+    _require(grad_red_feat.shape[0] >= unpool_ind.shape[0], "grad_red_feat has fewer rows than unpool_ind")
+    _require(grad_red_feat.shape[1] == input_feat.shape[1] == grad_input_feat.shape[1], "feature dims differ")
+    _require(grad_input_feat.shape[0] == input_feat.shape[0], "grad_input_feat and input_feat differ in length")
+    _require(0 <= int(reduction_op) <= 3, f"Unsupported reduction_op={reduction_op}")
+    st = _cabi.load().f3d_batch_subbuck_reduce_backward(
+        _ptr(grad_red_feat), _ptr(input_feat), _ptr(unpool_ind), _ptr(grad_input_feat), input_feat.shape[0],
+        unpool_ind.shape[0], input_feat.shape[1], code, int(subbuck_size), int(reduction_op), _dev_index(dev),
+        _stream(dev))
+    _cabi.check(st, "batch_subbuck_reduce_backward")
+
+
+def additive_unpool_fwd(res_feat, down_feat, up_add_feat, unpool_ind, subbuck_size, covered_rows=None) -> None:
+    """f3d::additive_unpool_fwd (src/psh/additive_unpool_dispatcher.cu:26-79).  `covered_rows` (not in the
+    reference) is the number of leading rows that unpool_ind refers to; rows behind it are zero-filled instead of
+    being left uninitialised.  None keeps the reference behaviour."""
+    dev = _check_tensors([res_feat, down_feat, up_add_feat, unpool_ind],
+                         ["res_feat", "down_feat", "up_add_feat", "unpool_ind"])
+    code = _feat_code(res_feat, "res_feat")
+    _check_dtype([down_feat, up_add_feat], ["down_feat", "up_add_feat"], res_feat.dtype)
+    _check_dtype([unpool_ind], ["unpool_ind"], torch.uint32)
+    _require(unpool_ind.dim() == 2 and unpool_ind.shape[1] == subbuck_size,
+             f"Unpool_ind last dimension({unpool_ind.shape[-1]}) != subbucket_size({subbuck_size})")
+    _require(res_feat.shape == up_add_feat.shape, "res_feat and up_add_feat differ in shape")
+    _require(down_feat.shape[0] >= unpool_ind.shape[0], "down_feat has fewer rows than unpool_ind")
+    _require(down_feat.shape[1] == res_feat.shape[1], "feature dims differ")
+    up_rows = res_feat.shape[0]
+    st = _cabi.load().f3d_additive_unpool_fwd(
+        _ptr(res_feat), _ptr(down_feat), _ptr(up_add_feat), _ptr(unpool_ind), up_rows, unpool_ind.shape[0],
+        up_rows if covered_rows is None else int(covered_rows), res_feat.shape[1], code, int(subbuck_size),
+        _dev_index(dev), _stream(dev))
+    _cabi.check(st, "additive_unpool_fwd")
+
+
+def additive_unpool_bwd(grad_res, grad_down, grad_up_added, unpool_ind, subbuck_size) -> None:
+    """f3d::additive_unpool_bwd (src/psh/additive_unpool_dispatcher.cu:81-134)."""
+    dev = _check_tensors([grad_res, grad_down, grad_up_added, unpool_ind],
+                         ["grad_res", "grad_down", "grad_up_added", "unpool_ind"])
+    code = _feat_code(grad_up_added, "grad_up_added")
+    _check_dtype([grad_res, grad_down], ["grad_res", "grad_down"], grad_up_added.dtype)
+    _check_dtype([unpool_ind], ["unpool_ind"], torch.uint32)
+    _require(unpool_ind.dim() == 2 and unpool_ind.shape[1] == subbuck_size,
+             f"Unpool_ind last dimension({unpool_ind.shape[-1]}) != subbucket_size({subbuck_size})")
+    _require(grad_res.shape == grad_up_added.shape, "grad_res and grad_up_added differ in shape")
+    _require(grad_down.shape[0] >= unpool_ind.shape[0], "grad_down has fewer rows than unpool_ind")
+    st = _cabi.load().f3d_additive_unpool_bwd(
+        _ptr(grad_res), _ptr(grad_down), _ptr(grad_up_added), _ptr(unpool_ind), grad_up_added.shape[0],
+        unpool_ind.shape[0], grad_up_added.shape[1], code, int(subbuck_size), _dev_index(dev), _stream(dev))
+    _cabi.check(st, "additive_unpool_bwd")

@@ -68,6 +68,52 @@ int f3d_batch_psh_scatter_pad_hash(
     void *cumsum_counter, void *scatter_coord, uint32_t pad_to_N, float pad_num, uint32_t hash_type,
     int device, void *stream);
 
+/* ---- sub-bucket construction + feature pooling ----
+ * replaces f3d::batch_subbuck_reduce (src/psh/batch_subbuck_pooling_dispatcher.cu:35-144; binding
+ * src/f3d_frontend.cu:127): local_subbuck_ker followed by reduce_feat_ker.
+ *   scattered_coord   fp16 [total_N,3]                 in
+ *   scattered_feat    feat_dtype [>= total_N, feat_dim] in
+ *   batch_sep         u32 [batch]                      in
+ *   bbox_min/max      fp16 [3]                         in  (accepted for signature parity; the hash normalises
+ *                                                          with each 1024-point block's own bounding box)
+ *   subbuck_id        u32 [total_N]                    out (row inside the scene's reduced rows)
+ *   subbuck_off       u16 [total_N]                    out (slot inside the sub-bucket)
+ *   reduced_batch_sep u32 [batch]                      in  (inclusive end of each scene's reduced rows)
+ *   reduced_coord     fp16 [reduced_rows,3]            out (mean member coordinate; rows >= unpool_rows := 0)
+ *   reduced_feat      feat_dtype [reduced_rows,feat_dim] out (rows >= unpool_rows := 0)
+ *   unpool_ind        u32 [unpool_rows,subbuck_size]   in/out (caller pre-fills with a value >= total_N)
+ *   red_op            0 mean, 1 sum, 2 min, 3 max
+ */
+int f3d_batch_subbuck_reduce(
+    const void *scattered_coord, const void *scattered_feat, const void *batch_sep, uint32_t total_N,
+    uint32_t batch_size, uint32_t instance_max_N, uint32_t subbuck_size, uint32_t num_vox, const void *bbox_min,
+    const void *bbox_max, void *subbuck_id, void *subbuck_off, const void *reduced_batch_sep, void *reduced_coord,
+    void *reduced_feat, void *unpool_ind, uint32_t unpool_rows, uint32_t reduced_rows, uint32_t feat_dim,
+    int feat_dtype, uint32_t hash_type, uint32_t red_op, int device, void *stream);
+
+/* replaces f3d::batch_subbuck_reduce_backward (src/psh/batch_subbuck_pooling_bwd_dispatcher.cu:26-85; binding
+ * src/f3d_frontend.cu:128).  grad_input_feat must be zero-initialised by the caller
+ * (flash3dxfmr/layers/pooling.py:102); only rows referenced by unpool_ind are written. */
+int f3d_batch_subbuck_reduce_backward(
+    const void *grad_red_feat, const void *input_feat, const void *unpool_ind, void *grad_input_feat, uint32_t total_N,
+    uint32_t unpool_rows, uint32_t feat_dim, int feat_dtype, uint32_t subbuck_size, uint32_t red_op, int device,
+    void *stream);
+
+/* replaces f3d::additive_unpool_fwd (src/psh/additive_unpool_dispatcher.cu:26-79; binding
+ * src/f3d_frontend.cu:123): up[r] = res[r] + down[i] for every valid r = unpool_ind[i, s].
+ * Rows [covered_rows, up_rows) of up_add_feat, which no index refers to (tail padding), are set to zero; pass
+ * covered_rows = up_rows to leave them untouched as the reference does. */
+int f3d_additive_unpool_fwd(
+    const void *res_feat, const void *down_feat, void *up_add_feat, const void *unpool_ind, uint32_t up_rows,
+    uint32_t unpool_rows, uint32_t covered_rows, uint32_t feat_dim, int feat_dtype, uint32_t subbuck_size, int device,
+    void *stream);
+
+/* replaces f3d::additive_unpool_bwd (src/psh/additive_unpool_dispatcher.cu:81-134; binding
+ * src/f3d_frontend.cu:124): grad_res[r] = g[r]; grad_down[i] = sum_s g[unpool_ind[i,s]]. */
+int f3d_additive_unpool_bwd(
+    void *grad_res, void *grad_down, const void *grad_up_added, const void *unpool_ind, uint32_t up_rows,
+    uint32_t unpool_rows, uint32_t feat_dim, int feat_dtype, uint32_t subbuck_size, int device, void *stream);
+
 #ifdef __cplusplus
 }
 #endif
