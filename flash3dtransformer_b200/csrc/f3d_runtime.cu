@@ -50,6 +50,24 @@ int workspace(int device, int slot, size_t bytes, void **out) {
   return F3D_OK;
 }
 
+static std::mutex g_st_mu;
+static int *g_status[16] = {nullptr};
+
+// Device word that kernels with bounded waits set (once, with atomicCAS) when a wait is abandoned.
+int *status_word(int device) {
+  std::lock_guard<std::mutex> lk(g_st_mu);
+  if (device < 0 || device >= 16) { set_error(F3D_ERR_ARG, "device %d out of range", device); return nullptr; }
+  if (!g_status[device]) {
+    int *p = nullptr;
+    if (cudaMalloc(&p, 256) != cudaSuccess || cudaMemset(p, 0, 256) != cudaSuccess) {
+      set_error(F3D_ERR_CUDA, "cannot allocate the device status word");
+      return nullptr;
+    }
+    g_status[device] = p;
+  }
+  return g_status[device];
+}
+
 void workspace_release_all() {
   std::lock_guard<std::mutex> lk(g_ws_mu);
   for (auto &kv : g_ws) {
@@ -84,6 +102,20 @@ int f3d_init_device(int device) {
   cudaDeviceProp p;
   F3D_CUDA_TRY(cudaGetDeviceProperties(&p, device));
   if (p.major != 10) return f3d::set_error(F3D_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library holds sm_100a code only", device, p.major, p.minor);
+  return F3D_OK;
+}
+
+int f3d_device_status(int device) {
+  f3d::DeviceGuard guard(device);
+  int *p = f3d::status_word(device);
+  if (!p) return F3D_ERR_CUDA;
+  int v = 0;
+  F3D_CUDA_TRY(cudaDeviceSynchronize());
+  F3D_CUDA_TRY(cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost));
+  if (v != 0) {
+    cudaMemset(p, 0, sizeof(int));
+    return f3d::set_error(F3D_ERR_DEVICE_STATUS, "a kernel abandoned a bounded wait (site code %d)", v);
+  }
   return F3D_OK;
 }
 

@@ -1,0 +1,361 @@
+// bf16 GEMM for the per-token projections: C[M,N] = A[M,K] . W[N,K]^T (+ bias) (+ residual), fp32 accumulation.
+//
+// Replaces the cuBLAS calls behind nn.Linear in the reference's attention block (qkv and proj,
+// flash3dxfmr/layers/buck_swin.py:159,163,185-194) and the toy mma.sync kernel gemm_sm_bf16_ker
+// (src/psh/gemm.cuh:30-85, host src/psh/gemm_dispatcher.cu:26-80, which demands M == 128 and synchronises).
+//
+// Structure (one persistent CTA per SM, 192 threads):
+//   warp 0      TMA producer: A tile 128x64 and W tile BNx64 per stage, 128-byte swizzle, mbarrier completion
+//   warp 1      owns tensor memory; one elected lane issues tcgen05.mma (M=128, N=BN, K=16) four times per
+//               stage and commits the stage's "empty" barrier; after the last k-block it commits "accumulator full"
+//   warps 2-5   epilogue: tcgen05.ld the 128xBN fp32 accumulator (each warp its 32-lane quadrant), add bias /
+//               residual, convert to bf16, stage in swizzled shared memory and write with TMA stores
+// Two accumulators (2*BN tensor-memory columns) let the epilogue of tile i overlap the MMAs of tile i+1.
+// Outputs may be split column-wise into `nsplit` separate [M, N/nsplit] matrices (Q, K, V written directly in
+// the [L, H*D] layout the attention kernel reads, instead of three .contiguous() copies,
+// flash3dxfmr/layers/buck_swin.py:188-190).
+#include "f3d_common.cuh"
+#include "tc_sm100.cuh"
+#include "../../include/f3d_b200.h"
+
+namespace f3d {
+
+constexpr int kGemmThreads = 192;
+constexpr int BM = 128;
+constexpr int BK = 64;
+
+enum GemmEpilogue : int { EPI_NONE = 0, EPI_GELU = 1, EPI_SWIGLU = 2 };
+
+struct GemmArgs {
+  int M, N, K;
+  int nsplit;            // output column splits
+  int split_n;           // N / nsplit (columns per split; for SWIGLU: output columns = N/2)
+  const float *bias;     // [N] fp32 or null
+  const __nv_bfloat16 *residual;   // [M, ldr] bf16 or null (added after bias; only with nsplit == 1)
+  int ldr;
+  int epilogue;
+  int direct_store;      // 1: plain 16-byte global stores instead of TMA stores (split rows shorter than a 64-column chunk)
+  __nv_bfloat16 *c_ptr;
+  long long split_stride;
+  int *status;
+};
+
+template <int BN> struct GemmSmem {
+  static constexpr int kStages = BN >= 256 ? 3 : 4;
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kOutBytes = 4 /*warps*/ * 2 /*buffers*/ * 32 * 128;   // 32 rows x 64 bf16 per buffer
+  static constexpr int kBarBytes = 256;
+  static constexpr int kTotal = kStages * kStageBytes + kOutBytes + kBarBytes + 1024 /*alignment slack*/;
+};
+
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  float u = k0 * (x + k1 * x * x * x);
+  return 0.5f * x * (1.f + tanhf(u));
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         const __grid_constant__ CUtensorMap map_c, GemmArgs g) {
+  using S = GemmSmem<BN>;
+  constexpr int kStages = S::kStages;
+  constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char *stage_base = smem;
+  unsigned char *out_base = smem + kStages * S::kStageBytes;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(out_base + S::kOutBytes);
+  uint64_t *full = bars, *empty = bars + kStages, *acc_full = bars + 2 * kStages, *acc_empty = bars + 2 * kStages + 2;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 4);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tiles = (g.M + BM - 1) / BM, n_tiles = (g.N + BN - 1) / BN;
+  const int num_tiles = m_tiles * n_tiles;
+  const int kb_count = (g.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { tc::mbar_init(&full[s], 1); tc::mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { tc::mbar_init(&acc_full[a], 1); tc::mbar_init(&acc_empty[a], 4); }
+    *abort_flag = 0;
+    tc::mbar_fence_init();
+  }
+  if (warp == 1) { tc::tmem_alloc(tmem_slot, kTmemCols); tc::tmem_relinquish(); }
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  tc::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  tc::WaitCtx wc{abort_flag, g.status};
+
+  if (warp == 0) {
+    if (tc::elect_one()) {
+      tc::tma_prefetch_desc(&map_a); tc::tma_prefetch_desc(&map_b); tc::tma_prefetch_desc(&map_c);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile / n_tiles) * BM, n0 = (tile % n_tiles) * BN;
+        for (int kb = 0; kb < kb_count; ++kb, ++it) {
+          const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+          if (!tc::mbar_wait(&empty[s], ph ^ 1u, wc, 101)) { ok = false; break; }
+          unsigned char *sa = stage_base + s * S::kStageBytes;
+          tc::mbar_expect_tx(&full[s], S::kStageBytes);
+          tc::tma_load_2d(sa, &map_a, &full[s], kb * BK, m0);
+          if (g.epilogue == EPI_SWIGLU) {
+            // gate rows [n0/2, n0/2 + BN/2) and up rows [N/2 + n0/2, ...) of W share one tile
+            tc::tma_load_2d(sa + S::kABytes, &map_b, &full[s], kb * BK, n0 / 2);
+            tc::tma_load_2d(sa + S::kABytes + S::kBBytes / 2, &map_b, &full[s], kb * BK, g.N / 2 + n0 / 2);
+          } else {
+            tc::tma_load_2d(sa + S::kABytes, &map_b, &full[s], kb * BK, n0);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (tc::elect_one()) {
+      constexpr uint32_t idesc = tc::make_idesc_f16(BM, BN, true, false, false);
+      uint32_t it = 0, t_local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t_local) {
+        const uint32_t acc = t_local & 1u, aph = (t_local >> 1) & 1u;
+        if (!tc::mbar_wait(&acc_empty[acc], aph ^ 1u, wc, 102)) { ok = false; break; }
+        tc::tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < kb_count; ++kb, ++it) {
+          const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+          if (!tc::mbar_wait(&full[s], ph, wc, 103)) { ok = false; break; }
+          tc::tc_fence_after_sync();
+          const uint32_t sa = tc::smem_u32(stage_base + s * S::kStageBytes);
+          const uint64_t adesc = tc::kmajor_sw128_desc(sa), bdesc = tc::kmajor_sw128_desc(sa + S::kABytes);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            tc::mma_f16_ss(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          tc::mma_commit(&empty[s]);
+        }
+        if (ok) tc::mma_commit(&acc_full[acc]);
+      }
+    }
+  } else {
+    const int q = warp & 3;                       // tensor-memory lane quadrant this warp may read
+    unsigned char *my_out = out_base + (warp - 2) * 2 * 32 * 128;
+    uint32_t t_local = 0, obuf = 0;
+    bool ok = true;
+    const int out_cols = g.epilogue == EPI_SWIGLU ? BN / 2 : BN;     // output columns produced per tile
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t_local) {
+      const uint32_t acc = t_local & 1u, aph = (t_local >> 1) & 1u;
+      const int m0 = (tile / n_tiles) * BM, n0 = (tile % n_tiles) * BN;
+      if (!tc::mbar_wait(&acc_full[acc], aph, wc, 104)) { ok = false; break; }
+      tc::tc_fence_after_sync();
+      const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+      const int row = m0 + q * 32 + lane;
+      for (int c0 = 0; c0 < out_cols; c0 += 64) {
+        const int ncol = min(64, out_cols - c0);             // 32 or 64 columns in this chunk
+        float v[64];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          if (h * 32 < ncol) {
+            uint32_t r[32];
+            tc::tmem_ld_32x32b_x32(t_row + c0 + h * 32, r);
+            if (g.epilogue == EPI_SWIGLU) {
+              uint32_t u[32];
+              tc::tmem_ld_32x32b_x32(t_row + BN / 2 + c0 + h * 32, u);
+              tc::tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const int col = n0 / 2 + c0 + h * 32 + j;
+                float gt = __uint_as_float(r[j]) + (g.bias ? __ldg(g.bias + col) : 0.f);
+                float up = __uint_as_float(u[j]) + (g.bias ? __ldg(g.bias + g.N / 2 + col) : 0.f);
+                v[h * 32 + j] = gt / (1.f + __expf(-gt)) * up;
+              }
+            } else {
+              tc::tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const int col = n0 + c0 + h * 32 + j;
+                float x = __uint_as_float(r[j]);
+                if (g.bias && col < g.N) x += __ldg(g.bias + col);
+                if (g.epilogue == EPI_GELU) x = gelu_tanh(x);
+                v[h * 32 + j] = x;
+              }
+            }
+          }
+        }
+        if (g.residual && row < g.M) {
+          const __nv_bfloat16 *rp = g.residual + (size_t)row * g.ldr + n0 + c0;
+          const bool vec_ok = (n0 + c0 + ncol <= g.N) && ((reinterpret_cast<uintptr_t>(rp) & 15) == 0);
+          if (vec_ok) {
+#pragma unroll
+            for (int j = 0; j < 64; j += 8) {
+              if (j < ncol) {
+                uint4 w = __ldg(reinterpret_cast<const uint4 *>(rp + j));
+                const __nv_bfloat162 *h2 = reinterpret_cast<const __nv_bfloat162 *>(&w);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { float2 f = __bfloat1622float2(h2[e]); v[j + 2 * e] += f.x; v[j + 2 * e + 1] += f.y; }
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) if (j < ncol && n0 + c0 + j < g.N) v[j] += __bfloat162float(rp[j]);
+          }
+        }
+        if (g.direct_store) {
+          if (row < g.M) {
+#pragma unroll
+            for (int j = 0; j < 64; j += 8) {
+              const int oc = n0 + c0 + j;
+              if (j >= ncol || oc >= g.N) continue;
+              uint4 w;
+              __nv_bfloat162 *h2 = reinterpret_cast<__nv_bfloat162 *>(&w);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(v[j + 2 * e], v[j + 2 * e + 1]);
+              *reinterpret_cast<uint4 *>(g.c_ptr + (size_t)(oc / g.split_n) * g.split_stride + (size_t)row * g.split_n + oc % g.split_n) = w;
+            }
+          }
+          continue;
+        }
+        // stage 32 rows x 64 columns (128 bytes per row) in the layout the 128-byte-swizzled TMA store reads
+        unsigned char *ob = my_out + obuf * 32 * 128;
+        if (lane == 0) tc::tma_wait_read<1>();    // the store issued two chunks ago has drained this buffer
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          uint4 w;
+          __nv_bfloat162 *h2 = reinterpret_cast<__nv_bfloat162 *>(&w);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(v[j * 8 + 2 * e], v[j * 8 + 2 * e + 1]);
+          if (j * 8 < ncol) *reinterpret_cast<uint4 *>(ob + lane * 128 + ((j ^ (lane & 7)) * 16)) = w;
+        }
+        tc::fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+          const int oc = (g.epilogue == EPI_SWIGLU ? n0 / 2 : n0) + c0;   // output column
+          const int sp = oc / g.split_n, xc = oc % g.split_n;
+          tc::tma_store_3d(&map_c, ob, xc, m0 + q * 32, sp);
+          tc::tma_commit();
+        }
+        obuf ^= 1u;
+      }
+      tc::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(&acc_empty[acc]);
+    }
+    if (lane == 0) tc::tma_wait_all<0>();
+  }
+
+  __syncthreads();
+  if (*abort_flag) {
+    // a wait was abandoned: give copies that may still be in flight time to land before the CTA retires
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) { tc::tc_fence_after_sync(); tc::tmem_dealloc(tmem_base, kTmemCols); }
+}
+
+static int g_sm_count[16] = {0};
+
+static int sm_count(int device) {
+  if (device < 16 && g_sm_count[device]) return g_sm_count[device];
+  int n = 148;
+  cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device);
+  if (device < 16) g_sm_count[device] = n;
+  return n;
+}
+
+int *status_word(int device);   // device word, zero until a kernel reports an abandoned wait
+
+template <int BN>
+static int launch_gemm(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mc, const GemmArgs &g, int device,
+                       cudaStream_t st) {
+  static bool attr[16] = {false};
+  auto kern = gemm_bf16_tcgen05_kernel<BN>;
+  if (device < 16 && !attr[device]) {
+    F3D_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN>::kTotal));
+    attr[device] = true;
+  }
+  int tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN);
+  int grid = tiles < sm_count(device) ? tiles : sm_count(device);
+  kern<<<grid, kGemmThreads, GemmSmem<BN>::kTotal, st>>>(ma, mb, mc, g);
+  return check_launch("gemm_bf16_tcgen05");
+}
+
+// C (bf16, nsplit matrices of [M, split_n] with leading dimension split_n, `split_stride` elements apart)
+int linear_bf16(const void *A, int lda, const void *W, int ldw, const void *bias, const void *residual, int ldr, void *C,
+                long long split_stride, int M, int N, int K, int nsplit, int epilogue, int device, cudaStream_t st) {
+  if (M <= 0 || N <= 0 || K <= 0) return set_error(F3D_ERR_ARG, "gemm: M, N, K must be positive (got %d, %d, %d)", M, N, K);
+  if (K % 8 || lda % 8 || ldw % 8) return set_error(F3D_ERR_ARG, "gemm: K and the leading dimensions must be multiples of 8 (TMA 16-byte rule)");
+  if (nsplit < 1 || N % nsplit) return set_error(F3D_ERR_ARG, "gemm: N=%d is not divisible into %d splits", N, nsplit);
+  if (epilogue < 0 || epilogue > 2) return set_error(F3D_ERR_ARG, "gemm: unknown epilogue %d", epilogue);
+  int out_n = epilogue == EPI_SWIGLU ? N / 2 : N;
+  if (epilogue == EPI_SWIGLU && (nsplit != 1 || N % 128)) return set_error(F3D_ERR_ARG, "gemm: swiglu needs nsplit == 1 and N %% 128 == 0");
+  int split_n = out_n / nsplit;
+  if (split_n % 8) return set_error(F3D_ERR_ARG, "gemm: output row length %d is not a multiple of 8", split_n);
+  if (residual && nsplit != 1) return set_error(F3D_ERR_ARG, "gemm: residual needs nsplit == 1");
+  int BN = 256;
+  if (epilogue == EPI_SWIGLU) BN = 128;
+  else if (N <= 32) BN = 32;
+  else if (N <= 64) BN = 64;
+  else if (N <= 128 || (nsplit > 1 && split_n % 256)) BN = 128;
+  const int direct = (nsplit > 1 && split_n % 64) ? 1 : 0;
+  if (nsplit > 1 && !direct && split_n % BN) BN = 64;
+  if (reinterpret_cast<uintptr_t>(C) % 16) return set_error(F3D_ERR_ARG, "gemm: output pointer is not 16-byte aligned");
+  CUtensorMap ma, mb, mc;
+  F3D_TRY(encode_tmap_2d(&ma, 0, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, BM, 128));
+  int b_box_rows = epilogue == EPI_SWIGLU ? BN / 2 : BN;
+  F3D_TRY(encode_tmap_2d(&mb, 0, W, (uint64_t)K, (uint64_t)N, (uint64_t)ldw * 2, BK, b_box_rows, 128));
+  F3D_TRY(encode_tmap_3d(&mc, 0, C, (uint64_t)split_n, (uint64_t)M, (uint64_t)nsplit, (uint64_t)split_n * 2,
+                         (uint64_t)split_stride * 2, 64, 32, 1, 128));
+  GemmArgs g{M, N, K, nsplit, split_n, static_cast<const float *>(bias), static_cast<const __nv_bfloat16 *>(residual), ldr,
+             epilogue, direct, static_cast<__nv_bfloat16 *>(C), split_stride, status_word(device)};
+  if (!g.status) return F3D_ERR_CUDA;
+  switch (BN) {
+    case 32: return launch_gemm<32>(ma, mb, mc, g, device, st);
+    case 64: return launch_gemm<64>(ma, mb, mc, g, device, st);
+    case 128: return launch_gemm<128>(ma, mb, mc, g, device, st);
+    default: return launch_gemm<256>(ma, mb, mc, g, device, st);
+  }
+}
+
+}  // namespace f3d
+
+using namespace f3d;
+
+extern "C" int f3d_linear_bf16(const void *A, const void *W, const void *bias, const void *residual, void *C, int M, int N,
+                               int K, int nsplit, int epilogue, int device, void *stream) {
+  DeviceGuard guard(device);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  F3D_TRY(maybe_sync(st, "linear_bf16"));
+  int out_n = epilogue == EPI_SWIGLU ? N / 2 : N;
+  F3D_TRY(linear_bf16(A, K, W, K, bias, residual, out_n, C, (long long)M * (out_n / (nsplit > 0 ? nsplit : 1)), M, N, K, nsplit,
+                      epilogue, device, st));
+  return maybe_sync(st, "linear_bf16");
+}
+
+// O[M,N] = A[M,K] . B[K,N]: the reference's gemm_sm_bf16 export (src/psh/gemm_dispatcher.cu:26-80).  B is
+// transposed into a scratch [N,K] matrix first so that both operands are K-major for the tensor cores.
+namespace f3d {
+__global__ void transpose_bf16_kernel(const __nv_bfloat16 *in, __nv_bfloat16 *out, int rows, int cols) {
+  __shared__ __nv_bfloat16 t[32][33];
+  int x = blockIdx.x * 32 + threadIdx.x, y = blockIdx.y * 32 + threadIdx.y;
+  for (int j = 0; j < 32; j += 8) if (x < cols && y + j < rows) t[threadIdx.y + j][threadIdx.x] = in[(size_t)(y + j) * cols + x];
+  __syncthreads();
+  x = blockIdx.y * 32 + threadIdx.x; y = blockIdx.x * 32 + threadIdx.y;
+  for (int j = 0; j < 32; j += 8) if (x < rows && y + j < cols) out[(size_t)(y + j) * rows + x] = t[threadIdx.x][threadIdx.y + j];
+}
+}  // namespace f3d
+
+extern "C" int f3d_gemm_sm_bf16(const void *A, const void *B, void *O, int M, int N, int K, int device, void *stream) {
+  DeviceGuard guard(device);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (M <= 0 || N <= 0 || K <= 0) return set_error(F3D_ERR_ARG, "gemm_sm_bf16: empty operand");
+  void *bt = nullptr;
+  F3D_TRY(workspace(device, 1, (size_t)N * K * 2, &bt));
+  dim3 grid((N + 31) / 32, (K + 31) / 32), block(32, 8);
+  transpose_bf16_kernel<<<grid, block, 0, st>>>(static_cast<const __nv_bfloat16 *>(B), static_cast<__nv_bfloat16 *>(bt), K, N);
+  F3D_TRY(check_launch("transpose"));
+  F3D_TRY(linear_bf16(A, K, bt, K, nullptr, nullptr, 0, O, (long long)M * N, M, N, K, 1, EPI_NONE, device, st));
+  // the reference synchronises here (src/psh/gemm_dispatcher.cu:77)
+  F3D_CUDA_TRY(cudaStreamSynchronize(st));
+  return F3D_OK;
+}

@@ -254,3 +254,55 @@ def additive_unpool_bwd(grad_res, grad_down, grad_up_added, unpool_ind, subbuck_
         _ptr(grad_res), _ptr(grad_down), _ptr(grad_up_added), _ptr(unpool_ind), grad_up_added.shape[0],
         unpool_ind.shape[0], grad_up_added.shape[1], code, int(subbuck_size), _dev_index(dev), _stream(dev))
     _cabi.check(st, "additive_unpool_bwd")
+
+
+# ------------------------------------------------------------------------------------------------- GEMMs
+EPI_NONE, EPI_GELU, EPI_SWIGLU = 0, 1, 2
+
+
+def device_status(device=None) -> None:
+    """Raise if a kernel of this library abandoned a bounded wait on `device` since the last check."""
+    idx = torch.cuda.current_device() if device is None else _dev_index(torch.device(device))
+    _cabi.check(_cabi.load().f3d_device_status(idx), "device_status")
+
+
+def gemm_sm_bf16(A, B, O) -> None:
+    """f3d::gemm_sm_bf16 (src/psh/gemm_dispatcher.cu:26-80): O[M,N] = A[M,K] @ B[K,N], bf16."""
+    dev = _check_tensors([A, B, O], ["A", "B", "O"])
+    _check_dtype([A, B, O], ["A", "B", "O"], torch.bfloat16)
+    _require(A.dim() == 2 and B.dim() == 2 and O.dim() == 2, "A, B, O must be matrices")
+    m, k = A.shape
+    _require(B.shape[0] == k, f"A is [{m},{k}] but B is {tuple(B.shape)}")
+    n = B.shape[1]
+    _require(tuple(O.shape) == (m, n), f"O must be [{m},{n}], got {tuple(O.shape)}")
+    _cabi.check(_cabi.load().f3d_gemm_sm_bf16(_ptr(A), _ptr(B), _ptr(O), m, n, k, _dev_index(dev), _stream(dev)),
+                "gemm_sm_bf16")
+
+
+def linear_bf16(x, weight, bias, out, residual=None, nsplit=1, epilogue=EPI_NONE) -> None:
+    """out = x @ weight^T (+ bias) (+ residual) on the tcgen05 GEMM; `out` holds nsplit contiguous
+    [M, N/nsplit] matrices (nsplit=3: Q, K, V).  Not part of the reference's operator module: the reference leaves
+    these projections to nn.Linear / cuBLAS (flash3dxfmr/layers/buck_swin.py:159,163)."""
+    tensors, names = [x, weight, out], ["x", "weight", "out"]
+    if residual is not None:
+        tensors.append(residual); names.append("residual")
+    dev = _check_tensors(tensors, names)
+    _check_dtype(tensors, names, torch.bfloat16)
+    m, k = x.shape
+    n = weight.shape[0]
+    _require(weight.shape[1] == k, f"weight must be [N,{k}], got {tuple(weight.shape)}")
+    out_n = n // 2 if epilogue == EPI_SWIGLU else n
+    _require(out.numel() == m * out_n, f"out must hold {m}x{out_n} elements, got {out.numel()}")
+    bptr = ctypes.c_void_p(0)
+    if bias is not None:
+        _check_tensors([bias], ["bias"])
+        _check_dtype([bias], ["bias"], torch.float32)
+        _require(bias.numel() == n, f"bias must have {n} elements")
+        bptr = _ptr(bias)
+    rptr = ctypes.c_void_p(0)
+    if residual is not None:
+        _require(tuple(residual.shape) == (m, out_n), f"residual must be [{m},{out_n}]")
+        rptr = _ptr(residual)
+    st = _cabi.load().f3d_linear_bf16(_ptr(x), _ptr(weight), bptr, rptr, _ptr(out), m, n, k, int(nsplit), int(epilogue),
+                                      _dev_index(dev), _stream(dev))
+    _cabi.check(st, "linear_bf16")

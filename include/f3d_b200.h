@@ -114,6 +114,28 @@ int f3d_additive_unpool_bwd(
     void *grad_res, void *grad_down, const void *grad_up_added, const void *unpool_ind, uint32_t up_rows,
     uint32_t unpool_rows, uint32_t feat_dim, int feat_dtype, uint32_t subbuck_size, int device, void *stream);
 
+/* reads and clears the device status word: kernels that wait on mbarriers give up after a bounded time and record
+ * the waiting site there; returns F3D_STATUS_DEVICE if a wait was abandoned since the last call (synchronises). */
+int f3d_device_status(int device);
+
+/* ---- per-token projection GEMM ----
+ * replaces the cuBLAS GEMMs behind nn.Linear in BucketSwinAttentionModule (flash3dxfmr/layers/buck_swin.py:159,163,
+ * 185-194): C = A . W^T (+ bias) (+ residual), bf16 operands, fp32 accumulation on tcgen05 tensor cores.
+ *   A        bf16 [M,K]   in   (activations, row-major)
+ *   W        bf16 [N,K]   in   (nn.Linear weight layout)
+ *   bias     fp32 [N]     in   or NULL
+ *   residual bf16 [M,N]   in   or NULL (added after the bias; nsplit must be 1)
+ *   C        bf16         out  nsplit matrices [M, N/nsplit], stored one after another (nsplit = 3 writes Q, K and V
+ *                              as three contiguous [M, H*D] matrices)
+ *   epilogue 0 none, 1 GELU(tanh), 2 SwiGLU: W = [gate; up] (N = 2*F rows), C[M,F] = silu(gate) * up
+ * K, N/nsplit must be multiples of 8; pointers 16-byte aligned. */
+int f3d_linear_bf16(const void *A, const void *W, const void *bias, const void *residual, void *C, int M, int N, int K,
+                    int nsplit, int epilogue, int device, void *stream);
+
+/* replaces f3d::gemm_sm_bf16 (src/psh/gemm_dispatcher.cu:26-80; binding src/f3d_frontend.cu:135): O[M,N] = A[M,K] . B[K,N],
+ * bf16 in/out, fp32 accumulation; synchronises the stream like the reference (:77).  Any M; N, K multiples of 8. */
+int f3d_gemm_sm_bf16(const void *A, const void *B, void *O, int M, int N, int K, int device, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

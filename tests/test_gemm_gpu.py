@@ -1,0 +1,96 @@
+"""GPU parity of the tcgen05 GEMM against an fp32 torch reference.  Tolerance (bf16 outputs of unit scale):
+max abs <= 2e-2 against the fp32 reference, and mean|err| / mean|ref| <= 1e-3 against the fp32 reference rounded to
+the output dtype (rounding an exact result to bf16 alone has a mean relative error of 1.4e-3, so the mean bound is
+only meaningful after the reference has been rounded the same way)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _check(out, ref, max_abs=2e-2, mean_rel=1e-3):
+    err = (out.float() - ref).abs()
+    assert torch.isfinite(out.float()).all()
+    scaled = err / ref.abs().clamp(min=1.0)          # absolute below 1, relative above (bf16 keeps 8 bits)
+    assert scaled.max().item() <= max_abs, f"max abs {scaled.max().item()}"
+    err_r = (out.float() - ref.to(out.dtype).float()).abs()
+    rel = (err_r.mean() / ref.abs().mean()).item()
+    assert rel <= mean_rel, f"mean rel {rel}"
+
+
+def _mk(dev, m, n, k, seed=0):
+    g = torch.Generator(dev).manual_seed(seed)
+    x = torch.randn(m, k, device=dev, generator=g).bfloat16()
+    w = (torch.randn(n, k, device=dev, generator=g) / k ** 0.5).bfloat16()
+    b = torch.randn(n, device=dev, generator=g) * 0.1
+    return x, w, b
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (256, 256, 256), (1000, 96, 32), (4096, 768, 256), (333, 512, 512),
+                                   (2048, 64, 128), (777, 1536, 512), (128, 32, 2048), (5000, 256, 40)])
+def test_linear_plain(cuda_device, m, n, k):
+    from flash3dtransformer_b200.lib import pshattn
+    x, w, b = _mk(cuda_device, m, n, k)
+    out = torch.full((m, n), float("nan"), device=cuda_device, dtype=torch.bfloat16)
+    pshattn.linear_bf16(x, w, b, out)
+    pshattn.device_status()
+    _check(out, x.float() @ w.float().t() + b)
+    out2 = torch.empty_like(out)
+    pshattn.linear_bf16(x, w, None, out2)
+    _check(out2, x.float() @ w.float().t())
+
+
+@pytest.mark.parametrize("m,c", [(1024, 32), (3000, 64), (2048, 128), (1536, 256), (640, 512)])
+def test_qkv_split_and_residual(cuda_device, m, c):
+    from flash3dtransformer_b200.lib import pshattn
+    x, w, b = _mk(cuda_device, m, 3 * c, c, seed=1)
+    qkv = torch.full((3, m, c), float("nan"), device=cuda_device, dtype=torch.bfloat16)
+    pshattn.linear_bf16(x, w, b, qkv, nsplit=3)
+    ref = x.float() @ w.float().t() + b
+    for i in range(3):
+        _check(qkv[i], ref[:, i * c:(i + 1) * c])
+    xw, ww, bw = _mk(cuda_device, m, c, c, seed=2)
+    out = torch.empty(m, c, device=cuda_device, dtype=torch.bfloat16)
+    pshattn.linear_bf16(xw, ww, bw, out, residual=x)
+    pshattn.device_status()
+    _check(out, xw.float() @ ww.float().t() + bw + x.float(), max_abs=4e-2)
+
+
+@pytest.mark.parametrize("m,c,f", [(1024, 128, 256), (700, 64, 256), (2048, 256, 1024)])
+def test_swiglu_and_gelu(cuda_device, m, c, f):
+    from flash3dtransformer_b200.lib import pshattn
+    x, w, b = _mk(cuda_device, m, 2 * f, c, seed=3)
+    out = torch.empty(m, f, device=cuda_device, dtype=torch.bfloat16)
+    pshattn.linear_bf16(x, w, b, out, epilogue=pshattn.EPI_SWIGLU)
+    y = x.float() @ w.float().t() + b
+    _check(out, torch.nn.functional.silu(y[:, :f]) * y[:, f:])
+    out2 = torch.empty(m, 2 * f, device=cuda_device, dtype=torch.bfloat16)
+    pshattn.linear_bf16(x, w, b, out2, epilogue=pshattn.EPI_GELU)
+    pshattn.device_status()
+    _check(out2, torch.nn.functional.gelu(y, approximate="tanh"))
+
+
+def test_gemm_sm_bf16_export(cuda_device):
+    """The reference's own GEMM test: 128x256 @ 256x128, atol = rtol = 1e-2 (tests/test_gemm.py:26-43)."""
+    from flash3dtransformer_b200.lib import pshattn
+    torch.manual_seed(2)
+    a = torch.randn(128, 256, device=cuda_device).bfloat16() / 16
+    b = torch.randn(256, 128, device=cuda_device).bfloat16() / 16
+    o = torch.zeros(128, 128, device=cuda_device, dtype=torch.bfloat16)
+    pshattn.gemm_sm_bf16(a, b, o)
+    assert torch.allclose(o.float(), (a.float() @ b.float()), atol=1e-2, rtol=1e-2)
+    a = torch.randn(300, 72, device=cuda_device).bfloat16() / 8
+    b = torch.randn(72, 40, device=cuda_device).bfloat16() / 8
+    o = torch.zeros(300, 40, device=cuda_device, dtype=torch.bfloat16)
+    pshattn.gemm_sm_bf16(a, b, o)
+    assert torch.allclose(o.float(), (a.float() @ b.float()), atol=1e-2, rtol=1e-2)
+
+
+def test_gemm_errors(cuda_device):
+    from flash3dtransformer_b200.lib import pshattn
+    x = torch.zeros(16, 12, device=cuda_device, dtype=torch.bfloat16)
+    w = torch.zeros(8, 12, device=cuda_device, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="multiples of 8"):
+        pshattn.linear_bf16(x, w, None, torch.zeros(16, 8, device=cuda_device, dtype=torch.bfloat16))
+    with pytest.raises(RuntimeError, match="dtype"):
+        pshattn.linear_bf16(x.float(), w, None, torch.zeros(16, 8, device=cuda_device, dtype=torch.bfloat16))
