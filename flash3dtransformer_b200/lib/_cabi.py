@@ -33,6 +33,7 @@ PROTOTYPES = {
     "f3d_device_status": (_int, [_int]),
     "f3d_linear_bf16": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _int, _int, _int, _int, _int, _vp]),
     "f3d_gemm_sm_bf16": (_int, [_vp, _vp, _vp, _int, _int, _int, _int, _vp]),
+    "f3d_buck_swin_fwd": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _int, _int, _int, _int, _int, _int, _u32, _int, _vp]),
 }
 
 _lib = None

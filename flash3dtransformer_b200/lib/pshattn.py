@@ -306,3 +306,29 @@ def linear_bf16(x, weight, bias, out, residual=None, nsplit=1, epilogue=EPI_NONE
     st = _cabi.load().f3d_linear_bf16(_ptr(x), _ptr(weight), bptr, rptr, _ptr(out), m, n, k, int(nsplit), int(epilogue),
                                       _dev_index(dev), _stream(dev))
     _cabi.check(st, "linear_bf16")
+
+
+# --------------------------------------------------------------------------------------- bucketed attention
+def _check_qkv(tensors, names):
+    dev = _check_tensors(tensors, names)
+    _check_dtype(tensors, names, torch.bfloat16)
+    shape = tuple(tensors[0].shape)
+    _require(len(shape) == 4, f"Expect {names[0]} with four axes [B, L, H, D], but got shape={shape}")
+    for t, n in zip(tensors, names):
+        _require(tuple(t.shape) == shape, f"{n} has shape {tuple(t.shape)}, expected {shape}")
+    return dev, shape
+
+
+def buck_swin_fwd(Q, K, V, O, L, Scope_buckets, bucket_size) -> None:
+    """f3d::buck_swin_fwd (declared src/f3d_frontend.cu:90-92; caller flash3dxfmr/layers/buck_swin.py:57).
+    O[B,L,H,D] and the log-sum-exp L[B,L,H] are written in place."""
+    dev, (b, l, h, d) = _check_qkv([Q, K, V, O], ["Q", "K", "V", "O"])
+    _check_tensors([L, Scope_buckets], ["L", "Scope_buckets"])
+    _check_dtype([L], ["L"], torch.float32)
+    _check_dtype([Scope_buckets], ["Scope_buckets"], torch.uint32)
+    _require(tuple(L.shape) == (b, l, h), f"L must be [{b},{l},{h}], got {tuple(L.shape)}")
+    _require(Scope_buckets.dim() == 2, "Scope_buckets must be [num_scopes, scope_size]")
+    st = _cabi.load().f3d_buck_swin_fwd(_ptr(Q), _ptr(K), _ptr(V), _ptr(O), _ptr(L), _ptr(Scope_buckets), b, l, h, d,
+                                        Scope_buckets.shape[0], Scope_buckets.shape[1], int(bucket_size),
+                                        _dev_index(dev), _stream(dev))
+    _cabi.check(st, "buck_swin_fwd")

@@ -136,6 +136,19 @@ int f3d_linear_bf16(const void *A, const void *W, const void *bias, const void *
  * bf16 in/out, fp32 accumulation; synchronises the stream like the reference (:77).  Any M; N, K multiples of 8. */
 int f3d_gemm_sm_bf16(const void *A, const void *B, void *O, int M, int N, int K, int device, void *stream);
 
+/* ---- bucketed self-attention forward ----
+ * provides f3d::buck_swin_fwd, declared at src/f3d_frontend.cu:90-92 and called by
+ * flash3dxfmr/layers/buck_swin.py:57; the reference snapshot holds neither its kernel nor its binding
+ * (src/f3d_frontend.cu:136 is commented out).  Semantics: tests/test_attn_fwd.py:295-452.
+ *   Q, K, V        bf16 [B,L,H,D]          in
+ *   O              bf16 [B,L,H,D]          out (tokens of buckets no scope lists are left untouched)
+ *   LSE            fp32 [B,L,H]            out (natural-log softmax normaliser)
+ *   scope_buckets  u32  [num_scopes,scope_size]  in: each row lists the buckets that attend to each other
+ * D in {16,32,64,128}; bucket_size a multiple of 128; L a multiple of bucket_size. */
+int f3d_buck_swin_fwd(const void *Q, const void *K, const void *V, void *O, void *LSE, const void *scope_buckets,
+                      int B, int L, int H, int D, int num_scopes, int scope_size, uint32_t bucket_size,
+                      int device, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

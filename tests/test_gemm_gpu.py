@@ -1,7 +1,6 @@
 """GPU parity of the tcgen05 GEMM against an fp32 torch reference.  Tolerance (bf16 outputs of unit scale):
-max abs <= 2e-2 against the fp32 reference, and mean|err| / mean|ref| <= 1e-3 against the fp32 reference rounded to
-the output dtype (rounding an exact result to bf16 alone has a mean relative error of 1.4e-3, so the mean bound is
-only meaningful after the reference has been rounded the same way)."""
+max abs <= 2e-2 against the fp32 reference, and mean|err| / mean|ref| exceeds the floor set by rounding the exact
+result to bf16 (about 1.4e-3 mean relative) by at most 1e-3."""
 import pytest
 import torch
 
@@ -13,9 +12,9 @@ def _check(out, ref, max_abs=2e-2, mean_rel=1e-3):
     assert torch.isfinite(out.float()).all()
     scaled = err / ref.abs().clamp(min=1.0)          # absolute below 1, relative above (bf16 keeps 8 bits)
     assert scaled.max().item() <= max_abs, f"max abs {scaled.max().item()}"
-    err_r = (out.float() - ref.to(out.dtype).float()).abs()
-    rel = (err_r.mean() / ref.abs().mean()).item()
-    assert rel <= mean_rel, f"mean rel {rel}"
+    rel = (err.mean() / ref.abs().mean()).item()
+    floor = ((ref.to(out.dtype).float() - ref).abs().mean() / ref.abs().mean()).item()
+    assert rel <= floor + mean_rel, f"mean rel {rel} (bf16 rounding floor {floor})"
 
 
 def _mk(dev, m, n, k, seed=0):
