@@ -153,33 +153,68 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       for (int c0 = 0; c0 < out_cols; c0 += 64) {
         const int ncol = min(64, out_cols - c0);             // 32 or 64 columns in this chunk
         float v[64];
+        // runtime switches (bias, activation) are tested once per chunk, never per element
+        if (g.epilogue == EPI_SWIGLU) {
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          if (h * 32 < ncol) {
-            uint32_t r[32];
+          for (int h = 0; h < 2; ++h) {
+            uint32_t r[32], u[32];
             tc::tmem_ld_32x32b_x32(t_row + c0 + h * 32, r);
-            if (g.epilogue == EPI_SWIGLU) {
-              uint32_t u[32];
-              tc::tmem_ld_32x32b_x32(t_row + BN / 2 + c0 + h * 32, u);
-              tc::tmem_ld_wait();
+            tc::tmem_ld_32x32b_x32(t_row + BN / 2 + c0 + h * 32, u);
+            tc::tmem_ld_wait();
+            float bg[32], bu[32];
+            if (g.bias) {
+              const float4 *pg = reinterpret_cast<const float4 *>(g.bias + n0 / 2 + c0 + h * 32);
+              const float4 *pu = reinterpret_cast<const float4 *>(g.bias + g.N / 2 + n0 / 2 + c0 + h * 32);
 #pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                const int col = n0 / 2 + c0 + h * 32 + j;
-                float gt = __uint_as_float(r[j]) + (g.bias ? __ldg(g.bias + col) : 0.f);
-                float up = __uint_as_float(u[j]) + (g.bias ? __ldg(g.bias + g.N / 2 + col) : 0.f);
-                v[h * 32 + j] = gt / (1.f + __expf(-gt)) * up;
+              for (int j = 0; j < 8; ++j) {
+                float4 a4 = __ldg(pg + j), b4 = __ldg(pu + j);
+                bg[4 * j] = a4.x; bg[4 * j + 1] = a4.y; bg[4 * j + 2] = a4.z; bg[4 * j + 3] = a4.w;
+                bu[4 * j] = b4.x; bu[4 * j + 1] = b4.y; bu[4 * j + 2] = b4.z; bu[4 * j + 3] = b4.w;
               }
             } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) { bg[j] = 0.f; bu[j] = 0.f; }
+            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              float gt = __uint_as_float(r[j]) + bg[j];
+              float up = __uint_as_float(u[j]) + bu[j];
+              v[h * 32 + j] = __fdividef(gt, 1.f + __expf(-gt)) * up;
+            }
+          }
+        } else {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            if (h * 32 < ncol) {
+              uint32_t r[32];
+              tc::tmem_ld_32x32b_x32(t_row + c0 + h * 32, r);
               tc::tmem_ld_wait();
 #pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                const int col = n0 + c0 + h * 32 + j;
-                float x = __uint_as_float(r[j]);
-                if (g.bias && col < g.N) x += __ldg(g.bias + col);
-                if (g.epilogue == EPI_GELU) x = gelu_tanh(x);
-                v[h * 32 + j] = x;
+              for (int j = 0; j < 32; ++j) v[h * 32 + j] = __uint_as_float(r[j]);
+            }
+          }
+          if (g.bias) {
+            const int cb = n0 + c0;
+            const float4 *bp = reinterpret_cast<const float4 *>(g.bias + cb);
+            if (ncol == 64 && cb + 64 <= g.N) {                  // common case: no guards inside the loop
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                float4 b4 = __ldg(bp + j);
+                v[4 * j] += b4.x; v[4 * j + 1] += b4.y; v[4 * j + 2] += b4.z; v[4 * j + 3] += b4.w;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if (4 * j < ncol && cb + 4 * j < g.N) {          // N is a multiple of 8: groups of 4 are all in or all out
+                  float4 b4 = __ldg(bp + j);
+                  v[4 * j] += b4.x; v[4 * j + 1] += b4.y; v[4 * j + 2] += b4.z; v[4 * j + 3] += b4.w;
+                }
               }
             }
+          }
+          if (g.epilogue == EPI_GELU) {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) v[j] = gelu_tanh(v[j]);
           }
         }
         if (g.residual && row < g.M) {
