@@ -1,0 +1,83 @@
+"""Autograd glue between torch modules and the native operators.
+
+Forward passes run the hand-written kernels (tcgen05 GEMM with fused bias / residual / SwiGLU epilogues, bucketed
+attention, pooling, unpooling).  Backward passes of the projections use torch matmuls (plain library GEMMs); the
+backward passes of attention, pooling and unpooling run the native kernels.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+from torch.autograd import Function
+
+from ..lib import pshattn
+
+_BF16_CACHE = {}
+
+
+def bf16_weight(p: torch.Tensor) -> torch.Tensor:
+    """bf16 copy of a parameter, refreshed when the parameter is modified in place (optimizer step)."""
+    if p.dtype == torch.bfloat16:
+        return p.detach()
+    key = id(p)
+    hit = _BF16_CACHE.get(key)
+    if hit is not None and hit[0] == p._version and hit[1].device == p.device and hit[2] is p:
+        return hit[1]
+    w = p.detach().to(torch.bfloat16).contiguous()
+    _BF16_CACHE[key] = (p._version, w, p)
+    return w
+
+
+def _fp32_bias(b: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    if b is None:
+        return None
+    return b.detach() if b.dtype == torch.float32 else b.detach().float()
+
+
+class LinearFn(Function):
+    """y = x W^T + b (+ residual); forward on the tcgen05 GEMM."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, residual, nsplit, epilogue):
+        xb = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
+        xb = xb.contiguous()
+        m, n = xb.shape[0], weight.shape[0]
+        out_n = n // 2 if epilogue == pshattn.EPI_SWIGLU else n
+        shape = (nsplit, m, out_n // nsplit) if nsplit > 1 else (m, out_n)
+        out = torch.empty(shape, dtype=torch.bfloat16, device=x.device)
+        res = None if residual is None else residual.contiguous()
+        pshattn.linear_bf16(xb, bf16_weight(weight), _fp32_bias(bias), out, residual=res, nsplit=nsplit, epilogue=epilogue)
+        ctx.save_for_backward(xb, weight, bias)
+        ctx.cfg = (nsplit, epilogue, residual is not None)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        xb, weight, bias = ctx.saved_tensors
+        nsplit, epilogue, has_res = ctx.cfg
+        wb = bf16_weight(weight)
+        if nsplit > 1:
+            g = g.permute(1, 0, 2).reshape(g.shape[1], -1)
+        g = g.contiguous()
+        g_res = g if has_res else None
+        if epilogue == pshattn.EPI_SWIGLU:
+            y = torch.addmm(bias.to(wb.dtype), xb, wb.t()) if bias is not None else xb @ wb.t()
+            f = y.shape[1] // 2
+            gate, up = y[:, :f].float(), y[:, f:].float()
+            sig = torch.sigmoid(gate)
+            gf = g.float()
+            g = torch.cat([gf * up * sig * (1 + gate * (1 - sig)), gf * gate * sig], dim=1).to(wb.dtype)
+        elif epilogue == pshattn.EPI_GELU:
+            y = (torch.addmm(bias.to(wb.dtype), xb, wb.t()) if bias is not None else xb @ wb.t()).float().requires_grad_(True)
+            with torch.enable_grad():
+                z = torch.nn.functional.gelu(y, approximate="tanh")
+            g = torch.autograd.grad(z, y, g.float())[0].to(wb.dtype)
+        gx = g @ wb
+        gw = (g.t() @ xb).to(weight.dtype)
+        gb = g.float().sum(0).to(bias.dtype) if bias is not None else None
+        return gx, gw, gb, g_res, None, None
+
+
+def linear(x, weight, bias=None, residual=None, nsplit=1, epilogue=pshattn.EPI_NONE):
+    return LinearFn.apply(x, weight, bias, residual, nsplit, epilogue)

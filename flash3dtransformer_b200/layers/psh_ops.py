@@ -1,0 +1,39 @@
+"""PSH scatter layers (mirror of the reference's flash3dxfmr/layers/psh_ops.py:16-67)."""
+from __future__ import annotations
+
+from typing import Tuple
+
+import torch
+from torch import nn
+
+from ..psh import arithmatic as f3darith
+from ..psh import psh_main as pm
+
+
+class PSHScatterLayer(nn.Module):
+    def __init__(self, bucket_size: int = 512) -> None:
+        super().__init__()
+        self.bucket_size = bucket_size
+
+    def forward(self, coords, seps, hash_op: int) -> Tuple[torch.Tensor, pm.BucketScatterBuffers]:
+        pad_to = f3darith.cdiv(coords.shape[0], self.bucket_size) * self.bucket_size
+        return pm.batch_bucket_scatter(coords, seps, self.bucket_size, pad_to, hash_op)
+
+
+class PSH3DCoordEmbedding(nn.Module):
+    """Bucket-sorts the coordinates and embeds them with a 3 -> C linear layer (the reference uses te.Linear,
+    psh_ops.py:61).  `bbox` optionally carries the bounding box of the global batch for scene-sharded runs."""
+
+    def __init__(self, emb_dim: int, bucket_size, alignment, feat_dtype=torch.bfloat16):
+        super().__init__()
+        self.bucket_size = bucket_size
+        self.alignment = alignment
+        self.feat_dtype = feat_dtype
+        self.lin = nn.Linear(3, emb_dim)
+
+    def forward(self, coords, seps, hash_op, bbox=None):
+        pad_to = f3darith.cdiv(coords.shape[0], self.alignment) * self.alignment
+        scattered, _ = pm.batch_bucket_scatter(coords, seps, self.bucket_size, pad_to, hash_op, bbox=bbox)
+        # K = 3 is below the tensor-core GEMM's 8-element granularity: three FMAs per output, left to torch
+        return torch.nn.functional.linear(scattered.to(self.feat_dtype), self.lin.weight.to(self.feat_dtype),
+                                          self.lin.bias.to(self.feat_dtype))
