@@ -35,8 +35,7 @@ class LayerNormMLP(nn.Module):
         nn.init.normal_(self.fc2_weight, std=0.023)
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor = None) -> torch.Tensor:
-        h = torch.nn.functional.layer_norm(x, (x.shape[-1],), self.layer_norm_weight.to(x.dtype),
-                                           self.layer_norm_bias.to(x.dtype), self.eps)
+        h = F3.layer_norm(x, self.layer_norm_weight, self.layer_norm_bias, self.eps)
         epi = pshattn.EPI_SWIGLU if self.activation == "swiglu" else pshattn.EPI_GELU
         h = F3.linear(h, self.fc1_weight, self.fc1_bias, epilogue=epi)
         return F3.linear(h, self.fc2_weight, self.fc2_bias, residual=residual)

@@ -81,3 +81,52 @@ class LinearFn(Function):
 
 def linear(x, weight, bias=None, residual=None, nsplit=1, epilogue=pshattn.EPI_NONE):
     return LinearFn.apply(x, weight, bias, residual, nsplit, epilogue)
+
+
+class LayerNormFn(Function):
+    """LayerNorm (+ optional GELU) on the native kernel; backward by autograd of the fp32 torch formula."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, eps, gelu):
+        xb = (x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)).contiguous()
+        out = torch.empty_like(xb)
+        pshattn.layernorm_bf16(xb, weight.detach().float().contiguous(), bias.detach().float().contiguous(), out, eps, gelu)
+        ctx.save_for_backward(xb, weight, bias)
+        ctx.cfg = (eps, gelu)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        xb, weight, bias = ctx.saved_tensors
+        eps, gelu = ctx.cfg
+        with torch.enable_grad():
+            xf = xb.float().requires_grad_(True)
+            wf = weight.detach().float().requires_grad_(True)
+            bf = bias.detach().float().requires_grad_(True)
+            y = torch.nn.functional.layer_norm(xf, (xf.shape[-1],), wf, bf, eps)
+            if gelu:
+                y = torch.nn.functional.gelu(y)
+            gx, gw, gb = torch.autograd.grad(y, (xf, wf, bf), g.float())
+        return gx.to(xb.dtype), gw.to(weight.dtype), gb.to(bias.dtype), None, None
+
+
+def layer_norm(x, weight, bias, eps=1e-5, gelu=False):
+    return LayerNormFn.apply(x, weight, bias, eps, gelu)
+
+
+def apply_norm(norm: torch.nn.Module, x: torch.Tensor, act: torch.nn.Module = None):
+    """Run a user-supplied normalisation (and activation) module.  nn.LayerNorm over the channel dimension goes to
+    the native kernel, with an nn.GELU activation fused; anything else (BatchNorm, custom modules) runs as given,
+    in the dtype of its parameters."""
+    if (isinstance(norm, torch.nn.LayerNorm) and x.is_cuda and x.dim() == 2 and norm.elementwise_affine
+            and norm.bias is not None and tuple(norm.normalized_shape) == (x.shape[-1],) and x.shape[-1] % 8 == 0):
+        fuse = isinstance(act, torch.nn.GELU) and getattr(act, "approximate", "none") == "none"
+        y = layer_norm(x, norm.weight, norm.bias, norm.eps, gelu=fuse)
+        return y if (act is None or fuse) else act(y)
+    if norm is not None:
+        p = next(norm.parameters(), None)
+        y = norm(x.to(p.dtype) if p is not None and p.dtype != x.dtype else x)
+    else:
+        y = x
+    y = act(y) if act is not None else y
+    return y.to(torch.bfloat16) if y.dtype != torch.bfloat16 else y

@@ -41,10 +41,8 @@ class PoolingWrapper(nn.Module):
             nvtx.range_push(self.NVTX_SCOPE)
         projected = self.proj(input_feat)
         reduced_feat, subbuffers = self.pooling(coords, projected, seps)
-        if self.norm is not None:
-            reduced_feat = self.norm(reduced_feat)
-        if self.act is not None:
-            reduced_feat = self.act(reduced_feat)
+        if self.norm is not None or self.act is not None:
+            reduced_feat = F3.apply_norm(self.norm, reduced_feat, self.act)
         if f3ddev.get_nvtx():
             nvtx.range_pop()
         return reduced_feat, projected, subbuffers
@@ -66,10 +64,18 @@ class AdditiveUnpoolingWrapper(nn.Module):
             self.proj_skip.add_module("act", act_layer())
         self.unpool = unpool.AdditiveUnpoolLayer(subbuck_size)
 
+    @staticmethod
+    def _branch(seq: nn.Sequential, x):
+        """Linear -> (norm) -> (act), with LayerNorm + GELU on the fused native kernel."""
+        y = seq[0](x)
+        norm = getattr(seq, "norm", None)
+        act = getattr(seq, "act", None)
+        return F3.apply_norm(norm, y, act) if (norm is not None or act is not None) else y
+
     def forward(self, residual, down, buffers: f3dsubbuck.SubbuckBuffers) -> torch.Tensor:
         if f3ddev.get_nvtx():
             nvtx.range_push(self.NVTX_SCOPE)
-        output = self.unpool(self.proj_skip(residual), self.proj(down), buffers)
+        output = self.unpool(self._branch(self.proj_skip, residual), self._branch(self.proj, down), buffers)
         if f3ddev.get_nvtx():
             nvtx.range_pop()
         return output

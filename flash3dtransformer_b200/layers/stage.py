@@ -14,6 +14,7 @@ import torch.cuda.nvtx as nvtx
 from torch import nn
 
 from . import buck_swin, elem_wise
+from . import functional as F3
 from ..psh import bucket_scope
 from ..psh import dev_context as f3ddev
 
@@ -49,7 +50,7 @@ class XFMR(nn.Module):
         if f3ddev.get_nvtx():
             nvtx.range_push(self.NVTX_SCOPE)
         feat = reduced_feat if reduced_feat.dtype == torch.bfloat16 else reduced_feat.to(torch.bfloat16)
-        x = self.norm(feat)
+        x = F3.apply_norm(self.norm, feat)
         mid = self.bwa(x.view(1, n, c), scope_bucks, residual=feat).view(n, c)
         out = self.mlp(mid, residual=mid)
         if f3ddev.get_nvtx():

@@ -332,3 +332,16 @@ def buck_swin_fwd(Q, K, V, O, L, Scope_buckets, bucket_size) -> None:
                                         Scope_buckets.shape[0], Scope_buckets.shape[1], int(bucket_size),
                                         _dev_index(dev), _stream(dev))
     _cabi.check(st, "buck_swin_fwd")
+
+
+def layernorm_bf16(x, weight, bias, out, eps=1e-5, gelu=False) -> None:
+    """out = LayerNorm(x) (optionally followed by GELU) over the last dimension; x/out bf16 [rows, C], weight/bias
+    fp32 [C].  Not part of the reference's operator module (it uses te.LayerNorm / nn.LayerNorm)."""
+    dev = _check_tensors([x, weight, bias, out], ["x", "weight", "bias", "out"])
+    _check_dtype([x, out], ["x", "out"], torch.bfloat16)
+    _check_dtype([weight, bias], ["weight", "bias"], torch.float32)
+    _require(x.dim() == 2 and x.shape == out.shape, "x and out must be [rows, C] of equal shape")
+    _require(weight.numel() == x.shape[1] and bias.numel() == x.shape[1], "weight / bias must have C elements")
+    st = _cabi.load().f3d_layernorm_bf16(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), x.shape[0], x.shape[1], float(eps),
+                                         1 if gelu else 0, _dev_index(dev), _stream(dev))
+    _cabi.check(st, "layernorm_bf16")

@@ -149,6 +149,12 @@ int f3d_buck_swin_fwd(const void *Q, const void *K, const void *V, void *O, void
                       int B, int L, int H, int D, int num_scopes, int scope_size, uint32_t bucket_size,
                       int device, void *stream);
 
+/* LayerNorm over the last dimension of bf16 [rows, C] with fp32 weight/bias [C] and an optional exact GELU.
+ * Stands in for the te.LayerNorm / nn.LayerNorm steps of XFMR and the pooling wrappers
+ * (flash3dxfmr/layers/stage.py:67,95; flash3dxfmr/layers/hourglass.py:76-79).  C a multiple of 8, <= 2048. */
+int f3d_layernorm_bf16(const void *x, const void *weight, const void *bias, void *y, uint32_t rows, uint32_t C, float eps,
+                       int gelu, int device, void *stream);
+
 #ifdef __cplusplus
 }
 #endif
