@@ -26,7 +26,7 @@ NUM_VOX = 0xFFFF
 
 def bucket_plan(seps: torch.Tensor, bucket_size: int):
     """(mean scene size, largest scene, num_buck, divisor) as psh_main.py:97-104 computes them."""
-    sizes = f3dbatch.sep2sizes(seps.to(torch.int64)).cpu()
+    sizes = f3dbatch.sep2sizes(f3dbatch.host_seps(seps))
     mean_n = float(sizes.to(torch.float32).mean())
     max_n = int(sizes.max())
     num_buck = max(1, f3darith.round_next_two_power(int(mean_n / bucket_size)))

@@ -13,6 +13,7 @@ import dataclasses as dcls
 
 import torch
 
+from . import batching as f3dbatch
 from .arithmatic import cdiv
 
 BLOCK_POINTS = 1024
@@ -21,12 +22,13 @@ BLOCK_POINTS = 1024
 def calc_red_sep_sizes(seps: torch.Tensor, subbuck_size: int):
     """(total reduced rows, rows per scene, inclusive row separators) for a flat batch."""
     assert seps.dim() == 1, f"Seps dimension is expected to be 1, got {seps.dim()} instead"
-    wide = seps.to(torch.int64)
+    wide = f3dbatch.host_seps(seps)                      # scene sizes are planned on the host
     sizes = torch.diff(wide, prepend=wide.new_zeros(1))
     per_block = -(-BLOCK_POINTS // subbuck_size)
     red_sizes = (sizes // BLOCK_POINTS) * per_block + ((sizes % BLOCK_POINTS) + subbuck_size - 1) // subbuck_size
-    red_sep = torch.cumsum(red_sizes, dim=0)
-    return int(red_sizes.sum()), red_sizes.to(seps.dtype), red_sep.to(seps.dtype)
+    red_sep_cpu = torch.cumsum(red_sizes, dim=0)
+    red_sep = f3dbatch.attach_host_seps(red_sep_cpu.to(seps.dtype).to(seps.device), red_sep_cpu)
+    return int(red_sizes.sum()), red_sizes.to(seps.dtype).to(seps.device), red_sep
 
 
 @dcls.dataclass(slots=True)
@@ -40,7 +42,7 @@ class SubbuckBuffers:
     reduced_coord: torch.Tensor
     reduced_feat: torch.Tensor
     unpool_ind: torch.Tensor
-    pooled_rows: int = 0          # leading rows of the input that unpool_ind refers to (= coords.shape[0])
+    pooled_rows: int = 0          # leading rows of the input that belong to a scene (= last separator)
 
     @staticmethod
     def create_subbuck_buff(coords: torch.Tensor, input_feat: torch.Tensor, seps: torch.Tensor,
@@ -63,7 +65,7 @@ class SubbuckBuffers:
             reduced_feat=torch.empty(aligned, feat_dim, dtype=input_feat.dtype, device=dev),
             # out-of-range default marks an unfilled sub-bucket slot
             unpool_ind=torch.full((red_len, subbuck_size), total_n + 3, dtype=torch.uint32, device=dev),
-            pooled_rows=total_n,
+            pooled_rows=min(total_n, int(f3dbatch.host_seps(seps)[-1])) if seps.numel() else 0,
         )
 
     def remove_unused_buffers(self):

@@ -56,3 +56,26 @@ def test_xfmr_block_matches_torch(cuda_device):
         ref = (torch.nn.functional.silu(y[:, :f]) * y[:, f:]) @ m.fc2_weight.t() + m.fc2_bias + mid
     err = (out - ref).abs()
     assert err.max().item() <= 6e-2 and (err.mean() / ref.abs().mean()).item() <= 8e-3
+
+
+def test_backbone_forward_matches_cpu_oracle(cuda_device):
+    """Three-level backbone on two small scans against the composed CPU oracle (fp32 with bf16 storage rounding).
+    Every layer re-rounds to bf16, so the tolerance is the per-layer bar accumulated over ~10 layers."""
+    from flash3dtransformer_b200 import configs
+    from oracle import backbone_oracle
+    torch.manual_seed(0)
+    model = configs.flash3d_backbone(channels=(32, 64, 128), depths=(1, 1, 1), bucket_size=256, scope_size=2)
+    c32, seps = synthetic.batch(synthetic.lidar_scan, [5000, 3500], seed=2)
+    c16 = c32.astype(np.float16)
+    ref = backbone_oracle.flash3d_forward(model, c16, seps)
+    model = model.to(cuda_device)
+    with torch.no_grad():
+        out = model(torch.from_numpy(c16).to(cuda_device), None, torch.from_numpy(seps.astype(np.uint32)).to(cuda_device))
+    out = out.float().cpu()
+    assert out.shape == ref.shape
+    err = (out - ref).abs()
+    scaled = err / ref.abs().clamp(min=1.0)       # coordinates in metres make some features large: 1 bf16 ulp at 64 is 0.25
+    assert scaled.max().item() <= 0.1, scaled.max().item()
+    assert (err.mean() / ref.abs().mean()).item() <= 1e-2, (err.mean() / ref.abs().mean()).item()
+    # rows behind the last scene (tail padding) carry no garbage
+    assert torch.isfinite(out).all()
