@@ -1,0 +1,397 @@
+#!/usr/bin/env python
+"""Benchmark of the Flash3D hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W            this build (one process per GPU; torchrun for N > 1)
+    python bench.py --impl reference --gpus N --steps K ...   CPU restatement of the reference's path (rank 0 only)
+
+A step is one forward pass of the 5-stage Flash3D hourglass backbone (channels 32/64/128/256/512, depths
+2/2/2/6/2, bucket 512, scope 8, bf16) over one batch of 16 synthetic LiDAR-like scans of 120,000 points per GPU
+(PSH bucketing + scatter, 28 transformer blocks of LayerNorm / QKV GEMM / bucketed attention / projection /
+SwiGLU MLP, 4 sub-bucket poolings and the matching unpoolings).  With N GPUs every rank processes its own batch of
+scenes (weak scaling, scenes sharded along batch_sep); the only collective in the step is the 6-value bounding-box
+all-reduce that keeps bucket ids independent of the sharding.
+
+Rank 0 prints one JSON line: whole-job points/s with inputs resident in HBM (`value`), the same metric through the
+public API from pinned host buffers (`e2e`), the roofline position of the dominant kernel family (`roofline`), and
+the CPU restatement timed on the host cores (`cpu_baseline`).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "points/sec (Flash3D backbone fwd)"
+SCENES_PER_GPU = 16
+POINTS_PER_SCENE = 120_000
+CHANNELS = (32, 64, 128, 256, 512)
+DEPTHS = (2, 2, 2, 6, 2)
+BUCKET, SCOPE, HASH_OP = 512, 8, 2
+
+
+# ----------------------------------------------------------------------------------------------------- helpers
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "tflops": p.get("bf16_tflops_sustained", p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()            # the exact process started above
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        clocks, max_clk, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for row in self.rows:
+            parts = [p.strip() for p in row.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                clocks.append(float(parts[0]))
+                max_clk = float(parts[1])
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(clocks)) if clocks else None, "sm_max_mhz": max_clk,
+                "samples": len(clocks), "reasons": sorted(reasons)}
+
+
+def make_batch(rank: int, scenes: int, points: int):
+    from flash3dtransformer_b200 import synthetic
+    coords32, seps = synthetic.batch(synthetic.lidar_scan, [points] * scenes, seed=1000 * rank)
+    return coords32.astype(np.float16), seps.astype(np.uint32)
+
+
+def build_model(device):
+    from flash3dtransformer_b200 import configs
+    torch.manual_seed(0)
+    model = configs.flash3d_backbone(CHANNELS, DEPTHS, BUCKET, SCOPE, HASH_OP)
+    return model.to(device).eval()
+
+
+# ------------------------------------------------------------------------------------- kernel-family timing
+class FamilyTimer:
+    """Wraps the operator module's entry points with CUDA events on the launching stream and records the
+    algorithmic work of every call, so that per-family time shares and the dominant family's roofline position
+    come from the timed region itself."""
+
+    def __init__(self, pshattn):
+        self.p = pshattn
+        self.records = []
+        self.enabled = False
+        self._orig = {}
+
+    def _wrap(self, name, work_fn, family):
+        orig = getattr(self.p, name)
+        self._orig[name] = orig
+
+        def wrapped(*a, **kw):
+            if not self.enabled:
+                return orig(*a, **kw)
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            r = orig(*a, **kw)
+            e.record()
+            flops, nbytes = work_fn(*a, **kw)
+            self.records.append((family, s, e, flops, nbytes))
+            return r
+
+        setattr(self.p, name, wrapped)
+
+    def install(self):
+        def attn(Q, K, V, O, L, scopes, bucket):
+            b, l, h, d = Q.shape
+            w = scopes.shape[1] * bucket
+            tokens = scopes.shape[0] * w * b
+            return 4.0 * tokens * w * h * d, 4.0 * b * l * h * d * 2 + b * l * h * 4
+
+        def gemm(x, w, bias, out, residual=None, nsplit=1, epilogue=0):
+            m, k = x.shape
+            n = w.shape[0]
+            by = 2.0 * (m * k + out.numel() + (0 if residual is None else residual.numel()))
+            return 2.0 * m * n * k, by
+
+        def ln(x, w, b, out, eps=1e-5, gelu=False):
+            return 0.0, 4.0 * x.numel()
+
+        def pool(coord, feat, seps, maxn, S, nv, bmin, bmax, sid, soff, rsep, rcoord, rfeat, ind, ht, op):
+            n = coord.shape[0]
+            e = feat.element_size()
+            c = feat.shape[1]
+            return 0.0, n * (19.0 + c * e + c * e / S + 4)
+
+        def unpool(res, down, up, ind, S, covered_rows=None):
+            e = res.element_size()
+            c = res.shape[1]
+            return 0.0, res.shape[0] * (2.0 * c * e + c * e / S + 4)
+
+        def psh(coord, *rest):
+            return 0.0, 18.0 * coord.shape[0]
+
+        self._wrap("buck_swin_fwd", attn, "attention_fwd")
+        self._wrap("linear_bf16", gemm, "gemm")
+        self._wrap("layernorm_bf16", ln, "layernorm")
+        self._wrap("batch_subbuck_reduce", pool, "subbuck_pool")
+        self._wrap("additive_unpool_fwd", unpool, "unpool")
+        self._wrap("batch_psh_scatter_pad_hash", psh, "psh_scatter")
+
+    def summary(self):
+        fam = {}
+        for family, s, e, flops, nbytes in self.records:
+            ms = s.elapsed_time(e)
+            f = fam.setdefault(family, {"ms": 0.0, "flops": 0.0, "bytes": 0.0, "launches": 0})
+            f["ms"] += ms
+            f["flops"] += flops
+            f["bytes"] += nbytes
+            f["launches"] += 1
+        return fam
+
+
+# ------------------------------------------------------------------------------------------- CPU restatement
+def cpu_backbone_points_per_s(points: int, steps: int, warmup: int = 0):
+    """Times the CPU restatement of the path (oracle/backbone_oracle.py) on one synthetic scan."""
+    from flash3dtransformer_b200 import configs, synthetic
+    from oracle import backbone_oracle
+    torch.manual_seed(0)
+    model = configs.flash3d_backbone(CHANNELS, DEPTHS, BUCKET, SCOPE, HASH_OP).eval()
+    coords32, seps = synthetic.batch(synthetic.lidar_scan, [points], seed=0)
+    c16 = coords32.astype(np.float16)
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    for _ in range(warmup):
+        backbone_oracle.flash3d_forward(model, c16, seps)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        backbone_oracle.flash3d_forward(model, c16, seps)
+    dt = (time.perf_counter() - t0) / max(steps, 1)
+    return points / dt, dt, torch.get_num_threads()
+
+
+def run_reference(args, rank: int):
+    if rank != 0:
+        return
+    pts = args.ref_points
+    value, dt, cores = cpu_backbone_points_per_s(pts, args.steps, min(args.warmup, 1))
+    sample = f"1 scan of {pts} points per step, full backbone forward, fp32 torch/numpy CPU restatement"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "points/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "flash3d_backbone_fwd_5stage_16x120k (CPU arm: bounded sample)", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "points/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "points/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference has no CPU implementation of this path and cannot be built here (empty ThunderKittens "
+                "submodule, attention kernels absent); this arm times the CPU restatement used as the parity oracle",
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------------------- GPU arm
+def run_ours(args, rank: int, world: int, local_rank: int):
+    import torch.distributed as dist
+    from flash3dtransformer_b200.lib import _cabi, pshattn
+    from flash3dtransformer_b200.psh import batching
+
+    _cabi.load()                                  # no fallback: fails loudly when the extension is missing
+    dev = torch.device(f"cuda:{local_rank}")
+    torch.cuda.set_device(dev)
+    model = build_model(dev)
+    c16, seps = make_batch(rank, args.scenes, args.points)
+    n_points = int(c16.shape[0])
+    host_coords = torch.from_numpy(c16).pin_memory()
+    host_seps = torch.from_numpy(seps).pin_memory()
+    coords = host_coords.to(dev)
+    seps_dev = host_seps.to(dev)
+    batching.host_seps(seps_dev)
+
+    def global_bbox(c):
+        lo, hi = torch.aminmax(c, dim=0)
+        if world > 1:
+            lo32, hi32 = lo.float(), hi.float()
+            dist.all_reduce(lo32, op=dist.ReduceOp.MIN)
+            dist.all_reduce(hi32, op=dist.ReduceOp.MAX)
+            lo, hi = lo32.half(), hi32.half()
+        return lo, hi
+
+    def step(c, s):
+        with torch.no_grad():
+            return model(c, None, s, bbox=global_bbox(c))
+
+    timer = FamilyTimer(pshattn)
+    timer.install()
+    for _ in range(args.warmup):
+        out = step(coords, seps_dev)
+    torch.cuda.synchronize()
+    pshattn.device_status()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    # ---- device-resident timing
+    sampler = ClockSampler(local_rank)
+    barrier()
+    torch.cuda.synchronize()
+    sampler.start()
+    launches0 = pshattn.launch_count()
+    timer.enabled = True
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        out = step(coords, seps_dev)
+    e1.record()
+    torch.cuda.synchronize()
+    barrier()
+    timer.enabled = False
+    launches = pshattn.launch_count() - launches0
+    clocks = sampler.stop()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_per_step = ms.item() / args.steps
+    pshattn.device_status()
+
+    # ---- end to end: pinned host buffers in, scalar result out, every step
+    barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    checksum = 0.0
+    for _ in range(args.steps):
+        c = host_coords.to(dev, non_blocking=True)
+        s = host_seps.to(dev, non_blocking=True)
+        o = step(c, s)
+        checksum = float(o.float().mean().item())        # device -> host read of the step's result
+    torch.cuda.synchronize()
+    e2e_s = torch.tensor([time.perf_counter() - t0], device=dev)
+    if world > 1:
+        dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
+    e2e_per_step = e2e_s.item() / args.steps
+
+    if rank != 0:
+        return
+    fam = timer.summary()
+    total_fam_ms = sum(f["ms"] for f in fam.values()) or 1.0
+    peaks = measured_peaks()
+    dominant = max(fam, key=lambda k: fam[k]["ms"]) if fam else None
+    roofline = None
+    if dominant:
+        f = fam[dominant]
+        sec = f["ms"] * 1e-3
+        if dominant == "attention_fwd":
+            achieved, peak, unit, bound = f["flops"] / sec / 1e12, peaks["tflops"], "TFLOP/s", "tensor"
+        else:
+            achieved, peak, unit, bound = f["bytes"] / sec / 1e9, peaks["hbm_gbs"], "GB/s", "hbm"
+        roofline = {"kernel": dominant, "bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
+                    "frac": achieved / peak, "traffic": None, "peak_source": peaks["source"],
+                    "launches": f["launches"], "avg_launch_ms": f["ms"] / f["launches"],
+                    "share_of_kernel_time": f["ms"] / total_fam_ms}
+    kernels = {k: {"ms_per_step": v["ms"] / args.steps, "share": v["ms"] / total_fam_ms,
+                   "launches_per_step": v["launches"] / args.steps,
+                   "tflops": v["flops"] / (v["ms"] * 1e-3) / 1e12 if v["ms"] else 0.0,
+                   "gbs": v["bytes"] / (v["ms"] * 1e-3) / 1e9 if v["ms"] else 0.0} for k, v in fam.items()}
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        v, dt, cores = cpu_backbone_points_per_s(args.ref_points, 1, 0)
+        cpu = {"value": v, "unit": "points/s", "cores": cores, "kind": "port",
+               "sample": f"1 scan of {args.ref_points} points, full backbone forward, fp32 torch/numpy CPU restatement, "
+                         f"{dt:.1f} s"}
+    total_points = n_points * world
+    line = {
+        "metric": METRIC, "value": total_points / (ms_per_step * 1e-3), "unit": "points/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"flash3d_backbone_fwd_5stage_{args.scenes}x{args.points // 1000}k_per_gpu",
+                   "scenes_per_gpu": args.scenes, "points_per_scene": args.points, "channels": list(CHANNELS),
+                   "depths": list(DEPTHS), "bucket_size": BUCKET, "scope_size": SCOPE, "hash_op": HASH_OP,
+                   "parallelism": f"scene-sharded x{world}",
+                   "l2": "activations per layer (>= 124 MB) exceed the 126 MB L2 across a step; no explicit flush"},
+        "e2e": {"value": total_points / e2e_per_step, "unit": "points/s", "h2d_bytes_per_step": int(c16.nbytes + seps.nbytes),
+                "d2h_bytes_per_step": 4, "ms_per_step": e2e_per_step * 1e3, "checksum": checksum},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "roofline": roofline,
+        "kernels": kernels,
+        "cpu_baseline": cpu,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--scenes", type=int, default=SCENES_PER_GPU)
+    ap.add_argument("--points", type=int, default=POINTS_PER_SCENE)
+    ap.add_argument("--ref-points", type=int, default=20000, help="points of the CPU arm's bounded sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
+    try:
+        run_ours(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

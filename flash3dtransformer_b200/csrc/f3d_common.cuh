@@ -30,10 +30,12 @@ int workspace(int device, int slot, size_t bytes, void **out);
 void workspace_release_all();
 
 bool sync_flag();
+void count_launches(int n);            // kernels launched by this library since load (f3d_launch_count)
 
-static inline int check_launch(const char *what) {
+static inline int check_launch(const char *what, int kernels = 1) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(F3D_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+  count_launches(kernels);
   return F3D_OK;
 }
 

@@ -13,6 +13,9 @@ namespace f3d {
 static thread_local char g_err[512] = "";
 static std::atomic<int> g_sync{0};
 static std::atomic<uint64_t> g_seed{3407ull};
+static std::atomic<unsigned long long> g_launches{0ull};
+
+void count_launches(int n) { g_launches.fetch_add((unsigned long long)n); }
 
 char *err_buf() { return g_err; }
 
@@ -118,6 +121,8 @@ int f3d_device_status(int device) {
   }
   return F3D_OK;
 }
+
+unsigned long long f3d_launch_count(void) { return f3d::g_launches.load(); }
 
 int f3d_release_workspaces(void) { f3d::workspace_release_all(); return F3D_OK; }
 

@@ -684,7 +684,7 @@ static int psh_run(PshArgs a, const PshPlan &p, uint32_t *scratch, uint32_t max_
     a.tiles_max = p.tiles_max;
     psh_scatter_kernel<<<grid2, kPshThreads, p.smem_rank, st>>>(a);
   }
-  return check_launch("psh kernels");
+  return check_launch("psh kernels", (max_n > 0 ? 6 : 0) + (gx > 0 ? 1 : 0));
 }
 
 }  // namespace f3d

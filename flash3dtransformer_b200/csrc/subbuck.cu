@@ -187,7 +187,7 @@ int subbuck_build(const void *coord, const void *batch_sep, const void *red_sep,
     uint32_t cnt = (red_coord_rows - red_rows) * 3;
     zero_rows3_kernel<<<cdiv_u32(cnt, 256), 256, 0, st>>>(a.reduced_coord, red_rows, red_coord_rows);
   }
-  return check_launch("subbuck_build");
+  return check_launch("subbuck_build", ((max_n > 0 && batch > 0) ? 1 : 0) + (red_coord_rows > red_rows ? 1 : 0));
 }
 
 }  // namespace f3d

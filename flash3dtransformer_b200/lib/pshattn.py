@@ -345,3 +345,8 @@ def layernorm_bf16(x, weight, bias, out, eps=1e-5, gelu=False) -> None:
     st = _cabi.load().f3d_layernorm_bf16(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), x.shape[0], x.shape[1], float(eps),
                                          1 if gelu else 0, _dev_index(dev), _stream(dev))
     _cabi.check(st, "layernorm_bf16")
+
+
+def launch_count() -> int:
+    """Kernels launched by the native library since it was loaded."""
+    return int(_cabi.load().f3d_launch_count())

@@ -44,6 +44,8 @@ int f3d_get_sync(void);
  * (src/common/device_manager.cu:58-67, seed 3407) */
 int f3d_set_seed(uint64_t seed);
 uint64_t f3d_get_seed(void);
+/* number of CUDA kernels this library has launched since it was loaded (benchmark bookkeeping) */
+unsigned long long f3d_launch_count(void);
 /* frees the library's cached scratch buffers on every device */
 int f3d_release_workspaces(void);
 
