@@ -322,12 +322,17 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     if dominant:
         f = fam[dominant]
         sec = f["ms"] * 1e-3
+        traffic = None
         if dominant == "attention_fwd":
             achieved, peak, unit, bound = f["flops"] / sec / 1e12, peaks["tflops"], "TFLOP/s", "tensor"
+            # ncu capture of this kernel (profiles/attn_fwd_d32_w4096_8x120k.md): dram read + write equal the
+            # algorithmic operand bytes (236.2 MB measured against 255.5 MB algorithmic on the captured launch), so
+            # the per-launch traffic of a full-size launch is its algorithmic bytes scaled by that ratio
+            traffic = 0.9245 * f["bytes"] / f["launches"]
         else:
             achieved, peak, unit, bound = f["bytes"] / sec / 1e9, peaks["hbm_gbs"], "GB/s", "hbm"
         roofline = {"kernel": dominant, "bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
-                    "frac": achieved / peak, "traffic": None, "peak_source": peaks["source"],
+                    "frac": achieved / peak, "traffic": traffic, "peak_source": peaks["source"],
                     "launches": f["launches"], "avg_launch_ms": f["ms"] / f["launches"],
                     "share_of_kernel_time": f["ms"] / total_fam_ms}
     kernels = {k: {"ms_per_step": v["ms"] / args.steps, "share": v["ms"] / total_fam_ms,

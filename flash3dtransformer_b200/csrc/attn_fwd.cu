@@ -45,6 +45,12 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float m;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(m) : "f"(a), "f"(b), "f"(c));
+  return m;
+}
+
 template <int D> struct AttnCfg {
   static constexpr int DCH = D < 64 ? D : 64;       // columns per swizzled row
   static constexpr int NDCH = D / DCH;
@@ -176,7 +182,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       tc::tmem_ld_wait();
       float mx = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(__uint_as_float(r0[i]), __uint_as_float(r1[i])));
+      for (int i = 0; i < 32; ++i) mx = max3(mx, __uint_as_float(r0[i]), __uint_as_float(r1[i]));
       const float m_new = fmaxf(m_run, mx * a.scale_log2);
       const float alpha = fast_exp2(m_run - m_new);                 // 0 on the first tile (m_run = -inf)
       float sum = 0.f;
