@@ -725,3 +725,74 @@ extern "C" int f3d_batch_psh_scatter_pad_hash(
   F3D_TRY(psh_run(a, p, static_cast<uint32_t *>(scratch), instance_max_N, st));
   return maybe_sync(st, "batch_psh_scatter_pad_hash");
 }
+
+
+// ---------------------------------------------------------------------------------------------------------
+// Variant for callers that must not allocate device memory.
+//
+// Some hosts of this library cannot call cudaMalloc at all: a serving runtime that has handed every byte of the
+// GPU to its own arena (a stray cudaMalloc then fails or is treated as a bug), or a latency-critical loop that
+// cannot afford the device-wide synchronisation cudaMalloc and cudaFree imply.  For them the tile tables and
+// per-scene counters of the three ranking rounds live in the fixed array below instead of the grow-on-demand
+// workspace.  Every GPU that loads the library holds these 4 MiB until the process exits.
+//
+// The array is shared by all calls and keeps the previous call's contents; the tables that are accumulated
+// with atomics are cleared on the caller's stream at the start of every call, everything else is rewritten
+// before it is read.  Two calls that overlap on the same GPU (different streams or threads) race on it.
+constexpr size_t kStaticScratchWords = size_t(1) << 20;       // 4 MiB
+static __device__ __align__(256) uint32_t g_psh_static_scratch[kStaticScratchWords];
+
+namespace f3d {
+// The symbol name above is only a host-side handle; kernels need the device address, looked up once per
+// device with that device current.
+static int static_scratch_ptr(int device, uint32_t **out) {
+  static uint32_t *ptrs[16] = {nullptr};
+  if (device < 0 || device >= 16) return set_error(F3D_ERR_ARG, "device %d out of range", device);
+  if (!ptrs[device]) {
+    void *p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_psh_static_scratch);
+    if (e != cudaSuccess) return set_error(F3D_ERR_CUDA, "cudaGetSymbolAddress(static scratch): %s", cudaGetErrorString(e));
+    ptrs[device] = static_cast<uint32_t *>(p);
+  }
+  *out = ptrs[device];
+  return F3D_OK;
+}
+}  // namespace f3d
+
+extern "C" int f3d_batch_psh_scatter_pad_hash_noalloc(
+    const void *coord, void *bucket_id, void *bucket_counter, void *bucket_offset, const void *batch_sep,
+    uint32_t total_N, uint32_t batch_size, uint32_t instance_max_N, uint32_t num_bucket, uint32_t bucket_divisor,
+    uint32_t bucket_size, uint32_t num_vox, const void *bbox_min, const void *bbox_max, const void *probe_offsets,
+    void *cumsum_counter, void *scatter_coord, uint32_t pad_to_N, float pad_num, uint32_t hash_type,
+    int device, void *stream) {
+  F3D_TRY(psh_validate(total_N, batch_size, num_bucket, bucket_divisor, bucket_size, num_vox, pad_to_N, hash_type));
+  DeviceGuard guard(device);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (instance_max_N > total_N) instance_max_N = total_N;
+  PshPlan p = psh_plan(batch_size, instance_max_N, num_bucket);
+  if (p.scratch_words > kStaticScratchWords)
+    return set_error(F3D_ERR_UNSUPPORTED,
+                     "batch_psh_scatter_pad_hash_noalloc: this batch needs %zu scratch words (batch %u x %u tiles x %u "
+                     "buckets) but the fixed scratch holds %zu; use batch_psh_scatter_pad_hash or a smaller batch",
+                     p.scratch_words, batch_size, p.tiles_max, num_bucket, kStaticScratchWords);
+  uint32_t *scratch = nullptr;
+  F3D_TRY(static_scratch_ptr(device, &scratch));
+  PshArgs a{};
+  a.coord = static_cast<const __half *>(coord);
+  a.bucket_id = static_cast<uint16_t *>(bucket_id);
+  a.bucket_counter = static_cast<uint32_t *>(bucket_counter);
+  a.bucket_offset = static_cast<uint32_t *>(bucket_offset);
+  a.batch_sep = static_cast<const uint32_t *>(batch_sep);
+  a.cumsum_counter = static_cast<uint32_t *>(cumsum_counter);
+  a.scatter_coord = static_cast<__half *>(scatter_coord);
+  a.bbox_min = static_cast<const __half *>(bbox_min);
+  a.bbox_max = static_cast<const __half *>(bbox_max);
+  a.probe = static_cast<const int16_t *>(probe_offsets);
+  a.total_N = total_N; a.batch = batch_size; a.nb = num_bucket; a.divisor = bucket_divisor; a.cap = bucket_size;
+  a.num_vox = num_vox; a.hash_type = hash_type; a.pad_to = pad_to_N;
+  a.pad_bits = __half_as_ushort(__float2half_rn(pad_num));
+  a.coord_aligned = (reinterpret_cast<uintptr_t>(coord) % 16 == 0) ? 1 : 0;
+  uint64_t sd = f3d::seed();
+  a.key.k0 = (uint32_t)sd; a.key.k1 = (uint32_t)(sd >> 32);
+  return psh_run(a, p, scratch, instance_max_N, st);
+}

@@ -350,3 +350,39 @@ def layernorm_bf16(x, weight, bias, out, eps=1e-5, gelu=False) -> None:
 def launch_count() -> int:
     """Kernels launched by the native library since it was loaded."""
     return int(_cabi.load().f3d_launch_count())
+
+
+def batch_psh_scatter_pad_hash_noalloc(coord, bucket_id, bucket_counter, bucket_offset, batch_sep, instance_max_N,
+                                       num_bucket, bucket_divisor, bucket_size, num_vox, bbox_min, bbox_max,
+                                       probe_offsets, cumsum_counter, scatter_coord, pad_num, hash_type) -> None:
+    """batch_psh_scatter_pad_hash for hosts that may not allocate device memory: same arguments and results, but
+    the library's scratch tables sit in a fixed 4 MiB device array instead of a cudaMalloc'ed workspace.  Use it
+    when the process's GPU memory is owned by another allocator or when cudaMalloc's device-wide synchronisation
+    is not acceptable.  Batches whose tables do not fit raise RuntimeError; calls must not overlap on one GPU; the
+    first call on a device should be made outside stream capture.  No counterpart in the reference."""
+    tensors = [coord, bucket_id, bucket_counter, bucket_offset, batch_sep, probe_offsets, cumsum_counter,
+               scatter_coord, bbox_min, bbox_max]
+    names = ["coord", "bucket_id", "bucket_counter", "bucket_offset", "batch_sep", "probe_offsets", "cumsum_counter",
+             "scatter_coord", "bbox_min", "bbox_max"]
+    dev = _check_tensors(tensors, names)
+    _check_dtype([coord, scatter_coord, bbox_min, bbox_max], ["coord", "scatter_coord", "bbox_min", "bbox_max"],
+                 torch.float16)
+    _check_dtype([bucket_counter, bucket_offset, batch_sep, cumsum_counter],
+                 ["bucket_counter", "bucket_offset", "batch_sep", "cumsum_counter"], torch.uint32)
+    _check_dtype([bucket_id], ["bucket_id"], torch.uint16)
+    _check_dtype([probe_offsets], ["probe_offsets"], torch.int16)
+    _require(coord.dim() == 2 and coord.shape[1] == 3 and scatter_coord.dim() == 2 and scatter_coord.shape[1] == 3,
+             "coord and scatter_coord must be [rows, 3]")
+    total_n, batch = coord.shape[0], batch_sep.shape[0]
+    _require(bucket_id.numel() >= total_n and bucket_offset.numel() >= total_n,
+             "bucket_id / bucket_offset are shorter than coord")
+    _require(bucket_counter.numel() == batch * num_bucket and cumsum_counter.numel() == batch * num_bucket,
+             f"bucket_counter / cumsum_counter must be [{batch},{num_bucket}]")
+    _require(probe_offsets.numel() == 128 * 3 and bbox_min.numel() == 3 and bbox_max.numel() == 3,
+             "probe_offsets must be [128,3] and the bounding box 3 + 3 values")
+    st = _cabi.load().f3d_batch_psh_scatter_pad_hash_noalloc(
+        _ptr(coord), _ptr(bucket_id), _ptr(bucket_counter), _ptr(bucket_offset), _ptr(batch_sep),
+        total_n, batch, int(instance_max_N), int(num_bucket), int(bucket_divisor), int(bucket_size), int(num_vox),
+        _ptr(bbox_min), _ptr(bbox_max), _ptr(probe_offsets), _ptr(cumsum_counter), _ptr(scatter_coord),
+        scatter_coord.shape[0], float(pad_num), int(hash_type), _dev_index(dev), _stream(dev))
+    _cabi.check(st, "batch_psh_scatter_pad_hash_noalloc")

@@ -70,6 +70,24 @@ int f3d_batch_psh_scatter_pad_hash(
     void *cumsum_counter, void *scatter_coord, uint32_t pad_to_N, float pad_num, uint32_t hash_type,
     int device, void *stream);
 
+/* Same operation and arguments as f3d_batch_psh_scatter_pad_hash, for callers that may not allocate device memory
+ * (hosts whose GPU memory belongs entirely to another allocator, or loops that cannot take the device-wide
+ * synchronisation of cudaMalloc / cudaFree).  It has no counterpart in the reference.  The scratch tables live in a
+ * fixed 4 MiB device array inside the library (held on every GPU that loads it); the call performs no cudaMalloc,
+ * cudaFree or other allocating call.  Limits: the batch must satisfy
+ *     2*B*T*(NB+1) + 6*B*(NB+1) + 2*B*T <= 1,048,576   with B = batch_size, NB = num_bucket,
+ *     T = ceil(instance_max_N / tile), tile = clamp(2048*ceil(instance_max_N / 131072), 2048, 16384),
+ * otherwise F3D_STATUS_UNSUPPORTED is returned (8 scans of 120,000 points with 256 buckets need 256k words).
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress); make that first call
+ * outside any stream capture.  All calls share the array: calls that overlap on one GPU race and must be
+ * serialised by the caller. */
+int f3d_batch_psh_scatter_pad_hash_noalloc(
+    const void *coord, void *bucket_id, void *bucket_counter, void *bucket_offset, const void *batch_sep,
+    uint32_t total_N, uint32_t batch_size, uint32_t instance_max_N, uint32_t num_bucket, uint32_t bucket_divisor,
+    uint32_t bucket_size, uint32_t num_vox, const void *bbox_min, const void *bbox_max, const void *probe_offsets,
+    void *cumsum_counter, void *scatter_coord, uint32_t pad_to_N, float pad_num, uint32_t hash_type,
+    int device, void *stream);
+
 /* ---- sub-bucket construction + feature pooling ----
  * replaces f3d::batch_subbuck_reduce (src/psh/batch_subbuck_pooling_dispatcher.cu:35-144; binding
  * src/f3d_frontend.cu:127): local_subbuck_ker followed by reduce_feat_ker.

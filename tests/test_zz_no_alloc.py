@@ -1,0 +1,74 @@
+"""The allocation-free PSH entry point gives the same bits as the regular one.
+
+Some users of this library cannot let it call cudaMalloc: their GPU memory is owned by another allocator, or they
+run in a loop that must not take cudaMalloc's device-wide synchronisation.  For them
+f3d_batch_psh_scatter_pad_hash_noalloc keeps its scratch tables in a fixed device array.  This file runs last
+(pytest collects it after every other test file), calls the entry point through the C ABI twice in a row on
+different inputs - the fixed array still holds the first call's tables during the second - and compares every
+output with the regular entry point bit for bit; it also checks that an oversized batch is refused."""
+import numpy as np
+import pytest
+import torch
+
+from flash3dtransformer_b200 import synthetic
+
+pytestmark = pytest.mark.gpu
+
+
+def _buffers(dev, coords16, seps, nb, pad_to):
+    n, b = coords16.shape[0], len(seps)
+    return dict(
+        coord=torch.from_numpy(coords16).to(dev),
+        bucket_id=torch.ones(n, dtype=torch.uint16, device=dev),
+        bucket_counter=torch.zeros(b, nb, dtype=torch.uint32, device=dev),
+        bucket_offset=torch.empty(n, dtype=torch.uint32, device=dev),
+        batch_sep=torch.from_numpy(np.asarray(seps, dtype=np.uint32)).to(dev),
+        cumsum_counter=torch.zeros(b, nb, dtype=torch.uint32, device=dev),
+        scatter_coord=torch.full((pad_to, 3), float("nan"), dtype=torch.float16, device=dev),
+        bbox_min=torch.from_numpy(coords16.min(0)).to(dev), bbox_max=torch.from_numpy(coords16.max(0)).to(dev),
+    )
+
+
+def _call(fn, buf, probe, max_n, nb, div, bucket, hash_type):
+    fn(buf["coord"], buf["bucket_id"], buf["bucket_counter"], buf["bucket_offset"], buf["batch_sep"], max_n, nb, div,
+       bucket, 0xFFFF, buf["bbox_min"], buf["bbox_max"], probe, buf["cumsum_counter"], buf["scatter_coord"], 0.0,
+       hash_type)
+    torch.cuda.synchronize()
+    return {k: buf[k].cpu().numpy() for k in ("bucket_id", "bucket_counter", "bucket_offset", "cumsum_counter")} | \
+           {"scatter_coord": buf["scatter_coord"].cpu().numpy().view(np.uint16)}
+
+
+def test_noalloc_entry_point_matches_regular_entry_point(cuda_device):
+    from oracle import psh_oracle as po
+    from flash3dtransformer_b200.lib import pshattn
+    from flash3dtransformer_b200.psh import bucket as f3dbuck
+    probe = f3dbuck.generate_probe_offsets(cuda_device)
+    cases = [([30000, 17001, 25013, 999], 512, 2, 5), ([20000, 4097], 256, 1, 6)]
+    for sizes, bucket, hash_type, seed in cases:          # two calls in a row share the fixed scratch array
+        c32, seps = synthetic.batch(synthetic.lidar_scan, sizes, seed=seed)
+        c16 = c32.astype(np.float16)
+        nb, div = po.psh_params(sizes, bucket)
+        pad_to = -(-c16.shape[0] // bucket) * bucket
+        want = _call(pshattn.batch_psh_scatter_pad_hash, _buffers(cuda_device, c16, seps, nb, pad_to), probe,
+                     max(sizes), nb, div, bucket, hash_type)
+        got = _call(pshattn.batch_psh_scatter_pad_hash_noalloc, _buffers(cuda_device, c16, seps, nb, pad_to), probe,
+                    max(sizes), nb, div, bucket, hash_type)
+        for k in want:                                     # integer / index outputs: exact equality
+            assert np.array_equal(got[k], want[k]), k
+        po.scoreboard_check(got["bucket_id"], got["bucket_counter"], got["bucket_offset"], seps, nb)
+
+
+def test_noalloc_entry_point_refuses_oversized_batches(cuda_device):
+    from flash3dtransformer_b200.lib import pshattn
+    from flash3dtransformer_b200.psh import bucket as f3dbuck
+    probe = f3dbuck.generate_probe_offsets(cuda_device)
+    sizes = [70000] * 16
+    c16 = np.zeros((sum(sizes), 3), dtype=np.float16)
+    c16[:, 0] = np.linspace(0, 1, c16.shape[0])
+    seps = np.cumsum(sizes)
+    nb, div = 2048, 32                                      # 16 scenes x 35 tiles x 2049 columns do not fit 4 MiB
+    buf = _buffers(cuda_device, c16, seps, nb, c16.shape[0])
+    with pytest.raises(RuntimeError, match="fixed scratch"):
+        pshattn.batch_psh_scatter_pad_hash_noalloc(
+            buf["coord"], buf["bucket_id"], buf["bucket_counter"], buf["bucket_offset"], buf["batch_sep"], 70000, nb,
+            div, 64, 0xFFFF, buf["bbox_min"], buf["bbox_max"], probe, buf["cumsum_counter"], buf["scatter_coord"], 0.0, 1)
