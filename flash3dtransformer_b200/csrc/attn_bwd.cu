@@ -1,0 +1,414 @@
+// Bucketed self-attention backward on tcgen05 tensor cores, sm_100a.
+//
+// Implements buck_swin_bwd(Q, K, V, O, dO, LSE, Delta, dQ, dK, dV, Scope_buckets, bucket_size), which the reference's
+// Python layer calls (flash3dxfmr/layers/buck_swin.py:91) but whose kernel and binding are absent from the reference
+// snapshot (declaration src/f3d_frontend.cu:94-97, binding commented out :137).  Semantics follow the reference's
+// tests (tests/test_attn_bwd.py:24-27,54-62,79-441): Delta[b,t,h] = sum_d dO*O is written to the caller's buffer;
+// with P = exp(S - LSE), dV = P^T dO, dP = dO V^T, dS = P o (dP - Delta), dQ = dS K / sqrt(D), dK = dS^T Q / sqrt(D).
+// O and LSE may come from any forward implementation (the tests pass FlashAttention's).
+//
+// Kernels:
+//   attn_bwd_delta_kernel   Delta = rowsum(dO o O), one thread per (token, head)
+//   attn_bwd_kernel<D>      one CTA per (scope, 128-key block, head, batch row); it loops over the query tiles of
+//                           the scope and keeps dK, dV for its keys in tensor memory
+//       warp 0      TMA producer: K_j, V_j once; Q_i, dO_i through a 2-stage ring
+//       warp 1      issues S^T = K Q^T and dP^T = V dO^T into tensor memory (keys on the lanes), then, once the
+//                   compute warps have published P^T and dS^T as bf16 in shared memory, dV += P^T dO, dK += dS^T Q
+//                   (shared-memory A, K-major) and dQ_i = dS K (the same dS^T tile read as an MN-major A operand)
+//       warps 2-9   compute: each thread owns one key row and half of the query columns; p = exp2(s*c - lse),
+//                   ds = p*(dp - delta) with lse/delta of the tile staged in shared memory; then they read dQ_i from
+//                   tensor memory (queries on the lanes) and add it to an fp32 scratch with vector atomics
+//   attn_bwd_dq_convert     dQ = bf16(scratch / sqrt(D))
+// dQ needs the scratch because every key block of a scope contributes to every query; dK and dV are written once.
+#include "f3d_common.cuh"
+#include "tc_sm100.cuh"
+#include "../../include/f3d_b200.h"
+
+namespace f3d {
+
+int *status_word(int device);
+
+constexpr int kBwdThreads = 320;       // producer warp, MMA warp, 8 compute warps
+constexpr int kBK = 128;               // keys per CTA (tensor-memory lanes)
+
+struct AttnBwdArgs {
+  const float *lse; const float *delta; float *dq_acc; __nv_bfloat16 *dK; __nv_bfloat16 *dV; const uint32_t *scopes;
+  int B, L, H, num_scopes, k, bucket, kblocks_per_bucket;
+  float scale_log2, scale;
+  int *status;
+};
+
+__device__ __forceinline__ float bwd_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <int D> struct BwdCfg {
+  static constexpr int BQ = D == 128 ? 64 : 128;                 // queries per inner tile
+  static constexpr int DCH = D < 64 ? D : 64;
+  static constexpr int NDCH = D / DCH;
+  static constexpr int RB = DCH * 2;
+  static constexpr uint64_t SWZ = RB == 128 ? tc::kSwizzle128 : (RB == 64 ? tc::kSwizzle64 : tc::kSwizzle32);
+  static constexpr int kKVBytes = kBK * D * 2;                   // one of K_j, V_j
+  static constexpr int kQBytes = BQ * D * 2;                     // one of Q_i, dO_i
+  static constexpr int kQStage = 2 * kQBytes;
+  static constexpr int QCH = BQ / 64 ? BQ / 64 : 1;              // 64-query column chunks of the P^T / dS^T tiles
+  static constexpr int kPBytes = kBK * BQ * 2;                   // P^T or dS^T tile
+  static constexpr int kLsdBytes = 2 /*stages*/ * 2 * BQ * 4;
+  static constexpr int kSmem = 2 * kKVBytes + 2 * kQStage + 2 * kPBytes + kLsdBytes + 256 + 1024;
+  // tensor-memory columns: S^T, dP^T, dV, dK, dQ (dQ shares the S^T columns when 512 would be exceeded)
+  static constexpr bool kAliasDq = (2 * BQ + 3 * D) > 512;
+  static constexpr uint32_t kSCol = 0, kDpCol = BQ, kDvCol = 2 * BQ, kDkCol = 2 * BQ + D;
+  static constexpr uint32_t kDqCol = kAliasDq ? 0 : 2 * BQ + 2 * D;
+};
+
+template <int D>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, AttnBwdArgs a) {
+  using C = BwdCfg<D>;
+  constexpr int BQ = C::BQ;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char *sk = smem, *sv = sk + C::kKVBytes;
+  unsigned char *sqdo = sv + C::kKVBytes;                         // [2 stages][Q | dO]
+  // dS^T sits in front of P^T: with 64-query tiles the dQ MMA (M = 128) reads one 64-row atom past the dS^T tile,
+  // which then falls inside the P^T tile (rows 64..127 of that product are never used)
+  unsigned char *sds = sqdo + 2 * C::kQStage, *spt = sds + C::kPBytes;
+  float *slsd = reinterpret_cast<float *>(spt + C::kPBytes);      // [stage][lse2 | delta][BQ]
+  uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<unsigned char *>(slsd) + C::kLsdBytes);
+  uint64_t *kv_full = bars, *qdo_full = bars + 1, *qdo_empty = bars + 3, *s_full = bars + 5, *dp_full = bars + 6;
+  uint64_t *pds_full = bars + 7, *pds_empty = bars + 8, *dq_full = bars + 9, *dq_read = bars + 10, *dkv_full = bars + 11;
+  uint64_t *lsd_full = bars + 12;                                 // [2]
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 14);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kb_lin = blockIdx.x;
+  const int kb = kb_lin % a.kblocks_per_bucket;
+  const int bj = (kb_lin / a.kblocks_per_bucket) % a.k;
+  const int scope = kb_lin / (a.kblocks_per_bucket * a.k);
+  const int head = blockIdx.y, brow = blockIdx.z;
+  const uint32_t *my_scope = a.scopes + (size_t)scope * a.k;
+  const int qtiles_per_bucket = a.bucket / BQ;
+  const int num_qtiles = a.k * qtiles_per_bucket;
+  const int key_tok = (int)my_scope[bj] * a.bucket + kb * kBK;
+
+  if (threadIdx.x == 0) {
+    tc::mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; ++s) { tc::mbar_init(&qdo_full[s], 1); tc::mbar_init(&qdo_empty[s], 1); }
+    tc::mbar_init(s_full, 1); tc::mbar_init(dp_full, 1); tc::mbar_init(pds_full, 256); tc::mbar_init(pds_empty, 1);
+    tc::mbar_init(dq_full, 1); tc::mbar_init(dq_read, 256); tc::mbar_init(dkv_full, 1);
+    tc::mbar_init(&lsd_full[0], BQ); tc::mbar_init(&lsd_full[1], BQ);
+    *abort_flag = 0;
+    tc::mbar_fence_init();
+  }
+  if (warp == 1) { tc::tmem_alloc(tmem_slot, 512); tc::tmem_relinquish(); }
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  tc::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  tc::WaitCtx wc{abort_flag, a.status};
+
+  if (warp == 0) {
+    if (tc::elect_one()) {
+      tc::tma_prefetch_desc(&map_q); tc::tma_prefetch_desc(&map_k); tc::tma_prefetch_desc(&map_v); tc::tma_prefetch_desc(&map_do);
+      tc::mbar_expect_tx(kv_full, 2 * C::kKVBytes);
+#pragma unroll
+      for (int c = 0; c < C::NDCH; ++c) {
+        tc::tma_load_3d(sk + c * kBK * C::RB, &map_k, kv_full, c * C::DCH, head, brow * a.L + key_tok);
+        tc::tma_load_3d(sv + c * kBK * C::RB, &map_v, kv_full, c * C::DCH, head, brow * a.L + key_tok);
+      }
+      for (int i = 0; i < num_qtiles; ++i) {
+        const int s = i & 1;
+        const uint32_t ph = (uint32_t)(i >> 1) & 1u;
+        if (!tc::mbar_wait(&qdo_empty[s], ph ^ 1u, wc, 301)) break;
+        const int q_tok = (int)my_scope[i / qtiles_per_bucket] * a.bucket + (i % qtiles_per_bucket) * BQ;
+        unsigned char *sq = sqdo + s * C::kQStage, *sdo = sq + C::kQBytes;
+        tc::mbar_expect_tx(&qdo_full[s], C::kQStage);
+#pragma unroll
+        for (int c = 0; c < C::NDCH; ++c) {
+          tc::tma_load_3d(sq + c * BQ * C::RB, &map_q, &qdo_full[s], c * C::DCH, head, brow * a.L + q_tok);
+          tc::tma_load_3d(sdo + c * BQ * C::RB, &map_do, &qdo_full[s], c * C::DCH, head, brow * a.L + q_tok);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (tc::elect_one()) {
+      constexpr uint32_t idesc_s = tc::make_idesc_f16(kBK, BQ, true, false, false);          // S^T, dP^T
+      constexpr uint32_t idesc_kv = tc::make_idesc_f16(kBK, C::DCH, true, false, true);      // dV, dK: B MN-major
+      constexpr uint32_t idesc_dq = tc::make_idesc_f16(128, C::DCH, true, true, true);       // dQ: A and B MN-major
+      const uint32_t k_addr = tc::smem_u32(sk), v_addr = tc::smem_u32(sv);
+      const uint32_t pt_addr = tc::smem_u32(spt), ds_addr = tc::smem_u32(sds);
+      bool ok = tc::mbar_wait(kv_full, 0, wc, 302);
+
+      auto issue_s_dp = [&](int i) -> bool {
+        const int s = i & 1;
+        const uint32_t ph = (uint32_t)(i >> 1) & 1u;
+        if (!tc::mbar_wait(&qdo_full[s], ph, wc, 303)) return false;
+        if (C::kAliasDq && i > 0 && !tc::mbar_wait(dq_read, (uint32_t)(i - 1) & 1u, wc, 304)) return false;
+        tc::tc_fence_after_sync();
+        const uint32_t q_addr = tc::smem_u32(sqdo + s * C::kQStage), do_addr = q_addr + C::kQBytes;
+#pragma unroll
+        for (int c = 0; c < C::NDCH; ++c)
+#pragma unroll
+          for (int kk = 0; kk < C::DCH / 16; ++kk)
+            tc::mma_f16_ss(tmem_base + C::kSCol, tc::make_smem_desc(k_addr + c * kBK * C::RB + kk * 32, 16, 8 * C::RB, C::SWZ),
+                           tc::make_smem_desc(q_addr + c * BQ * C::RB + kk * 32, 16, 8 * C::RB, C::SWZ), idesc_s, (c | kk) != 0);
+        tc::mma_commit(s_full);
+#pragma unroll
+        for (int c = 0; c < C::NDCH; ++c)
+#pragma unroll
+          for (int kk = 0; kk < C::DCH / 16; ++kk)
+            tc::mma_f16_ss(tmem_base + C::kDpCol, tc::make_smem_desc(v_addr + c * kBK * C::RB + kk * 32, 16, 8 * C::RB, C::SWZ),
+                           tc::make_smem_desc(do_addr + c * BQ * C::RB + kk * 32, 16, 8 * C::RB, C::SWZ), idesc_s, (c | kk) != 0);
+        tc::mma_commit(dp_full);
+        return true;
+      };
+
+      if (ok) ok = issue_s_dp(0);
+      for (int i = 0; i < num_qtiles && ok; ++i) {
+        const int s = i & 1;
+        if (!tc::mbar_wait(pds_full, (uint32_t)i & 1u, wc, 305)) { ok = false; break; }
+        tc::tc_fence_after_sync();
+        const uint32_t q_addr = tc::smem_u32(sqdo + s * C::kQStage), do_addr = q_addr + C::kQBytes;
+        // dV += P^T dO and dK += dS^T Q: A = [keys x queries] tiles in shared memory (128-byte rows of 64 queries)
+#pragma unroll
+        for (int c = 0; c < C::NDCH; ++c) {
+#pragma unroll
+          for (int qk = 0; qk < BQ / 16; ++qk) {
+            const uint32_t a_off = (qk / 4) * (kBK * 128) + (qk % 4) * 32;
+            const uint32_t b_off = c * BQ * C::RB + qk * 16 * C::RB;
+            tc::mma_f16_ss(tmem_base + C::kDvCol + c * C::DCH, tc::make_smem_desc(pt_addr + a_off, 16, 1024, tc::kSwizzle128),
+                           tc::make_smem_desc(do_addr + b_off, 16, 8 * C::RB, C::SWZ), idesc_kv, (i | qk) != 0);
+            tc::mma_f16_ss(tmem_base + C::kDkCol + c * C::DCH, tc::make_smem_desc(ds_addr + a_off, 16, 1024, tc::kSwizzle128),
+                           tc::make_smem_desc(q_addr + b_off, 16, 8 * C::RB, C::SWZ), idesc_kv, (i | qk) != 0);
+          }
+        }
+        tc::mma_commit(&qdo_empty[s]);
+        // dQ_i = dS K_j: A = the dS^T tile read M-major (queries contiguous), K = keys in steps of 16 rows
+        if (i > 0 && !C::kAliasDq && !tc::mbar_wait(dq_read, (uint32_t)(i - 1) & 1u, wc, 306)) { ok = false; break; }
+        tc::tc_fence_after_sync();
+#pragma unroll
+        for (int c = 0; c < C::NDCH; ++c)
+#pragma unroll
+          for (int ks = 0; ks < kBK / 16; ++ks)
+            tc::mma_f16_ss(tmem_base + C::kDqCol + c * C::DCH,
+                           tc::make_smem_desc(ds_addr + ks * 16 * 128, kBK * 128, 1024, tc::kSwizzle128),
+                           tc::make_smem_desc(k_addr + c * kBK * C::RB + ks * 16 * C::RB, 16, 8 * C::RB, C::SWZ), idesc_dq, ks != 0);
+        tc::mma_commit(pds_empty);
+        tc::mma_commit(dq_full);
+        if (i + 1 < num_qtiles) {
+          if (C::kAliasDq) {
+            // S^T of the next tile overwrites the dQ columns: it is issued after the compute warps have read them
+            ok = issue_s_dp(i + 1);
+          } else {
+            ok = issue_s_dp(i + 1);
+          }
+        } else {
+          tc::mma_commit(dkv_full);
+        }
+      }
+    }
+  } else {
+    const int cw = warp - 2;                          // 0..7
+    const int q4 = warp & 3;                          // tensor-memory lane quadrant of this warp
+    const int wg = cw >> 2;                           // which half of the columns
+    const int ctid = cw * 32 + lane;                  // 0..255
+    const int row = q4 * 32 + lane;                   // key row (S^T, dP^T, dK, dV) or query row (dQ)
+    const uint32_t lane_off = (uint32_t)(q4 * 32) << 16;
+    constexpr int HALF = BQ / 2;                      // query columns per compute thread
+    bool ok = true;
+    for (int i = 0; i < num_qtiles && ok; ++i) {
+      const int s = i & 1;
+      const int q_tok = (int)my_scope[i / qtiles_per_bucket] * a.bucket + (i % qtiles_per_bucket) * BQ;
+      float *lse2 = slsd + s * 2 * BQ, *dl = lse2 + BQ;
+      if (ctid < BQ) {
+        const size_t idx = ((size_t)brow * a.L + q_tok + ctid) * a.H + head;
+        lse2[ctid] = a.lse[idx] * 1.4426950408889634f;
+        dl[ctid] = a.delta[idx];
+        tc::mbar_arrive(&lsd_full[s]);
+      }
+      if (!tc::mbar_wait(&lsd_full[s], (uint32_t)(i >> 1) & 1u, wc, 312)) { ok = false; break; }
+      if (!tc::mbar_wait(s_full, (uint32_t)i & 1u, wc, 307) || !tc::mbar_wait(dp_full, (uint32_t)i & 1u, wc, 308)) { ok = false; break; }
+      if (i > 0 && !tc::mbar_wait(pds_empty, (uint32_t)(i - 1) & 1u, wc, 309)) { ok = false; break; }
+      tc::tc_fence_after_sync();
+#pragma unroll
+      for (int ch = 0; ch < HALF / 32; ++ch) {
+        const int col0 = wg * HALF + ch * 32;
+        uint32_t sr[32], dr[32];
+        tc::tmem_ld_32x32b_x32(tmem_base + lane_off + C::kSCol + col0, sr);
+        tc::tmem_ld_32x32b_x32(tmem_base + lane_off + C::kDpCol + col0, dr);
+        tc::tmem_ld_wait();
+        unsigned char *prow = spt + (col0 / 64) * (kBK * 128) + row * 128;
+        unsigned char *drow = sds + (col0 / 64) * (kBK * 128) + row * 128;
+#pragma unroll
+        for (int v8 = 0; v8 < 4; ++v8) {
+          uint4 pw, dw;
+          __nv_bfloat162 *ph2 = reinterpret_cast<__nv_bfloat162 *>(&pw), *dh2 = reinterpret_cast<__nv_bfloat162 *>(&dw);
+          const float4 l0 = *reinterpret_cast<const float4 *>(lse2 + col0 + v8 * 8), l1 = *reinterpret_cast<const float4 *>(lse2 + col0 + v8 * 8 + 4);
+          const float4 d0 = *reinterpret_cast<const float4 *>(dl + col0 + v8 * 8), d1 = *reinterpret_cast<const float4 *>(dl + col0 + v8 * 8 + 4);
+          const float ls[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+          const float dd[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+          float p[8], g[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            p[e] = bwd_exp2(fmaf(__uint_as_float(sr[v8 * 8 + e]), a.scale_log2, -ls[e]));
+            g[e] = p[e] * (__uint_as_float(dr[v8 * 8 + e]) - dd[e]);
+          }
+#pragma unroll
+          for (int e = 0; e < 4; ++e) { ph2[e] = __floats2bfloat162_rn(p[2 * e], p[2 * e + 1]); dh2[e] = __floats2bfloat162_rn(g[2 * e], g[2 * e + 1]); }
+          const int chunk16 = ((col0 % 64) / 8 + v8) ^ (row & 7);
+          *reinterpret_cast<uint4 *>(prow + chunk16 * 16) = pw;
+          *reinterpret_cast<uint4 *>(drow + chunk16 * 16) = dw;
+        }
+      }
+      tc::fence_proxy_async();
+      tc::tc_fence_before_sync();
+      tc::mbar_arrive(pds_full);
+      // dQ_i: queries on the lanes; this warpgroup takes half of the D columns
+      if (!tc::mbar_wait(dq_full, (uint32_t)i & 1u, wc, 310)) { ok = false; break; }
+      tc::tc_fence_after_sync();
+      if (row < BQ && q_tok + row < a.L) {
+        float *dst = a.dq_acc + (((size_t)brow * a.L + q_tok + row) * a.H + head) * D + wg * (D / 2);
+#pragma unroll
+        for (int c = 0; c < D / 2; c += 8) {
+          uint32_t o[8];
+          asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                       : "=r"(o[0]), "=r"(o[1]), "=r"(o[2]), "=r"(o[3]), "=r"(o[4]), "=r"(o[5]), "=r"(o[6]), "=r"(o[7])
+                       : "r"(tmem_base + lane_off + C::kDqCol + wg * (D / 2) + c) : "memory");
+          tc::tmem_ld_wait();
+          atomicAdd(reinterpret_cast<float4 *>(dst + c), make_float4(__uint_as_float(o[0]), __uint_as_float(o[1]), __uint_as_float(o[2]), __uint_as_float(o[3])));
+          atomicAdd(reinterpret_cast<float4 *>(dst + c + 4), make_float4(__uint_as_float(o[4]), __uint_as_float(o[5]), __uint_as_float(o[6]), __uint_as_float(o[7])));
+        }
+      }
+      tc::tc_fence_before_sync();
+      tc::mbar_arrive(dq_read);
+    }
+    if (ok && tc::mbar_wait(dkv_full, 0, wc, 311) && key_tok + row < a.L) {
+      tc::tc_fence_after_sync();
+      const size_t base = (((size_t)brow * a.L + key_tok + row) * a.H + head) * D + wg * (D / 2);
+#pragma unroll
+      for (int c = 0; c < D / 2; c += 8) {
+        uint32_t kk[8], vv[8];
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                     : "=r"(kk[0]), "=r"(kk[1]), "=r"(kk[2]), "=r"(kk[3]), "=r"(kk[4]), "=r"(kk[5]), "=r"(kk[6]), "=r"(kk[7])
+                     : "r"(tmem_base + lane_off + C::kDkCol + wg * (D / 2) + c) : "memory");
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                     : "=r"(vv[0]), "=r"(vv[1]), "=r"(vv[2]), "=r"(vv[3]), "=r"(vv[4]), "=r"(vv[5]), "=r"(vv[6]), "=r"(vv[7])
+                     : "r"(tmem_base + lane_off + C::kDvCol + wg * (D / 2) + c) : "memory");
+        tc::tmem_ld_wait();
+        uint4 kw, vw;
+        __nv_bfloat162 *k2 = reinterpret_cast<__nv_bfloat162 *>(&kw), *v2 = reinterpret_cast<__nv_bfloat162 *>(&vw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          k2[e] = __floats2bfloat162_rn(__uint_as_float(kk[2 * e]) * a.scale, __uint_as_float(kk[2 * e + 1]) * a.scale);
+          v2[e] = __floats2bfloat162_rn(__uint_as_float(vv[2 * e]), __uint_as_float(vv[2 * e + 1]));
+        }
+        *reinterpret_cast<uint4 *>(a.dK + base + c) = kw;
+        *reinterpret_cast<uint4 *>(a.dV + base + c) = vw;
+      }
+    }
+  }
+
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) { tc::tc_fence_after_sync(); tc::tmem_dealloc(tmem_base, 512); }
+}
+
+// Delta[b,t,h] = sum_d dO * O  (tests/test_attn_bwd.py:24-27)
+__global__ void attn_bwd_delta_kernel(const __nv_bfloat16 *__restrict__ O, const __nv_bfloat16 *__restrict__ dO,
+                                      float *__restrict__ delta, size_t rows, int D) {
+  size_t r = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  const uint4 *po = reinterpret_cast<const uint4 *>(O + r * D), *pd = reinterpret_cast<const uint4 *>(dO + r * D);
+  float acc = 0.f;
+  for (int c = 0; c < D / 8; ++c) {
+    uint4 a4 = __ldg(po + c), b4 = __ldg(pd + c);
+    const __nv_bfloat162 *x = reinterpret_cast<const __nv_bfloat162 *>(&a4), *y = reinterpret_cast<const __nv_bfloat162 *>(&b4);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { float2 f = __bfloat1622float2(x[e]), g = __bfloat1622float2(y[e]); acc = fmaf(f.x, g.x, acc); acc = fmaf(f.y, g.y, acc); }
+  }
+  delta[r] = acc;
+}
+
+__global__ void attn_bwd_dq_convert_kernel(const float *__restrict__ acc, __nv_bfloat16 *__restrict__ dQ, size_t n8, float scale) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  float4 a4 = reinterpret_cast<const float4 *>(acc)[2 * i], b4 = reinterpret_cast<const float4 *>(acc)[2 * i + 1];
+  uint4 w;
+  __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&w);
+  h[0] = __floats2bfloat162_rn(a4.x * scale, a4.y * scale); h[1] = __floats2bfloat162_rn(a4.z * scale, a4.w * scale);
+  h[2] = __floats2bfloat162_rn(b4.x * scale, b4.y * scale); h[3] = __floats2bfloat162_rn(b4.z * scale, b4.w * scale);
+  reinterpret_cast<uint4 *>(dQ)[i] = w;
+}
+
+template <int D>
+static int launch_attn_bwd(const void *Q, const void *K, const void *V, const void *dO, AttnBwdArgs a, int device, cudaStream_t st) {
+  using C = BwdCfg<D>;
+  static bool attr[16] = {false};
+  auto kern = attn_bwd_kernel<D>;
+  if (device < 16 && !attr[device]) {
+    F3D_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem));
+    attr[device] = true;
+  }
+  CUtensorMap mq, mk, mv, mdo;
+  const uint64_t rows = (uint64_t)a.B * a.L;
+  const uint64_t s1 = (uint64_t)D * 2, s2 = (uint64_t)a.H * D * 2;
+  F3D_TRY(encode_tmap_3d(&mq, 0, Q, D, a.H, rows, s1, s2, C::DCH, 1, C::BQ, C::RB));
+  F3D_TRY(encode_tmap_3d(&mdo, 0, dO, D, a.H, rows, s1, s2, C::DCH, 1, C::BQ, C::RB));
+  F3D_TRY(encode_tmap_3d(&mk, 0, K, D, a.H, rows, s1, s2, C::DCH, 1, kBK, C::RB));
+  F3D_TRY(encode_tmap_3d(&mv, 0, V, D, a.H, rows, s1, s2, C::DCH, 1, kBK, C::RB));
+  dim3 grid(a.num_scopes * a.k * a.kblocks_per_bucket, a.H, a.B);
+  kern<<<grid, kBwdThreads, C::kSmem, st>>>(mq, mk, mv, mdo, a);
+  return check_launch("buck_swin_bwd");
+}
+
+}  // namespace f3d
+
+using namespace f3d;
+
+extern "C" int f3d_buck_swin_bwd(const void *Q, const void *K, const void *V, const void *O, const void *dO, const void *LSE,
+                                 void *Delta, void *dQ, void *dK, void *dV, const void *scope_buckets, int B, int L, int H,
+                                 int D, int num_scopes, int scope_size, uint32_t bucket_size, int device, void *stream) {
+  if (B <= 0 || L <= 0 || H <= 0) return set_error(F3D_ERR_ARG, "buck_swin_bwd: empty tensor");
+  if (D != 16 && D != 32 && D != 64 && D != 128) return set_error(F3D_ERR_UNSUPPORTED, "buck_swin_bwd: head_dim %d (16, 32, 64, 128 are supported)", D);
+  if (bucket_size == 0 || bucket_size % 128) return set_error(F3D_ERR_UNSUPPORTED, "buck_swin_bwd: bucket_size %u must be a positive multiple of 128", bucket_size);
+  if (L % (int)bucket_size) return set_error(F3D_ERR_ARG, "buck_swin_bwd: sequence length %d is not a multiple of bucket_size %u", L, bucket_size);
+  if (num_scopes < 0 || scope_size <= 0) return set_error(F3D_ERR_ARG, "buck_swin_bwd: Scope_buckets must be [S,k] with k > 0");
+  if ((long long)H > 65535 || (long long)B > 65535) return set_error(F3D_ERR_UNSUPPORTED, "buck_swin_bwd: H and B must fit a grid dimension");
+  DeviceGuard guard(device);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  F3D_TRY(maybe_sync(st, "buck_swin_bwd"));
+  const size_t rows = (size_t)B * L * H;
+  attn_bwd_delta_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(O), static_cast<const __nv_bfloat16 *>(dO),
+                                                                       static_cast<float *>(Delta), rows, D);
+  F3D_TRY(check_launch("buck_swin_bwd (delta)"));
+  if (num_scopes == 0) return F3D_OK;
+  void *acc = nullptr;
+  F3D_TRY(workspace(device, 2, rows * D * sizeof(float), &acc));
+  F3D_CUDA_TRY(cudaMemsetAsync(acc, 0, rows * D * sizeof(float), st));
+  const float scale = 1.f / sqrtf((float)D);
+  AttnBwdArgs a{static_cast<const float *>(LSE), static_cast<const float *>(Delta), static_cast<float *>(acc),
+                static_cast<__nv_bfloat16 *>(dK), static_cast<__nv_bfloat16 *>(dV), static_cast<const uint32_t *>(scope_buckets),
+                B, L, H, num_scopes, scope_size, (int)bucket_size, (int)bucket_size / kBK, 1.4426950408889634f * scale, scale,
+                status_word(device)};
+  if (!a.status) return F3D_ERR_CUDA;
+  int rc;
+  switch (D) {
+    case 16: rc = launch_attn_bwd<16>(Q, K, V, dO, a, device, st); break;
+    case 32: rc = launch_attn_bwd<32>(Q, K, V, dO, a, device, st); break;
+    case 64: rc = launch_attn_bwd<64>(Q, K, V, dO, a, device, st); break;
+    default: rc = launch_attn_bwd<128>(Q, K, V, dO, a, device, st); break;
+  }
+  F3D_TRY(rc);
+  const size_t n8 = rows * D / 8;
+  attn_bwd_dq_convert_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>(static_cast<const float *>(acc), static_cast<__nv_bfloat16 *>(dQ), n8, scale);
+  F3D_TRY(check_launch("buck_swin_bwd (dq convert)"));
+  return maybe_sync(st, "buck_swin_bwd");
+}

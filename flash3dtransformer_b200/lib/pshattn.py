@@ -386,3 +386,18 @@ def batch_psh_scatter_pad_hash_noalloc(coord, bucket_id, bucket_counter, bucket_
         _ptr(bbox_min), _ptr(bbox_max), _ptr(probe_offsets), _ptr(cumsum_counter), _ptr(scatter_coord),
         scatter_coord.shape[0], float(pad_num), int(hash_type), _dev_index(dev), _stream(dev))
     _cabi.check(st, "batch_psh_scatter_pad_hash_noalloc")
+
+
+def buck_swin_bwd(Q, K, V, O, dO, LSE, Delta, dQ, dK, dV, Scope_buckets, bucket_size) -> None:
+    """f3d::buck_swin_bwd (declared src/f3d_frontend.cu:94-97; caller flash3dxfmr/layers/buck_swin.py:91).
+    Delta, dQ, dK, dV are written in place."""
+    dev, (b, l, h, d) = _check_qkv([Q, K, V, O, dO, dQ, dK, dV], ["Q", "K", "V", "O", "dO", "dQ", "dK", "dV"])
+    _check_tensors([LSE, Delta, Scope_buckets], ["LSE", "Delta", "Scope_buckets"])
+    _check_dtype([LSE, Delta], ["LSE", "Delta"], torch.float32)
+    _check_dtype([Scope_buckets], ["Scope_buckets"], torch.uint32)
+    _require(tuple(LSE.shape) == (b, l, h) and tuple(Delta.shape) == (b, l, h), f"LSE and Delta must be [{b},{l},{h}]")
+    _require(Scope_buckets.dim() == 2, "Scope_buckets must be [num_scopes, scope_size]")
+    st = _cabi.load().f3d_buck_swin_bwd(_ptr(Q), _ptr(K), _ptr(V), _ptr(O), _ptr(dO), _ptr(LSE), _ptr(Delta), _ptr(dQ),
+                                        _ptr(dK), _ptr(dV), _ptr(Scope_buckets), b, l, h, d, Scope_buckets.shape[0],
+                                        Scope_buckets.shape[1], int(bucket_size), _dev_index(dev), _stream(dev))
+    _cabi.check(st, "buck_swin_bwd")

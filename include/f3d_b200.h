@@ -134,6 +134,20 @@ int f3d_additive_unpool_bwd(
     void *grad_res, void *grad_down, const void *grad_up_added, const void *unpool_ind, uint32_t up_rows,
     uint32_t unpool_rows, uint32_t feat_dim, int feat_dtype, uint32_t subbuck_size, int device, void *stream);
 
+/* ---- bucketed self-attention backward ----
+ * provides f3d::buck_swin_bwd, declared at src/f3d_frontend.cu:94-97 and called by
+ * flash3dxfmr/layers/buck_swin.py:91; absent from the reference snapshot like the forward.  Semantics:
+ * tests/test_attn_bwd.py:24-27,54-62,79-441.
+ *   Q, K, V, O, dO  bf16 [B,L,H,D]   in  (O and LSE may come from any forward implementation)
+ *   LSE             fp32 [B,L,H]     in
+ *   Delta           fp32 [B,L,H]     out  rowsum(dO * O)
+ *   dQ, dK, dV      bf16 [B,L,H,D]   out  (dQ is written for every token - zero for buckets no scope lists; dK, dV
+ *                                          only for listed buckets)
+ * Uses an fp32 scratch of B*L*H*D elements for the dQ reduction (library workspace). */
+int f3d_buck_swin_bwd(const void *Q, const void *K, const void *V, const void *O, const void *dO, const void *LSE,
+                      void *Delta, void *dQ, void *dK, void *dV, const void *scope_buckets, int B, int L, int H, int D,
+                      int num_scopes, int scope_size, uint32_t bucket_size, int device, void *stream);
+
 /* reads and clears the device status word: kernels that wait on mbarriers give up after a bounded time and record
  * the waiting site there; returns F3D_STATUS_DEVICE if a wait was abandoned since the last call (synchronises). */
 int f3d_device_status(int device);

@@ -1,0 +1,93 @@
+"""GPU parity of bucketed attention backward against autograd of the fp32 CPU oracle.
+
+The reference accepts max < 4-8 and mean < 0.08-0.4 against FlashAttention's gradients
+(tests/test_attn_bwd.py:176-376).  The bars here are far tighter: for each of dQ, dK, dV the largest error is at most
+3 % of the tensor's largest entry, and the mean error exceeds the floor set by rounding the exact gradient to bf16 by
+at most 3e-3 of the mean magnitude (two bf16-rounded operands, P and dS, enter every product).  Delta is compared
+with sum(dO * O) directly (tests/test_attn_bwd.py:24-27)."""
+import pytest
+import torch
+
+from oracle import attn_oracle as ao
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(dev, b, l, h, d, bucket, scopes, seed=0, mul=1.0):
+    from flash3dtransformer_b200.lib import pshattn
+    g = torch.Generator().manual_seed(seed)
+    q, k, v, do = ((torch.randn(b, l, h, d, generator=g) * mul).bfloat16() for _ in range(4))
+    sc = torch.tensor(scopes, dtype=torch.int64)
+    scd = sc.to(torch.uint32).to(dev)
+    qd, kd, vd, dod = (t.to(dev) for t in (q, k, v, do))
+    o = torch.zeros_like(qd)
+    lse = torch.zeros(b, l, h, device=dev)
+    pshattn.buck_swin_fwd(qd, kd, vd, o, lse, scd, bucket)
+    delta = torch.zeros(b, l, h, device=dev)
+    dq, dk, dv = (torch.zeros_like(qd) for _ in range(3))
+    pshattn.buck_swin_bwd(qd, kd, vd, o, dod, lse, delta, dq, dk, dv, scd, bucket)
+    pshattn.device_status()
+    rq, rk, rv, rdelta = ao.buck_swin_bwd(q, k, v, do, sc, bucket)
+    exp_delta = (dod.float() * o.float()).sum(-1)
+    return dict(dq=dq.float().cpu(), dk=dk.float().cpu(), dv=dv.float().cpu(), delta=delta.cpu(),
+                rq=rq, rk=rk, rv=rv, rdelta=rdelta, exp_delta=exp_delta.cpu())
+
+
+def _check_grad(name, got, ref, max_frac=0.03, mean_excess=3e-3):
+    assert torch.isfinite(got).all(), name
+    err = (got - ref).abs()
+    assert err.max().item() <= max_frac * ref.abs().max().item(), f"{name}: max err {err.max().item()} vs max {ref.abs().max().item()}"
+    rel = (err.mean() / ref.abs().mean()).item()
+    floor = ((ref.bfloat16().float() - ref).abs().mean() / ref.abs().mean()).item()
+    assert rel <= floor + mean_excess, f"{name}: mean rel {rel} (floor {floor})"
+
+
+def _check_all(r):
+    assert torch.allclose(r["delta"], r["exp_delta"], atol=1e-3, rtol=1e-3)          # exact definition on the GPU's own O
+    assert (r["delta"] - r["rdelta"]).abs().max().item() <= 0.05                      # and close to the fp32 oracle's
+    _check_grad("dQ", r["dq"], r["rq"])
+    _check_grad("dK", r["dk"], r["rk"])
+    _check_grad("dV", r["dv"], r["rv"])
+
+
+@pytest.mark.parametrize("d", [16, 32, 64, 128])
+def test_single_bucket_scopes(cuda_device, d):
+    _check_all(_run(cuda_device, 2, 1024, 2, d, 256, [[0], [1], [2], [3]]))
+
+
+@pytest.mark.parametrize("b,l,h,d,bucket,k", [(1, 4096, 4, 32, 512, 8), (2, 2048, 8, 32, 512, 2), (1, 1536, 2, 64, 128, 3),
+                                             (1, 1280, 2, 128, 256, 5), (2, 2048, 4, 16, 512, 4)])
+def test_multi_bucket_scopes(cuda_device, b, l, h, d, bucket, k):
+    nb = l // bucket
+    scopes = [list(range(i, i + k)) for i in range(0, nb, k)]
+    _check_all(_run(cuda_device, b, l, h, d, bucket, scopes, seed=1))
+
+
+def test_unlisted_buckets_and_permutation(cuda_device):
+    r = _run(cuda_device, 1, 2048, 2, 32, 256, [[0, 5], [2, 7]], seed=4)
+    _check_all(r)
+    for bk in (1, 3, 4, 6):
+        for key in ("dq", "dk", "dv"):
+            assert torch.all(r[key][:, bk * 256:(bk + 1) * 256] == 0)
+    a = _run(cuda_device, 1, 1024, 2, 32, 256, [[0, 1, 2, 3]], seed=5)
+    b = _run(cuda_device, 1, 1024, 2, 32, 256, [[2, 0, 3, 1]], seed=5)
+    for key in ("dk", "dv"):
+        assert torch.allclose(a[key], b[key], atol=2e-2, rtol=2e-2)
+
+
+def test_uniform_attention_dv(cuda_device):
+    """Q = 0 makes attention uniform: dV is the column mean of dO over the scope (tests/test_attn_bwd.py:406-439)."""
+    from flash3dtransformer_b200.lib import pshattn
+    dev = cuda_device
+    l, h, d, bucket = 512, 2, 32, 256
+    g = torch.Generator().manual_seed(7)
+    q = torch.zeros(1, l, h, d, dtype=torch.bfloat16, device=dev)
+    k, v, do = (torch.randn(1, l, h, d, generator=g).bfloat16().to(dev) for _ in range(3))
+    sc = torch.tensor([[0, 1]], dtype=torch.uint32, device=dev)
+    o = torch.zeros_like(q); lse = torch.zeros(1, l, h, device=dev); delta = torch.zeros(1, l, h, device=dev)
+    dq, dk, dv = (torch.zeros_like(q) for _ in range(3))
+    pshattn.buck_swin_fwd(q, k, v, o, lse, sc, bucket)
+    pshattn.buck_swin_bwd(q, k, v, o, do, lse, delta, dq, dk, dv, sc, bucket)
+    exp = do.float().mean(dim=1, keepdim=True).expand_as(do)
+    assert torch.allclose(dv.float(), exp, atol=2e-3, rtol=2e-2)
+    assert dk.float().abs().max().item() <= 1e-6          # Q = 0 kills dK
