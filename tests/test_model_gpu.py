@@ -79,3 +79,55 @@ def test_backbone_forward_matches_cpu_oracle(cuda_device):
     assert (err.mean() / ref.abs().mean()).item() <= 1e-2, (err.mean() / ref.abs().mean()).item()
     # rows behind the last scene (tail padding) carry no garbage
     assert torch.isfinite(out).all()
+
+
+def test_backbone_forward_backward_runs(cuda_device):
+    """The reference's integration smoke test (tests/test_psh_hourglass.py:51-163): a two-level model runs forward
+    and backward, and gradients reach every parameter."""
+    from flash3dtransformer_b200 import configs
+    from flash3dtransformer_b200.lib import pshattn
+    torch.manual_seed(0)
+    model = configs.flash3d_backbone(channels=(32, 64), depths=(2, 2)).to(cuda_device)
+    coords, seps = _batch(cuda_device, [30000, 22000])
+    out = model(coords, coords, seps)
+    loss = out.float().mean()
+    loss.backward()
+    pshattn.device_status()
+    missing = [n for n, p in model.named_parameters() if p.grad is None]
+    assert not missing, missing
+    for n, p in model.named_parameters():
+        assert torch.isfinite(p.grad).all(), n
+    assert model.psh_scatter.lin.weight.grad.abs().sum().item() > 0          # tests/test_psh.py:367-396
+
+
+def test_xfmr_block_gradients_match_torch(cuda_device):
+    """Gradients of one XFMR block (attention backward kernel + torch GEMM backward) against autograd of an fp32
+    torch restatement of the block."""
+    from flash3dtransformer_b200 import layers
+    from flash3dtransformer_b200.psh import bucket_scope
+    torch.manual_seed(3)
+    c, heads, bucket, k = 64, 2, 256, 2
+    n = bucket * k * 2
+    blk = layers.XFMR(c, 4 * c, heads, bucket, True, bucket_scope.SwinPlan("swin", bucket, k, 0), torch.nn.LayerNorm).to(cuda_device)
+    x = torch.randn(n, c, device=cuda_device).bfloat16().requires_grad_(True)
+    g = torch.randn(n, c, device=cuda_device).bfloat16()
+    blk(None, x, None).backward(g)
+    got_x = x.grad.float()
+    got_w = blk.bwa.qkv.weight.grad.float().clone()
+    blk.zero_grad()
+    xf = x.detach().float().requires_grad_(True)
+    h = torch.nn.functional.layer_norm(xf, (c,), blk.norm.weight, blk.norm.bias)
+    qkv = h @ blk.bwa.qkv.weight.t() + blk.bwa.qkv.bias
+    q, kk, v = (t.view(n // (bucket * k), bucket * k, heads, c // heads).transpose(1, 2) for t in qkv.chunk(3, -1))
+    a = torch.nn.functional.scaled_dot_product_attention(q, kk, v).transpose(1, 2).reshape(n, c)
+    mid = a @ blk.bwa.proj.weight.t() + blk.bwa.proj.bias + xf
+    m = blk.mlp.mlp
+    h2 = torch.nn.functional.layer_norm(mid, (c,), m.layer_norm_weight, m.layer_norm_bias)
+    y = h2 @ m.fc1_weight.t() + m.fc1_bias
+    f = y.shape[1] // 2
+    out = (torch.nn.functional.silu(y[:, :f]) * y[:, f:]) @ m.fc2_weight.t() + m.fc2_bias + mid
+    out.backward(g.float())
+    for name, got, ref in (("x", got_x, xf.grad), ("qkv.weight", got_w, blk.bwa.qkv.weight.grad.float())):
+        err = (got - ref).abs()
+        assert err.max().item() <= 0.05 * ref.abs().max().item() + 1e-3, (name, err.max().item(), ref.abs().max().item())
+        assert (err.mean() / ref.abs().mean()).item() <= 2e-2, (name, (err.mean() / ref.abs().mean()).item())
