@@ -249,18 +249,13 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     seps_dev = host_seps.to(dev)
     batching.host_seps(seps_dev)
 
-    def global_bbox(c):
-        lo, hi = torch.aminmax(c, dim=0)
-        if world > 1:
-            lo32, hi32 = lo.float(), hi.float()
-            dist.all_reduce(lo32, op=dist.ReduceOp.MIN)
-            dist.all_reduce(hi32, op=dist.ReduceOp.MAX)
-            lo, hi = lo32.half(), hi32.half()
-        return lo, hi
+    from flash3dtransformer_b200 import parallel
 
     def step(c, s):
+        # bounding box + mean scene size over all ranks' scenes (three tiny all-reduces when world > 1)
+        bbox, mean_n = parallel.global_psh_stats(c, s)
         with torch.no_grad():
-            return model(c, None, s, bbox=global_bbox(c))
+            return model(c, None, s, bbox=bbox, mean_n=mean_n, scene_base=rank * args.scenes)
 
     timer = FamilyTimer(pshattn)
     timer.install()

@@ -14,6 +14,9 @@ static thread_local char g_err[512] = "";
 static std::atomic<int> g_sync{0};
 static std::atomic<uint64_t> g_seed{3407ull};
 static std::atomic<unsigned long long> g_launches{0ull};
+static std::atomic<uint32_t> g_scene_base{0u};
+
+uint32_t scene_base() { return g_scene_base.load(); }
 
 void count_launches(int n) { g_launches.fetch_add((unsigned long long)n); }
 
@@ -97,6 +100,10 @@ int f3d_get_sync(void) { return f3d::g_sync.load(); }
 int f3d_set_seed(uint64_t seed) { f3d::g_seed.store(seed); return F3D_OK; }
 
 uint64_t f3d_get_seed(void) { return f3d::g_seed.load(); }
+
+int f3d_set_scene_base(uint32_t base) { f3d::g_scene_base.store(base); return F3D_OK; }
+
+uint32_t f3d_get_scene_base(void) { return f3d::g_scene_base.load(); }
 
 int f3d_init_device(int device) {
   int n = 0;

@@ -36,6 +36,7 @@
 namespace f3d {
 
 uint64_t seed();
+uint32_t scene_base();
 
 constexpr int kPshThreads = 256;
 constexpr int kPshWarps = kPshThreads / 32;
@@ -51,6 +52,7 @@ struct PshArgs {
   uint32_t tile, tiles_max;
   uint16_t pad_bits; uint16_t coord_aligned;
   RngKey key;
+  uint32_t scene_base;     // added to the scene index in the random-number counter (global scene id of a shard)
   // scratch
   uint32_t *tabP, *tabQ;           // [batch*tiles_max][nbp] tile histograms / tile prefixes
   uint32_t *count0, *kept, *freeB, *rejpre, *cntB, *cntF;   // [batch][nbp]
@@ -410,7 +412,7 @@ __global__ void __launch_bounds__(kPshThreads) psh_rankA_kernel(PshArgs a) {
         uint32_t pt = t.t0 + g + k;
         uint32_t target = a.nb;                       // "no admissible probe" column
         for (uint32_t p = 0; p < kNumProbes; ++p) {
-          psh_rand(a.key, t.scene, pt, p, r);
+          psh_rand(a.key, t.scene + a.scene_base, pt, p, r);
           perturb_vox(r, a.num_vox, a.divisor, a.probe + 3u * p, vox, nvox);
           uint32_t c = first_hash(a.hash_type, nvox[0], nvox[1], nvox[2], a.divisor, a.nb);
           if (c != init && c != kRecycleBucket && s.aux[c] < a.cap) { target = c; break; }
@@ -503,13 +505,13 @@ __global__ void __launch_bounds__(kPshThreads) psh_resolveB_kernel(PshArgs a) {
       uint32_t vox[3], nvox[3], r[4];
 #pragma unroll
       for (int d = 0; d < 3; ++d) vox[d] = vox_axis(__half2float(a.coord[(size_t)gi * 3 + d]), lo[d], hi[d], a.num_vox);
-      psh_rand(a.key, t.scene, pt, 128u, r);
+      psh_rand(a.key, t.scene + a.scene_base, pt, 128u, r);
       uint32_t p = r[0] % kNumProbes;
-      psh_rand(a.key, t.scene, pt, 129u, r);
+      psh_rand(a.key, t.scene + a.scene_base, pt, 129u, r);
       perturb_vox(r, a.num_vox, a.divisor, a.probe + 3u * p, vox, nvox);
       uint32_t c = first_hash(a.hash_type, nvox[0], nvox[1], nvox[2], a.divisor, a.nb);
       if (c == kRecycleBucket) {
-        psh_rand(a.key, t.scene, pt, 130u, r);
+        psh_rand(a.key, t.scene + a.scene_base, pt, 130u, r);
         c = 1u + r[0] % (a.nb - 1u);
       }
       a.bucket_id[gi] = (uint16_t)c;
@@ -721,6 +723,7 @@ extern "C" int f3d_batch_psh_scatter_pad_hash(
   a.coord_aligned = (reinterpret_cast<uintptr_t>(coord) % 16 == 0) ? 1 : 0;
   uint64_t sd = f3d::seed();
   a.key.k0 = (uint32_t)sd; a.key.k1 = (uint32_t)(sd >> 32);
+  a.scene_base = f3d::scene_base();
   F3D_TRY(maybe_sync(st, "batch_psh_scatter_pad_hash"));
   F3D_TRY(psh_run(a, p, static_cast<uint32_t *>(scratch), instance_max_N, st));
   return maybe_sync(st, "batch_psh_scatter_pad_hash");
@@ -794,5 +797,6 @@ extern "C" int f3d_batch_psh_scatter_pad_hash_noalloc(
   a.coord_aligned = (reinterpret_cast<uintptr_t>(coord) % 16 == 0) ? 1 : 0;
   uint64_t sd = f3d::seed();
   a.key.k0 = (uint32_t)sd; a.key.k1 = (uint32_t)(sd >> 32);
+  a.scene_base = f3d::scene_base();
   return psh_run(a, p, scratch, instance_max_N, st);
 }

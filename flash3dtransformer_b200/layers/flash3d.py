@@ -75,13 +75,16 @@ class Flash3D(nn.Module):
         return f3dstage.Stage(encoder_specs=spec.encoder_specs, buck_size=self.buck_size, submodule=sub,
                               decoder_specs=spec.decoder_specs)
 
-    def forward(self, coords: torch.Tensor, input_feat: torch.Tensor, seps: torch.Tensor, bbox=None) -> torch.Tensor:
+    def forward(self, coords: torch.Tensor, input_feat: torch.Tensor, seps: torch.Tensor, bbox=None,
+                mean_n=None, scene_base=None) -> torch.Tensor:
         """coords fp16 [N, 3], seps uint32 [B] -> features [pad_to, C] in bucket-sorted order.  As in the reference
         (flash3d.py:162-163), input_feat is accepted and not read, and the unscattered coords travel down the tree
-        next to the scattered features."""
+        next to the scattered features.  `bbox` / `mean_n` (not in the reference) carry the bounding box and mean scene
+        size of the global batch in a scene-sharded run (parallel.global_psh_stats), `scene_base` the global index of the
+        shard's first scene."""
         if f3ddev.get_nvtx():
             nvtx.range_push(self.NVTX_SCOPE)
-        psh_feat = self.psh_scatter(coords, seps, self.first_hashtype, bbox=bbox)
+        psh_feat = self.psh_scatter(coords, seps, self.first_hashtype, bbox=bbox, mean_n=mean_n, scene_base=scene_base)
         out = self.module_tree(coords, psh_feat, seps)
         if f3ddev.get_nvtx():
             nvtx.range_pop()

@@ -31,9 +31,10 @@ class PSH3DCoordEmbedding(nn.Module):
         self.feat_dtype = feat_dtype
         self.lin = nn.Linear(3, emb_dim)
 
-    def forward(self, coords, seps, hash_op, bbox=None):
+    def forward(self, coords, seps, hash_op, bbox=None, mean_n=None, scene_base=None):
         pad_to = f3darith.cdiv(coords.shape[0], self.alignment) * self.alignment
-        scattered, _ = pm.batch_bucket_scatter(coords, seps, self.bucket_size, pad_to, hash_op, bbox=bbox)
+        scattered, _ = pm.batch_bucket_scatter(coords, seps, self.bucket_size, pad_to, hash_op, bbox=bbox, mean_n=mean_n,
+                                                scene_base=scene_base)
         # K = 3 is below the tensor-core GEMM's 8-element granularity: three FMAs per output, left to torch
         return torch.nn.functional.linear(scattered.to(self.feat_dtype), self.lin.weight.to(self.feat_dtype),
                                           self.lin.bias.to(self.feat_dtype))

@@ -22,6 +22,8 @@ PROTOTYPES = {
     "f3d_get_sync": (_int, []),
     "f3d_set_seed": (_int, [c_uint64]),
     "f3d_get_seed": (c_uint64, []),
+    "f3d_set_scene_base": (_int, [_u32]),
+    "f3d_get_scene_base": (_u32, []),
     "f3d_release_workspaces": (_int, []),
     "f3d_launch_count": (ctypes.c_ulonglong, []),
     "f3d_batch_psh_scatter_pad_hash": (_int, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _u32, _u32,

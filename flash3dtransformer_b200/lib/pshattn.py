@@ -96,6 +96,13 @@ class DeviceManagerSingleton:
     def get_seed(self) -> int:
         return int(_cabi.load().f3d_get_seed())
 
+    def set_scene_base(self, base: int) -> None:
+        """Global index of this process's first scene (scene-sharded runs); enters the PSH random-number counter."""
+        _cabi.check(_cabi.load().f3d_set_scene_base(int(base)), "set_scene_base")
+
+    def get_scene_base(self) -> int:
+        return int(_cabi.load().f3d_get_scene_base())
+
 
 # ----------------------------------------------------------------------------------------------- PSH scatter
 def batch_psh_scatter_pad_hash(coord, bucket_id, bucket_counter, bucket_offset, batch_sep, instance_max_N,

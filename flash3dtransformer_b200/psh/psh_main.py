@@ -24,11 +24,13 @@ from ..lib import pshattn
 NUM_VOX = 0xFFFF
 
 
-def bucket_plan(seps: torch.Tensor, bucket_size: int):
-    """(mean scene size, largest scene, num_buck, divisor) as psh_main.py:97-104 computes them."""
+def bucket_plan(seps: torch.Tensor, bucket_size: int, mean_n=None):
+    """(mean scene size, largest scene, num_buck, divisor) as psh_main.py:97-104 computes them.  `mean_n` overrides
+    the local mean scene size (a scene-sharded run passes the mean over all ranks' scenes)."""
     sizes = f3dbatch.sep2sizes(f3dbatch.host_seps(seps))
-    mean_n = float(sizes.to(torch.float32).mean())
-    max_n = int(sizes.max())
+    if mean_n is None:
+        mean_n = float(sizes.to(torch.float32).mean()) if sizes.numel() else 0.0
+    max_n = int(sizes.max()) if sizes.numel() else 0
     num_buck = max(1, f3darith.round_next_two_power(int(mean_n / bucket_size)))
     divisor = int(math.ceil(NUM_VOX / num_buck))
     return mean_n, max_n, num_buck, divisor
@@ -64,7 +66,7 @@ class BucketScatterBuffers:
 
 
 def batch_bucket_scatter(coords: torch.Tensor, seps: torch.Tensor, bucket_size: int, pad_to: int, hash_op: int,
-                         bbox=None) -> Tuple[torch.Tensor, BucketScatterBuffers]:
+                         bbox=None, mean_n=None, scene_base=None) -> Tuple[torch.Tensor, BucketScatterBuffers]:
     """Bucket and scatter a flat batch of fp16 coordinates.
 
     hash_op: 1 Z-order div, 2 XOR-sum div, 3 Z-order mod, 4 XOR-sum mod.
@@ -74,12 +76,14 @@ def batch_bucket_scatter(coords: torch.Tensor, seps: torch.Tensor, bucket_size: 
     Returns (scattered_coord, buffers).
     """
     f3ddev.init_dev(coords.get_device())
-    _, max_n, num_buck, divisor = bucket_plan(seps, bucket_size)
+    _, max_n, num_buck, divisor = bucket_plan(seps, bucket_size, mean_n)
     buffers = BucketScatterBuffers.create_buffers(coords, seps, bucket_size, pad_to, num_buck)
     if bbox is None:
         bbox_min, bbox_max = torch.aminmax(coords, dim=0)
     else:
         bbox_min, bbox_max = bbox
+    if scene_base is not None:
+        f3ddev.get_dev_manager().set_scene_base(scene_base)
     pshattn.batch_psh_scatter_pad_hash(
         coords, buffers.bucket_id, buffers.bucket_cntr, buffers.bucket_offs, seps, max_n, num_buck, divisor,
         bucket_size, NUM_VOX, bbox_min.contiguous(), bbox_max.contiguous(), buffers.probe_offs,

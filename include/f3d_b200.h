@@ -44,6 +44,10 @@ int f3d_get_sync(void);
  * (src/common/device_manager.cu:58-67, seed 3407) */
 int f3d_set_seed(uint64_t seed);
 uint64_t f3d_get_seed(void);
+/* index of the calling process's first scene inside the global batch (default 0).  It is added to the scene index in
+ * the random-number counter of the PSH rebalance, so that a scene-sharded run reproduces the single-process layout. */
+int f3d_set_scene_base(uint32_t base);
+uint32_t f3d_get_scene_base(void);
 /* number of CUDA kernels this library has launched since it was loaded (benchmark bookkeeping) */
 unsigned long long f3d_launch_count(void);
 /* frees the library's cached scratch buffers on every device */

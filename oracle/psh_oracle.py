@@ -240,8 +240,8 @@ def psh_scene(coord_f16, bbox_min, bbox_max, probe, scene: int, num_bucket: int,
 
 def psh_scatter(coord_f16: np.ndarray, seps, num_bucket: int, divisor: int, cap: int, num_vox: int,
                 bbox_min, bbox_max, probe: np.ndarray, pad_to: int, pad_num: float, hash_type: int,
-                seed: int = 3407):
-    """Whole operator: returns dict(bucket_id u16 [N], bucket_offs u32 [N], bucket_cntr u32 [B,NB],
+                seed: int = 3407, scene_base: int = 0):
+    """Whole operator (scene_base: global index of the first scene, for scene-sharded runs): returns dict(bucket_id u16 [N], bucket_offs u32 [N], bucket_cntr u32 [B,NB],
     bucket_cumsum u32 [B,NB], scattered_coord f16 [pad_to,3]) as batch_psh_scatter_pad_hash fills them
     (src/psh/batch_psh_bucket_dispatcher.cu:221-326)."""
     seps = np.asarray(seps, dtype=np.int64)
@@ -259,7 +259,7 @@ def psh_scatter(coord_f16: np.ndarray, seps, num_bucket: int, divisor: int, cap:
     for s in range(bsz):
         end = int(min(seps[s], n_total))
         if end > start:
-            bid, off, final = psh_scene(coord_f16[start:end], bbox_min, bbox_max, probe, s, num_bucket, divisor,
+            bid, off, final = psh_scene(coord_f16[start:end], bbox_min, bbox_max, probe, s + scene_base, num_bucket, divisor,
                                         cap, num_vox, hash_type, seed)
             bucket_id[start:end] = bid
             bucket_offs[start:end] = off

@@ -145,3 +145,25 @@ def test_full_size_properties(cuda_device):
     _, _, again = _gpu_scatter(cuda_device, c16, seps, 512, 2, pad_to)
     _compare(out, again)
     _compare(out, _oracle(c16, seps, nb, div, 512, 2, pad_to))
+
+
+def test_scene_sharded_run_reproduces_full_batch(cuda_device):
+    """Two 'ranks' (run one after the other on this GPU) that get the global bounding box, mean scene size and the
+    global index of their first scene produce, scene by scene, the bits of the unsharded run."""
+    from flash3dtransformer_b200 import parallel
+    from flash3dtransformer_b200.psh import psh_main
+    sizes = [9000, 7000, 11000, 5000, 6000]
+    coords32, seps = synthetic.batch(synthetic.lidar_scan, sizes, seed=21)
+    coords = torch.from_numpy(coords32.astype(np.float16)).to(cuda_device)
+    seps_t = torch.from_numpy(seps.astype(np.uint32)).to(cuda_device)
+    n = coords.shape[0]
+    _, full = psh_main.batch_bucket_scatter(coords, seps_t, 256, n, 2)
+    (lo, hi), mean_n = parallel.global_psh_stats(coords, seps_t)
+    for rank in range(2):
+        local, lseps, (r0, r1), scene0 = parallel.shard_batch(coords, seps_t, rank, 2)
+        _, mine = psh_main.batch_bucket_scatter(local, lseps, 256, local.shape[0], 2, bbox=(lo, hi), mean_n=mean_n,
+                                                scene_base=scene0)
+        assert torch.equal(mine.bucket_id, full.bucket_id[r0:r1])
+        assert torch.equal(mine.bucket_offs.view(torch.int32), full.bucket_offs[r0:r1].view(torch.int32))
+        assert torch.equal(mine.scattered_coord.view(torch.int16), full.scattered_coord[r0:r1].view(torch.int16))
+    psh_main.f3ddev.get_dev_manager().set_scene_base(0)
