@@ -51,6 +51,24 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return m;
 }
 
+// packed fp32 pairs (Blackwell executes fma / add on two fp32 values per instruction)
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float &lo, float &hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
 template <int D> struct AttnCfg {
   static constexpr int DCH = D < 64 ? D : 64;       // columns per swizzled row
   static constexpr int NDCH = D / DCH;
@@ -185,29 +203,34 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       for (int i = 0; i < 32; ++i) mx = max3(mx, __uint_as_float(r0[i]), __uint_as_float(r1[i]));
       const float m_new = fmaxf(m_run, mx * a.scale_log2);
       const float alpha = fast_exp2(m_run - m_new);                 // 0 on the first tile (m_run = -inf)
-      float sum = 0.f;
+      // x = s * c - m and the row sum run on packed fp32 pairs; the sum adds the unrounded probabilities (the
+      // bf16 rounding of P is unbiased, so the normaliser stays consistent with what the MMA reads)
+      const uint64_t c2 = pack2(a.scale_log2, a.scale_log2), m2 = pack2(-m_new, -m_new);
+      uint64_t sum2 = pack2(0.f, 0.f);
       uint32_t p[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        float e0 = fast_exp2(fmaf(__uint_as_float(r0[2 * i]), a.scale_log2, -m_new));
-        float e1 = fast_exp2(fmaf(__uint_as_float(r0[2 * i + 1]), a.scale_log2, -m_new));
+        float x0, x1;
+        unpack2(fma2(pack2(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1])), c2, m2), x0, x1);
+        const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
+        sum2 = add2(sum2, pack2(e0, e1));
         __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
-        // the sum uses the rounded probabilities so that O / l is the exact normalisation of what the MMA sees
-        float2 f = __bfloat1622float2(h);
-        sum += f.x + f.y;
         p[i] = *reinterpret_cast<uint32_t *>(&h);
       }
       tc::tmem_st_32x32b_x16(s_tmem, p);
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        float e0 = fast_exp2(fmaf(__uint_as_float(r1[2 * i]), a.scale_log2, -m_new));
-        float e1 = fast_exp2(fmaf(__uint_as_float(r1[2 * i + 1]), a.scale_log2, -m_new));
+        float x0, x1;
+        unpack2(fma2(pack2(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1])), c2, m2), x0, x1);
+        const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
+        sum2 = add2(sum2, pack2(e0, e1));
         __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
-        float2 f = __bfloat1622float2(h);
-        sum += f.x + f.y;
         p[i] = *reinterpret_cast<uint32_t *>(&h);
       }
       tc::tmem_st_32x32b_x16(s_tmem + 16, p);
+      float sum, sum_hi;
+      unpack2(sum2, sum, sum_hi);
+      sum += sum_hi;
       l_run = l_run * alpha + sum;
       m_run = m_new;
       if (j > 0) {
