@@ -54,8 +54,8 @@ struct PshArgs {
   RngKey key;
   uint32_t scene_base;     // added to the scene index in the random-number counter (global scene id of a shard)
   // scratch
-  uint32_t *tabP, *tabQ;           // [batch*tiles_max][nbp] tile histograms / tile prefixes
-  uint32_t *count0, *kept, *freeB, *rejpre, *cntB, *cntF;   // [batch][nbp]
+  uint32_t *tabA, *tabB, *tabC;    // [batch*tiles_max][nbp] tile histograms of rounds A, B, C (raw counts)
+  uint32_t *count0, *kept, *cntB;  // [batch][nbp] per-scene totals published by the tile-0 CTA of each round
   uint32_t *tile_pending, *tile_movers;                     // [batch*tiles_max]
 };
 
@@ -66,6 +66,8 @@ struct TileSmem {
   uint16_t *whist;     // [kPshWarps][nbp]   per-warp counts, then per-warp running ranks (tile-relative)
   uint32_t *tbase;     // [nbp]              rank of the tile's first element of each key
   uint32_t *aux;       // [nbp]              block histogram of the next round / cached per-scene table
+  uint32_t *aux2;      // [nbp]              second cached per-scene table
+  uint32_t *aux3;      // [nbp]              third cached per-scene table
   uint16_t *keys;      // [tile]             key cache between the counting and the ranking sweep
 };
 
@@ -73,7 +75,7 @@ __host__ __device__ inline size_t tile_smem_bytes(uint32_t nbp, uint32_t tile) {
   size_t b = 0;
   b += (size_t)kPshWarps * kStageHalves * 2;
   b += ((size_t)kPshWarps * nbp * 2 + 15) / 16 * 16;
-  b += (size_t)nbp * 4 * 2;
+  b += (size_t)nbp * 4 * 4;
   b += (size_t)tile * 2;
   return b + 64;
 }
@@ -87,6 +89,10 @@ __device__ __forceinline__ TileSmem carve(unsigned char *base, uint32_t nbp, uin
   s.tbase = reinterpret_cast<uint32_t *>(base);
   base += (size_t)nbp * 4;
   s.aux = reinterpret_cast<uint32_t *>(base);
+  base += (size_t)nbp * 4;
+  s.aux2 = reinterpret_cast<uint32_t *>(base);
+  base += (size_t)nbp * 4;
+  s.aux3 = reinterpret_cast<uint32_t *>(base);
   base += (size_t)nbp * 4;
   s.keys = reinterpret_cast<uint16_t *>(base);
   return s;
@@ -171,8 +177,8 @@ __device__ __forceinline__ void zero_whist(const TileSmem &s, uint32_t nbp) {
   for (uint32_t i = threadIdx.x; i < kPshWarps * nbp; i += kPshThreads) s.whist[i] = 0;
 }
 
-// per-warp counts -> per-warp exclusive prefix (tile-relative); tbase[key] = row[key] (+ add[key])
-__device__ __forceinline__ void warp_prefix(const TileSmem &s, uint32_t nbp, const uint32_t *row, const uint32_t *add) {
+// per-warp counts -> per-warp exclusive prefix (tile-relative)
+__device__ __forceinline__ void warp_prefix(const TileSmem &s, uint32_t nbp) {
   for (uint32_t b = threadIdx.x; b < nbp; b += kPshThreads) {
     uint32_t run = 0;
 #pragma unroll
@@ -181,8 +187,24 @@ __device__ __forceinline__ void warp_prefix(const TileSmem &s, uint32_t nbp, con
       s.whist[w * nbp + b] = (uint16_t)run;
       run += c;
     }
-    s.tbase[b] = row[b] + (add ? add[b] : 0u);
   }
+}
+
+// Column `col` of a scene's raw tile table: sum over the tiles before `my_tile` and over all tiles.  Every CTA of
+// a round recomputes these sums from the table (tiles <= 64 per scene by construction, all L2 hits) instead of
+// waiting for a separate scan launch.
+__device__ __forceinline__ void column_sums(const uint32_t *tab, uint32_t tiles, uint32_t nbp, uint32_t col, uint32_t my_tile,
+                                            uint32_t &prefix, uint32_t &total) {
+  uint32_t pre = 0, tot = 0, t = 0;
+  for (; t + 8 <= tiles; t += 8) {
+    uint32_t v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = __ldg(tab + (size_t)(t + j) * nbp + col);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { tot += v[j]; if (t + j < my_tile) pre += v[j]; }
+  }
+  for (; t < tiles; ++t) { uint32_t v = __ldg(tab + (size_t)t * nbp + col); tot += v; if (t < my_tile) pre += v; }
+  prefix = pre; total = tot;
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -217,26 +239,11 @@ __global__ void __launch_bounds__(kPshThreads) psh_hist_kernel(PshArgs a) {
     }
   }
   __syncthreads();
-  uint32_t *row = a.tabP + (size_t)t.row * a.nbp;
+  uint32_t *row = a.tabA + (size_t)t.row * a.nbp;
   for (uint32_t b = threadIdx.x; b < a.nbp; b += kPshThreads) row[b] = s.aux[b];
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// per-scene scans (one CTA per scene).  Column scan over tiles: table[tile][col] -> exclusive prefix.
-__device__ __forceinline__ uint32_t column_scan(uint32_t *tab, uint32_t tiles, uint32_t nbp, uint32_t col) {
-  uint32_t run = 0;
-  uint32_t t = 0;
-  for (; t + 8 <= tiles; t += 8) {
-    uint32_t v[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] = tab[(size_t)(t + j) * nbp + col];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) { tab[(size_t)(t + j) * nbp + col] = run; run += v[j]; }
-  }
-  for (; t < tiles; ++t) { uint32_t v = tab[(size_t)t * nbp + col]; tab[(size_t)t * nbp + col] = run; run += v; }
-  return run;
-}
-
 // block-wide exclusive scan of one value per thread (kPshThreads threads); returns exclusive prefix, total in *tot
 __device__ __forceinline__ uint32_t block_excl_scan(uint32_t v, uint32_t *wsum /*[kPshWarps+1]*/, uint32_t *tot) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -267,75 +274,6 @@ __device__ __forceinline__ uint32_t scene_tiles(const PshArgs &a, uint32_t scene
   return (n + a.tile - 1) / a.tile;
 }
 
-// K2: round A totals
-__global__ void __launch_bounds__(kPshThreads) psh_scanA_kernel(PshArgs a) {
-  const uint32_t scene = blockIdx.x;
-  const uint32_t tiles = scene_tiles(a, scene);
-  uint32_t *tab = a.tabP + (size_t)scene * a.tiles_max * a.nbp;
-  for (uint32_t b = threadIdx.x; b < a.nbp; b += kPshThreads) {
-    uint32_t tot = column_scan(tab, tiles, a.nbp, b);
-    a.count0[scene * a.nbp + b] = tot;
-    a.kept[scene * a.nbp + b] = (b == kRecycleBucket) ? tot : min(tot, a.cap);
-  }
-}
-
-// K4: round B totals -> free capacity, rejected prefix, counts after round B
-__global__ void __launch_bounds__(kPshThreads) psh_scanB_kernel(PshArgs a) {
-  __shared__ uint32_t wsum[kPshWarps + 1];
-  const uint32_t scene = blockIdx.x;
-  const uint32_t tiles = scene_tiles(a, scene);
-  uint32_t *tab = a.tabQ + (size_t)scene * a.tiles_max * a.nbp;
-  const uint32_t so = scene * a.nbp;
-  uint32_t carry = 0;
-  for (uint32_t b0 = 0; b0 < a.nbp; b0 += kPshThreads) {
-    uint32_t b = b0 + threadIdx.x;
-    uint32_t rej = 0;
-    if (b < a.nbp) {
-      uint32_t att = column_scan(tab, tiles, a.nbp, b);
-      uint32_t kept = a.kept[so + b];
-      uint32_t fr = (b != kRecycleBucket && b < a.nb && kept < a.cap) ? a.cap - kept : 0u;
-      uint32_t acc = min(att, fr);
-      rej = att - acc;
-      a.freeB[so + b] = fr;
-      a.cntB[so + b] = kept + acc;      // bucket 0 is fixed up below
-    }
-    uint32_t tot;
-    uint32_t ex = block_excl_scan(rej, wsum, &tot);
-    if (b < a.nbp) a.rejpre[so + b] = carry + ex;
-    carry += tot;
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) a.cntB[so + kRecycleBucket] = a.count0[so + kRecycleBucket] + carry;
-}
-
-// K6: round C totals -> final counts and inclusive cumsum
-__global__ void __launch_bounds__(kPshThreads) psh_scanC_kernel(PshArgs a) {
-  __shared__ uint32_t wsum[kPshWarps + 1];
-  const uint32_t scene = blockIdx.x;
-  const uint32_t tiles = scene_tiles(a, scene);
-  uint32_t *tab = a.tabP + (size_t)scene * a.tiles_max * a.nbp;
-  const uint32_t so = scene * a.nbp;
-  uint32_t carry = 0;
-  for (uint32_t b0 = 0; b0 < a.nbp; b0 += kPshThreads) {
-    uint32_t b = b0 + threadIdx.x;
-    uint32_t fin = 0;
-    if (b < a.nbp) {
-      uint32_t mv = column_scan(tab, tiles, a.nbp, b);
-      uint32_t cb = a.cntB[so + b];
-      if (b == kRecycleBucket) fin = (a.nb > 1) ? min(cb, a.cap) : cb;
-      else if (b < a.nb) fin = cb + mv;
-      a.cntF[so + b] = fin;
-    }
-    uint32_t tot;
-    uint32_t ex = block_excl_scan(fin, wsum, &tot);
-    if (b < a.nb) {
-      a.bucket_counter[scene * a.nb + b] = fin;
-      a.cumsum_counter[scene * a.nb + b] = carry + ex + fin;
-    }
-    carry += tot;
-  }
-}
-
 // ---------------------------------------------------------------------------------------------------------
 // K3: round A ranks, overflow detection, probe walk, round B histogram
 __global__ void __launch_bounds__(kPshThreads) psh_rankA_kernel(PshArgs a) {
@@ -350,6 +288,7 @@ __global__ void __launch_bounds__(kPshThreads) psh_rankA_kernel(PshArgs a) {
   __syncthreads();
   float lo[3], hi[3];
   load_bbox(a, lo, hi);
+  const float ratio = probe_ratio(a.num_vox, a.divisor);
   const uint32_t wt = a.tile / kPshWarps;
   const uint32_t w0 = warp * wt, w1 = min(w0 + wt, t.cnt);
   uint16_t *st = s.stage + warp * kStageHalves;
@@ -372,13 +311,25 @@ __global__ void __launch_bounds__(kPshThreads) psh_rankA_kernel(PshArgs a) {
     }
   }
   __syncthreads();
-  warp_prefix(s, a.nbp, a.tabP + (size_t)t.row * a.nbp, nullptr);
+  warp_prefix(s, a.nbp);
+  // rank base of this tile and the scene's kept counts, from the round A table
   const uint32_t so = t.scene * a.nbp;
-  for (uint32_t b = threadIdx.x; b < a.nbp; b += kPshThreads) s.aux[b] = a.kept[so + b];
+  {
+    const uint32_t tiles = scene_tiles(a, t.scene);
+    const uint32_t *tab = a.tabA + (size_t)t.scene * a.tiles_max * a.nbp;
+    for (uint32_t b = threadIdx.x; b < a.nbp; b += kPshThreads) {
+      uint32_t pre, tot;
+      column_sums(tab, tiles, a.nbp, b, t.tile, pre, tot);
+      const uint32_t kept = (b == kRecycleBucket) ? tot : min(tot, a.cap);
+      s.tbase[b] = pre;
+      s.aux[b] = kept;
+      if (t.tile == 0) { a.count0[so + b] = tot; a.kept[so + b] = kept; }
+    }
+  }
   __syncthreads();
   // sweep 2: ranks; overflowing points choose their attempt bucket and are counted into the round B table,
   // whose row is accumulated with global atomics (rare path) after being zeroed by the host memset.
-  uint32_t *rowB = a.tabQ + (size_t)t.row * a.nbp;
+  uint32_t *rowB = a.tabB + (size_t)t.row * a.nbp;
   uint32_t my_pending = 0;
   for (uint32_t g = w0; g < w1; g += kGroup) {
     uint32_t gc = min(kGroup, w1 - g);
@@ -411,9 +362,11 @@ __global__ void __launch_bounds__(kPshThreads) psh_rankA_kernel(PshArgs a) {
         load_vox(a, st, skew, k, lo, hi, vox);
         uint32_t pt = t.t0 + g + k;
         uint32_t target = a.nb;                       // "no admissible probe" column
+        ProbeStream ps;
+        probe_stream_init(a.key, t.scene + a.scene_base, pt, ps);
         for (uint32_t p = 0; p < kNumProbes; ++p) {
-          psh_rand(a.key, t.scene + a.scene_base, pt, p, r);
-          perturb_vox(r, a.num_vox, a.divisor, a.probe + 3u * p, vox, nvox);
+          probe_stream_next(ps, r);
+          perturb_vox(r, a.num_vox, ratio, a.probe + 3u * p, vox, nvox);
           uint32_t c = first_hash(a.hash_type, nvox[0], nvox[1], nvox[2], a.divisor, a.nb);
           if (c != init && c != kRecycleBucket && s.aux[c] < a.cap) { target = c; break; }
         }
@@ -435,14 +388,48 @@ __global__ void __launch_bounds__(kPshThreads) psh_rankA_kernel(PshArgs a) {
 __global__ void __launch_bounds__(kPshThreads) psh_resolveB_kernel(PshArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ uint32_t mover_cnt;
+  __shared__ uint32_t wsum[kPshWarps + 1];
   TileSmem s = carve(smem_raw, a.nbp, a.tile);
   TileInfo t = tile_info(a);
   if (!t.live) return;
-  if (a.tile_pending[t.row] == 0) {
+  const bool pending = a.tile_pending[t.row] != 0;
+  if (!pending && t.tile != 0) {
     if (threadIdx.x == 0) a.tile_movers[t.row] = 0;
-    return;                       // the round C row stays zero (host memset)
+    return;                       // this tile's round C row stays zero (host memset)
   }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t so = t.scene * a.nbp;
+  // Round B totals of the scene from the attempt table: rank base of this tile (tbase), free capacity (aux),
+  // kept count (aux2), recycle offset of the first rejected attempt per bucket (aux3).  The tile-0 CTA also
+  // publishes the bucket counts after round B.
+  {
+    const uint32_t tiles = scene_tiles(a, t.scene);
+    const uint32_t *tab = a.tabB + (size_t)t.scene * a.tiles_max * a.nbp;
+    uint32_t carry = 0;
+    for (uint32_t b0 = 0; b0 < a.nbp; b0 += kPshThreads) {
+      const uint32_t b = b0 + threadIdx.x;
+      uint32_t rej = 0;
+      if (b < a.nbp) {
+        uint32_t pre, att;
+        column_sums(tab, tiles, a.nbp, b, t.tile, pre, att);
+        const uint32_t kept = a.kept[so + b];
+        const uint32_t fr = (b != kRecycleBucket && b < a.nb && kept < a.cap) ? a.cap - kept : 0u;
+        const uint32_t acc = min(att, fr);
+        rej = att - acc;
+        s.tbase[b] = pre; s.aux[b] = fr; s.aux2[b] = kept;
+        if (t.tile == 0 && b != kRecycleBucket) a.cntB[so + b] = kept + acc;
+      }
+      uint32_t tot;
+      const uint32_t ex = block_excl_scan(rej, wsum, &tot);
+      if (b < a.nbp) s.aux3[b] = carry + ex;
+      carry += tot;
+    }
+    if (t.tile == 0 && threadIdx.x == 0) a.cntB[so + kRecycleBucket] = a.count0[so + kRecycleBucket] + carry;
+  }
+  if (!pending) {
+    if (threadIdx.x == 0) a.tile_movers[t.row] = 0;
+    return;
+  }
   zero_whist(s, a.nbp);
   if (threadIdx.x == 0) mover_cnt = 0;
   __syncthreads();
@@ -464,12 +451,12 @@ __global__ void __launch_bounds__(kPshThreads) psh_resolveB_kernel(PshArgs a) {
     warp_count(wh, key, valid, lane);
   }
   __syncthreads();
-  warp_prefix(s, a.nbp, a.tabQ + (size_t)t.row * a.nbp, nullptr);
+  warp_prefix(s, a.nbp);
   __syncthreads();
   float lo[3], hi[3];
   load_bbox(a, lo, hi);
-  const uint32_t so = t.scene * a.nbp;
-  uint32_t *rowC = a.tabP + (size_t)t.row * a.nbp;
+  const float ratio = probe_ratio(a.num_vox, a.divisor);
+  uint32_t *rowC = a.tabC + (size_t)t.row * a.nbp;
   const uint32_t count0_recycle = a.count0[so + kRecycleBucket];
   uint32_t my_movers = 0;
   for (uint32_t it = w0; it < w1; it += 32) {
@@ -483,12 +470,12 @@ __global__ void __launch_bounds__(kPshThreads) psh_resolveB_kernel(PshArgs a) {
     bool mover = false;
     uint32_t recycle_off = 0;
     if (valid) {
-      uint32_t fr = a.freeB[so + kk];
+      uint32_t fr = s.aux[kk];
       if (q < fr) {
         a.bucket_id[gi] = (uint16_t)kk;
-        a.bucket_offset[gi] = a.kept[so + kk] + q;
+        a.bucket_offset[gi] = s.aux2[kk] + q;
       } else {
-        recycle_off = count0_recycle + a.rejpre[so + kk] + (q - fr);
+        recycle_off = count0_recycle + s.aux3[kk] + (q - fr);
         if (recycle_off < a.cap || a.nb <= 1) {
           a.bucket_id[gi] = (uint16_t)kRecycleBucket;
           a.bucket_offset[gi] = recycle_off;
@@ -508,7 +495,7 @@ __global__ void __launch_bounds__(kPshThreads) psh_resolveB_kernel(PshArgs a) {
       psh_rand(a.key, t.scene + a.scene_base, pt, 128u, r);
       uint32_t p = r[0] % kNumProbes;
       psh_rand(a.key, t.scene + a.scene_base, pt, 129u, r);
-      perturb_vox(r, a.num_vox, a.divisor, a.probe + 3u * p, vox, nvox);
+      perturb_vox(r, a.num_vox, ratio, a.probe + 3u * p, vox, nvox);
       uint32_t c = first_hash(a.hash_type, nvox[0], nvox[1], nvox[2], a.divisor, a.nb);
       if (c == kRecycleBucket) {
         psh_rand(a.key, t.scene + a.scene_base, pt, 130u, r);
@@ -539,9 +526,15 @@ __global__ void __launch_bounds__(kPshThreads) psh_scatter_kernel(PshArgs a) {
     for (uint64_t e = b0 + threadIdx.x; e < b1; e += kPshThreads) dst[e] = a.pad_bits;
     return;
   }
+  __shared__ uint32_t wsum[kPshWarps + 1];
   TileSmem s = carve(smem_raw, a.nbp, a.tile);
   TileInfo t = tile_info(a);
-  if (!t.live) return;
+  if (!t.live) {
+    // an empty scene still reports zero counters
+    if (t.tile == 0)
+      for (uint32_t b = threadIdx.x; b < a.nb; b += kPshThreads) { a.bucket_counter[t.scene * a.nb + b] = 0; a.cumsum_counter[t.scene * a.nb + b] = 0; }
+    return;
+  }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const uint32_t so = t.scene * a.nbp;
   const bool movers = a.tile_movers[t.row] != 0;
@@ -550,9 +543,32 @@ __global__ void __launch_bounds__(kPshThreads) psh_scatter_kernel(PshArgs a) {
   uint16_t *wh = s.whist + warp * a.nbp;
   uint16_t *st = s.stage + warp * kStageHalves;
   const uint32_t gbase = t.start + t.t0;
-  // aux = exclusive bucket start inside the scene
-  for (uint32_t b = threadIdx.x; b < a.nb; b += kPshThreads)
-    s.aux[b] = a.cumsum_counter[t.scene * a.nb + b] - a.cntF[so + b];
+  // Round C totals of the scene: final bucket sizes, their exclusive cumsum (aux = first row of each bucket inside
+  // the scene) and the rank base of this tile's movers (tbase).  The tile-0 CTA writes the two counter outputs.
+  {
+    const uint32_t tiles = scene_tiles(a, t.scene);
+    const uint32_t *tab = a.tabC + (size_t)t.scene * a.tiles_max * a.nbp;
+    uint32_t carry = 0;
+    for (uint32_t b0 = 0; b0 < a.nbp; b0 += kPshThreads) {
+      const uint32_t b = b0 + threadIdx.x;
+      uint32_t fin = 0;
+      if (b < a.nbp) {
+        uint32_t pre, mv;
+        column_sums(tab, tiles, a.nbp, b, t.tile, pre, mv);
+        const uint32_t cb = a.cntB[so + b];
+        if (b == kRecycleBucket) fin = (a.nb > 1) ? min(cb, a.cap) : cb;
+        else if (b < a.nb) fin = cb + mv;
+        s.tbase[b] = pre + cb;
+      }
+      uint32_t tot;
+      const uint32_t ex = block_excl_scan(fin, wsum, &tot);
+      if (b < a.nb) {
+        s.aux[b] = carry + ex;
+        if (t.tile == 0) { a.bucket_counter[t.scene * a.nb + b] = fin; a.cumsum_counter[t.scene * a.nb + b] = carry + ex + fin; }
+      }
+      carry += tot;
+    }
+  }
   if (movers) {
     zero_whist(s, a.nbp);
     __syncthreads();
@@ -568,7 +584,7 @@ __global__ void __launch_bounds__(kPshThreads) psh_scatter_kernel(PshArgs a) {
       warp_count(wh, key, valid, lane);
     }
     __syncthreads();
-    warp_prefix(s, a.nbp, a.tabP + (size_t)t.row * a.nbp, a.cntB + so);
+    warp_prefix(s, a.nbp);
   }
   __syncthreads();
   uint16_t *dst = reinterpret_cast<uint16_t *>(a.scatter_coord);
@@ -627,7 +643,7 @@ static PshPlan psh_plan(uint32_t batch, uint32_t max_n, uint32_t nb) {
   p.tiles_max = max_n ? (max_n + tile - 1) / tile : 1;
   if (p.tiles_max == 0) p.tiles_max = 1;
   size_t rows = (size_t)batch * p.tiles_max;
-  p.scratch_words = 2 * rows * p.nbp + 6 * (size_t)batch * p.nbp + 2 * rows;
+  p.scratch_words = 3 * rows * p.nbp + 3 * (size_t)batch * p.nbp + 2 * rows;
   p.smem_hist = tile_smem_bytes(p.nbp, 0);
   p.smem_rank = tile_smem_bytes(p.nbp, tile);
   return p;
@@ -636,14 +652,12 @@ static PshPlan psh_plan(uint32_t batch, uint32_t max_n, uint32_t nb) {
 static int psh_run(PshArgs a, const PshPlan &p, uint32_t *scratch, uint32_t max_n, cudaStream_t st) {
   size_t rows = (size_t)a.batch * p.tiles_max;
   uint32_t *w = scratch;
-  a.tabP = w; w += rows * p.nbp;
-  a.tabQ = w; w += rows * p.nbp;
+  a.tabA = w; w += rows * p.nbp;
+  a.tabB = w; w += rows * p.nbp;
+  a.tabC = w; w += rows * p.nbp;
   a.count0 = w; w += (size_t)a.batch * p.nbp;
   a.kept = w; w += (size_t)a.batch * p.nbp;
-  a.freeB = w; w += (size_t)a.batch * p.nbp;
-  a.rejpre = w; w += (size_t)a.batch * p.nbp;
   a.cntB = w; w += (size_t)a.batch * p.nbp;
-  a.cntF = w; w += (size_t)a.batch * p.nbp;
   a.tile_pending = w; w += rows;
   a.tile_movers = w; w += rows;
   a.tile = p.tile; a.tiles_max = p.tiles_max; a.nbp = p.nbp;
@@ -662,17 +676,13 @@ static int psh_run(PshArgs a, const PshPlan &p, uint32_t *scratch, uint32_t max_
   if (p.smem_rank > 200 * 1024) return set_error(F3D_ERR_UNSUPPORTED, "num_bucket=%u needs %zu bytes of shared memory", a.nb, p.smem_rank);
 
   dim3 grid(p.tiles_max, a.batch);
-  // tabP is fully rewritten by K1 for live tiles; tabQ (round B) and the later tabP (round C) rows are
-  // accumulated with atomics and must start at zero.
-  F3D_CUDA_TRY(cudaMemsetAsync(a.tabQ, 0, rows * p.nbp * sizeof(uint32_t), st));
+  // the round A table is fully rewritten by the histogram kernel for live tiles; the round B and C tables are
+  // accumulated with atomics and must start at zero (they are adjacent: one memset)
   if (max_n > 0) {
+    F3D_CUDA_TRY(cudaMemsetAsync(a.tabB, 0, 2 * rows * p.nbp * sizeof(uint32_t), st));
     psh_hist_kernel<<<grid, kPshThreads, p.smem_hist, st>>>(a);
-    psh_scanA_kernel<<<a.batch, kPshThreads, 0, st>>>(a);
     psh_rankA_kernel<<<grid, kPshThreads, p.smem_rank, st>>>(a);
-    psh_scanB_kernel<<<a.batch, kPshThreads, 0, st>>>(a);
-    F3D_CUDA_TRY(cudaMemsetAsync(a.tabP, 0, rows * p.nbp * sizeof(uint32_t), st));
     psh_resolveB_kernel<<<grid, kPshThreads, p.smem_rank, st>>>(a);
-    psh_scanC_kernel<<<a.batch, kPshThreads, 0, st>>>(a);
   } else {
     F3D_CUDA_TRY(cudaMemsetAsync(a.bucket_counter, 0, (size_t)a.batch * a.nb * 4, st));
     F3D_CUDA_TRY(cudaMemsetAsync(a.cumsum_counter, 0, (size_t)a.batch * a.nb * 4, st));
@@ -686,7 +696,7 @@ static int psh_run(PshArgs a, const PshPlan &p, uint32_t *scratch, uint32_t max_
     a.tiles_max = p.tiles_max;
     psh_scatter_kernel<<<grid2, kPshThreads, p.smem_rank, st>>>(a);
   }
-  return check_launch("psh kernels", (max_n > 0 ? 6 : 0) + (gx > 0 ? 1 : 0));
+  return check_launch("psh kernels", (max_n > 0 ? 3 : 0) + (gx > 0 ? 1 : 0));
 }
 
 }  // namespace f3d

@@ -77,30 +77,52 @@ __device__ __forceinline__ void philox4x32(uint32_t c0, uint32_t c1, uint32_t c2
 
 struct RngKey { uint32_t k0, k1; };
 
-// Random words for (scene, point-in-scene, tag).  tag < 128 is the probe index of the rebalance walk,
-// 128..130 are the draws of the recycle redistribution.
+// Random words for (scene, point-in-scene, tag): tags 128..130 are the draws of the recycle redistribution, tag 200
+// seeds the probe walk of the rebalance.
 __device__ __forceinline__ void psh_rand(RngKey key, uint32_t scene, uint32_t point, uint32_t tag, uint32_t (&out)[4]) {
   philox4x32(point, scene, tag, 0u, key.k0, key.k1, out);
 }
 
-// Shifted voxel for one probe: segment length = round(num_vox * U(2.56,5.12) / divisor), the voxel moves by
-// probe[d] segments plus a uniform jitter of +-half a segment, and wraps by |v| mod num_vox.
-__device__ __forceinline__ void perturb_vox(const uint32_t (&r)[4], uint32_t num_vox, uint32_t divisor,
+// Random words of the 128-probe walk of one point.  One Philox call (tag 200) seeds four linear congruential
+// streams; every probe advances each stream once (s <- s * 1664525 + 1013904223) and uses s ^ (s >> 15).  The walk
+// needs four draws per probe for up to 128 probes per overflowing point; a full Philox call per probe made the
+// walk the most expensive part of the whole bucketing.
+struct ProbeStream { uint32_t s[4]; };
+
+__device__ __forceinline__ void probe_stream_init(RngKey key, uint32_t scene, uint32_t point, ProbeStream &st) {
+  psh_rand(key, scene, point, 200u, st.s);
+}
+
+__device__ __forceinline__ void probe_stream_next(ProbeStream &st, uint32_t (&r)[4]) {
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    st.s[k] = st.s[k] * 1664525u + 1013904223u;
+    r[k] = st.s[k] ^ (st.s[k] >> 15);
+  }
+}
+
+// Shifted voxel for one probe: segment length = round(U(2.56,5.12) * num_vox / divisor), the voxel moves by
+// probe[d] segments plus a uniform jitter of +-half a segment, and wraps by |v| mod num_vox
+// (src/common/rand.cuh:95-115).  `ratio` = fp32(num_vox) / fp32(divisor), computed once by the caller; the jitter
+// maps a 32-bit draw to [0, span) with a multiply-high instead of a division.
+__device__ __forceinline__ void perturb_vox(const uint32_t (&r)[4], uint32_t num_vox, float ratio,
                                             const int16_t *__restrict__ probe_row, const uint32_t (&vox)[3],
                                             uint32_t (&nvox)[3]) {
   float u = (float)(r[0] >> 8) * (1.0f / 16777216.0f);
   float scaling = __fadd_rn(2.56f, __fmul_rn(u, 2.56f));
-  float q = __fdiv_rn(__fmul_rn((float)num_vox, scaling), (float)divisor);
-  int32_t seg = (int32_t)floorf(__fadd_rn(q, 0.5f));
+  int32_t seg = (int32_t)floorf(__fadd_rn(__fmul_rn(scaling, ratio), 0.5f));
   int32_t half_seg = seg / 2;
   uint32_t span = (uint32_t)(2 * half_seg + 1);
 #pragma unroll
   for (int d = 0; d < 3; ++d) {
-    int32_t jitter = (int32_t)(r[1 + d] % span) - half_seg;
+    int32_t jitter = (int32_t)__umulhi(r[1 + d], span) - half_seg;
     int32_t shifted = (int32_t)vox[d] + (int32_t)probe_row[d] * seg + jitter;
     uint32_t mag = (uint32_t)(shifted < 0 ? -shifted : shifted);
-    nvox[d] = mag % num_vox;
+    if (mag >= num_vox) mag %= num_vox;
+    nvox[d] = mag;
   }
 }
+
+__device__ __forceinline__ float probe_ratio(uint32_t num_vox, uint32_t divisor) { return __fdiv_rn((float)num_vox, (float)divisor); }
 
 }  // namespace f3d

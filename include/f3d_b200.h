@@ -79,9 +79,9 @@ int f3d_batch_psh_scatter_pad_hash(
  * synchronisation of cudaMalloc / cudaFree).  It has no counterpart in the reference.  The scratch tables live in a
  * fixed 4 MiB device array inside the library (held on every GPU that loads it); the call performs no cudaMalloc,
  * cudaFree or other allocating call.  Limits: the batch must satisfy
- *     2*B*T*(NB+1) + 6*B*(NB+1) + 2*B*T <= 1,048,576   with B = batch_size, NB = num_bucket,
+ *     3*B*T*(NB+1) + 3*B*(NB+1) + 2*B*T <= 1,048,576   with B = batch_size, NB = num_bucket,
  *     T = ceil(instance_max_N / tile), tile = clamp(2048*ceil(instance_max_N / 131072), 2048, 16384),
- * otherwise F3D_STATUS_UNSUPPORTED is returned (8 scans of 120,000 points with 256 buckets need 256k words).
+ * otherwise F3D_STATUS_UNSUPPORTED is returned (8 scans of 120,000 points with 256 buckets need 372k words).
  * The first call on a device looks up the array's device address (cudaGetSymbolAddress); make that first call
  * outside any stream capture.  All calls share the array: calls that overlap on one GPU race and must be
  * serialised by the caller. */

@@ -13,7 +13,7 @@ Restated from the reference (file:line within the reference project):
   vox_coord                src/psh/hash_fns.cuh:23-33
   space_out_bit_3d, h1_zorder_{div,mod}_3d   src/psh/hash_fns.cuh:79-86,113-135
   h1_xorsum_{div,mod}      src/psh/hash_fns.cuh:48-68
-  perturb_vox              src/common/rand.cuh:95-115
+  perturb_vox              src/common/rand.cuh:95-115 (draws: Philox-seeded linear congruential streams, see psh_scene)
   first hash + in-bucket offsets   src/psh/batch_psh_bucket.cuh:42-139, src/psh/two_stage_counter.cuh:23-143
   overflow rebalance       src/psh/batch_psh_bucket.cuh:157-246
   recycle redistribution   src/psh/batch_psh_bucket.cuh:259-382
@@ -138,17 +138,17 @@ def psh_rand(seed: int, scene, point, tag):
 
 
 def perturb_vox(r, num_vox: int, divisor: int, probe_row: np.ndarray, vox: np.ndarray) -> np.ndarray:
-    """src/common/rand.cuh:95-115 with the four Philox words as the four draws.  probe_row is [M,3] (one row per
-    point) and vox is [M,3]."""
+    """src/common/rand.cuh:95-115 with four 32-bit draws per probe.  probe_row is [M,3] (one row per point) and vox
+    is [M,3].  segment = floor(U(2.56,5.12) * (fp32(num_vox) / fp32(divisor)) + 0.5); jitter = mulhi(draw, span) - half."""
+    ratio = F32(num_vox) / F32(divisor)
     u = (r[0] >> U32(8)).astype(F32) * F32(1.0 / 16777216.0)
     scaling = F32(2.56) + u * F32(2.56)
-    q = (F32(num_vox) * scaling) / F32(divisor)
-    seg = np.floor(q + F32(0.5)).astype(np.int64)
+    seg = np.floor(scaling * ratio + F32(0.5)).astype(np.int64)
     half = seg // 2
     span = (2 * half + 1)
     out = np.empty_like(vox)
     for d in range(3):
-        jitter = (r[1 + d].astype(np.int64) % span) - half
+        jitter = ((r[1 + d].astype(np.uint64) * span.astype(np.uint64)) >> np.uint64(32)).astype(np.int64) - half
         shifted = vox[:, d].astype(np.int64) + probe_row[:, d].astype(np.int64) * seg + jitter
         out[:, d] = (np.abs(shifted) % num_vox).astype(np.uint32)
     return out
@@ -193,11 +193,14 @@ def psh_scene(coord_f16, bbox_min, bbox_max, probe, scene: int, num_bucket: int,
     if idx_over.size:
         target = np.full(idx_over.size, nb, dtype=np.int64)          # nb = "no admissible probe"
         todo = np.arange(idx_over.size)
+        # one Philox call (tag 200) seeds four linear congruential streams per point; every probe advances them once
+        state = [w.astype(np.uint64) for w in psh_rand(seed, scene, idx_over, 200)]
         for p in range(NUM_PROBES):
+            state = [(w * np.uint64(1664525) + np.uint64(1013904223)) & np.uint64(0xFFFFFFFF) for w in state]
             if todo.size == 0:
                 break
             pts = idx_over[todo]
-            r = psh_rand(seed, scene, pts, p)
+            r = [((w[todo] ^ (w[todo] >> np.uint64(15))) & np.uint64(0xFFFFFFFF)).astype(np.uint32) for w in state]
             nv = perturb_vox(r, num_vox, divisor, np.broadcast_to(probe[p], (pts.size, 3)), vox[pts])
             c = first_hash(hash_type, nv, divisor, nb).astype(np.int64)
             ok = (c != b0[pts]) & (c != RECYCLE) & (kept[c] < cap)
