@@ -361,6 +361,141 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     print(json.dumps(line), flush=True)
 
 
+# ------------------------------------------------------------------------------- secondary workloads (1 GPU)
+def _time_ms(fn, steps, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def run_attn_layer(args):
+    """One bucketed-attention layer forward + backward on 8 LiDAR-like scans of 120,000 points: dim 256, 8 heads x
+    head_dim 32, bf16, bucket 512 (scope of one bucket).  Reports tokens/s and the attention kernels' TFLOP/s."""
+    from flash3dtransformer_b200.lib import pshattn
+    dev = torch.device("cuda:0")
+    peaks = measured_peaks()
+    l, h, d, c, bucket = 8 * 120000, 8, 32, 256, 512
+    g = torch.Generator(dev).manual_seed(0)
+    x = torch.randn(l, c, device=dev, generator=g).bfloat16()
+    wqkv = (torch.randn(3 * c, c, device=dev, generator=g) / c ** 0.5).bfloat16()
+    wp = (torch.randn(c, c, device=dev, generator=g) / c ** 0.5).bfloat16()
+    bqkv, bp = torch.zeros(3 * c, device=dev), torch.zeros(c, device=dev)
+    scopes = torch.arange(l // bucket, dtype=torch.int64).reshape(-1, 1).to(torch.uint32).to(dev)
+    qkv = torch.empty(3, l, c, device=dev, dtype=torch.bfloat16)
+    o = torch.empty(1, l, h, d, device=dev, dtype=torch.bfloat16)
+    lse = torch.zeros(1, l, h, device=dev)
+    out = torch.empty(l, c, device=dev, dtype=torch.bfloat16)
+    do = torch.randn(1, l, h, d, device=dev, generator=g).bfloat16()
+    delta = torch.zeros(1, l, h, device=dev)
+    dq, dk, dv = (torch.zeros_like(o) for _ in range(3))
+    q, k, v = (qkv[i].view(1, l, h, d) for i in range(3))
+
+    def fwd_attn():
+        pshattn.buck_swin_fwd(q, k, v, o, lse, scopes, bucket)
+
+    def bwd_attn():
+        pshattn.buck_swin_bwd(q, k, v, o, do, lse, delta, dq, dk, dv, scopes, bucket)
+
+    def layer():
+        pshattn.linear_bf16(x, wqkv, bqkv, qkv, nsplit=3)
+        fwd_attn()
+        pshattn.linear_bf16(o.view(l, c), wp, bp, out)
+        bwd_attn()
+        # gradients of the two projections (plain library GEMMs, as in the layer's autograd backward)
+        gx = out @ wp
+        gw = out.t() @ o.view(l, c)
+        gq = qkv.permute(1, 0, 2).reshape(l, 3 * c)
+        gx2 = gq @ wqkv
+        gw2 = gq.t() @ x
+        return gx, gw, gx2, gw2
+
+    t_f = _time_ms(fwd_attn, args.steps, args.warmup)
+    t_b = _time_ms(bwd_attn, args.steps, args.warmup)
+    t_l = _time_ms(layer, args.steps, args.warmup)
+    pshattn.device_status()
+    flops_f = 4.0 * l * bucket * h * d
+    line = {
+        "metric": "tokens/sec (bucketed-attention layer fwd+bwd)", "value": l / (t_l * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": t_l, "higher_is_better": True, "dtype": "bf16",
+        "data": "synthetic", "config": {"workload": "attn_layer_fwd_bwd_8x120k_dim256_h8_d32_bucket512"},
+        "attention_fwd": {"ms": t_f, "tflops": flops_f / (t_f * 1e-3) / 1e12, "frac_of_peak": flops_f / (t_f * 1e-3) / 1e12 / peaks["tflops"]},
+        "attention_bwd": {"ms": t_b, "tflops": 2.5 * flops_f / (t_b * 1e-3) / 1e12,
+                          "frac_of_peak": 2.5 * flops_f / (t_b * 1e-3) / 1e12 / peaks["tflops"]},
+        "peak_tflops": peaks["tflops"], "peak_source": peaks["source"],
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_psh_pool(args):
+    """PSH build + scatter, three rounds of stride-2 sub-bucket pooling and the matching unpools on 8 scenes of
+    1,000,000 points with heavy-tailed (Zipf 1.5) voxel occupancy, feature dim 128 fp32.  Reports points/s and the
+    algorithmic HBM GB/s of every kernel family."""
+    from flash3dtransformer_b200 import synthetic
+    from flash3dtransformer_b200.lib import pshattn
+    from flash3dtransformer_b200.psh import psh_main, subbuck as sbm
+    dev = torch.device("cuda:0")
+    peaks = measured_peaks()
+    scenes, pts, c, bucket = 8, args.points if args.points != POINTS_PER_SCENE else 1_000_000, 128, 2048
+    c32, seps = synthetic.batch(synthetic.zipf_voxels, [pts] * scenes, seed=0)
+    coords = torch.from_numpy(c32.astype(np.float16)).to(dev)
+    sp = torch.from_numpy(seps.astype(np.uint32)).to(dev)
+    n = coords.shape[0]
+    feat = torch.randn(n, c, device=dev, generator=torch.Generator(dev).manual_seed(0))
+    _, max_n, nb, div = psh_main.bucket_plan(sp, bucket)
+    buf = psh_main.BucketScatterBuffers.create_buffers(coords, sp, bucket, n, nb)
+    lo, hi = torch.aminmax(coords, dim=0)
+
+    def psh():
+        pshattn.batch_psh_scatter_pad_hash(coords, buf.bucket_id, buf.bucket_cntr, buf.bucket_offs, sp, max_n, nb, div, bucket,
+                                           0xFFFF, lo, hi, buf.probe_offs, buf.bucket_cumsum, buf.scattered_coord, 0.0, 1)
+
+    levels = []
+    cc, ff, ss = coords, feat, sp
+    for _ in range(3):
+        sb = sbm.SubbuckBuffers.create_subbuck_buff(cc, ff, ss, 2)
+        levels.append((cc, ff, ss, sb, int(sbm.calc_red_sep_sizes(ss, 1)[1].to(torch.int64).max())))
+        pshattn.batch_subbuck_reduce(cc, ff, ss, int(levels[-1][4]), 2, 0xFFFF, sb.bbox_min, sb.bbox_max, sb.subbuck_id, sb.subbuck_off,
+                                     sb.reduced_sep, sb.reduced_coord, sb.reduced_feat, sb.unpool_ind, 1, 1)
+        cc, ff, ss = sb.reduced_coord, sb.reduced_feat, sb.reduced_sep
+    ups = [torch.empty_like(lv[1]) for lv in levels]
+
+    def pools():
+        for cc_, ff_, ss_, sb_, mx in levels:
+            pshattn.batch_subbuck_reduce(cc_, ff_, ss_, int(mx), 2, 0xFFFF, sb_.bbox_min, sb_.bbox_max, sb_.subbuck_id, sb_.subbuck_off,
+                                         sb_.reduced_sep, sb_.reduced_coord, sb_.reduced_feat, sb_.unpool_ind, 1, 1)
+
+    def unpools():
+        down = levels[-1][3].reduced_feat
+        for (cc_, ff_, ss_, sb_, mx), up in zip(reversed(levels), reversed(ups)):
+            pshattn.additive_unpool_fwd(ff_, down, up, sb_.unpool_ind, 2)
+            down = up
+
+    t_psh = _time_ms(psh, args.steps, args.warmup)
+    t_pool = _time_ms(pools, args.steps, args.warmup)
+    t_unpool = _time_ms(unpools, args.steps, args.warmup)
+    rows = [lv[0].shape[0] for lv in levels]
+    by_pool = sum(r * (19.0 + c * 4 + c * 4 / 2 + 4) for r in rows)
+    by_unpool = sum(r * (2.0 * c * 4 + c * 4 / 2 + 4) for r in rows)
+    total_ms = t_psh + t_pool + t_unpool
+    fam = {"psh_scatter": {"ms": t_psh, "gbs": 18.0 * n / (t_psh * 1e-3) / 1e9},
+           "subbuck_pool_x3": {"ms": t_pool, "gbs": by_pool / (t_pool * 1e-3) / 1e9},
+           "unpool_x3": {"ms": t_unpool, "gbs": by_unpool / (t_unpool * 1e-3) / 1e9}}
+    for f in fam.values():
+        f["frac_of_hbm_peak"] = f["gbs"] / peaks["hbm_gbs"]
+    line = {"metric": "points/sec (PSH + 3x pool + 3x unpool)", "value": n / (total_ms * 1e-3), "unit": "points/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms, "higher_is_better": True, "dtype": "f32",
+            "data": "synthetic", "config": {"workload": f"psh_pool_unpool_8x{pts // 1000}k_zipf_c128_fp32_bucket2048"},
+            "kernels": fam, "peak_hbm_gbs": peaks["hbm_gbs"], "peak_source": peaks["source"]}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -371,6 +506,8 @@ def main():
     ap.add_argument("--points", type=int, default=POINTS_PER_SCENE)
     ap.add_argument("--ref-points", type=int, default=20000, help="points of the CPU arm's bounded sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="backbone", choices=["backbone", "attn_layer", "psh_pool"],
+                    help="backbone = the headline metric; the other two are single-GPU side measurements")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -379,6 +516,12 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.workload != "backbone":
+        if rank == 0:
+            from flash3dtransformer_b200.lib import _cabi
+            _cabi.load()
+            (run_attn_layer if args.workload == "attn_layer" else run_psh_pool)(args)
         return
     if world > 1:
         import torch.distributed as dist

@@ -4,13 +4,15 @@
 // flash3dxfmr/layers/buck_swin.py:159,163,185-194) and the toy mma.sync kernel gemm_sm_bf16_ker
 // (src/psh/gemm.cuh:30-85, host src/psh/gemm_dispatcher.cu:26-80, which demands M == 128 and synchronises).
 //
-// Structure (one persistent CTA per SM, 192 threads):
+// Structure (one persistent CTA per SM, 320 threads):
 //   warp 0      TMA producer: A tile 128x64 and W tile BNx64 per stage, 128-byte swizzle, mbarrier completion
 //   warp 1      owns tensor memory; one elected lane issues tcgen05.mma (M=128, N=BN, K=16) four times per
 //               stage and commits the stage's "empty" barrier; after the last k-block it commits "accumulator full"
-//   warps 2-5   epilogue: tcgen05.ld the 128xBN fp32 accumulator (each warp its 32-lane quadrant), add bias /
-//               residual, convert to bf16, stage in swizzled shared memory and write with TMA stores
-// Two accumulators (2*BN tensor-memory columns) let the epilogue of tile i overlap the MMAs of tile i+1.
+//   warps 2-9   epilogue: two warps per 32-lane quadrant of the 128xBN fp32 accumulator; a warp takes 32 columns at
+//               a time (tcgen05.ld), adds bias / residual, applies GELU / SwiGLU, converts to bf16, stages the
+//               32x32 block in swizzled shared memory and writes it with a TMA store
+// Up to four accumulators (at most 512 tensor-memory columns) let the epilogues of earlier tiles overlap the MMAs of
+// the following ones.
 // Outputs may be split column-wise into `nsplit` separate [M, N/nsplit] matrices (Q, K, V written directly in
 // the [L, H*D] layout the attention kernel reads, instead of three .contiguous() copies,
 // flash3dxfmr/layers/buck_swin.py:188-190).
@@ -20,7 +22,7 @@
 
 namespace f3d {
 
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 320;     // TMA warp, MMA warp, 8 epilogue warps
 constexpr int BM = 128;
 constexpr int BK = 64;
 
@@ -45,7 +47,8 @@ template <int BN> struct GemmSmem {
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kOutBytes = 4 /*warps*/ * 2 /*buffers*/ * 32 * 128;   // 32 rows x 64 bf16 per buffer
+  static constexpr int kOutBytes = 8 /*warps*/ * 2 /*buffers*/ * 32 * 64;    // 32 rows x 32 bf16 per buffer
+  static constexpr int kAcc = BN >= 256 ? 2 : 4;        // accumulator buffers in tensor memory (kAcc * BN <= 512 columns)
   static constexpr int kBarBytes = 256;
   static constexpr int kTotal = kStages * kStageBytes + kOutBytes + kBarBytes + 1024 /*alignment slack*/;
 };
@@ -62,14 +65,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                          const __grid_constant__ CUtensorMap map_c, GemmArgs g) {
   using S = GemmSmem<BN>;
   constexpr int kStages = S::kStages;
-  constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+  constexpr int kAcc = S::kAcc;
+  constexpr uint32_t kTmemCols = kAcc * BN < 32 ? 32 : kAcc * BN;
   extern __shared__ unsigned char smem_raw[];
   unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char *stage_base = smem;
   unsigned char *out_base = smem + kStages * S::kStageBytes;
   uint64_t *bars = reinterpret_cast<uint64_t *>(out_base + S::kOutBytes);
-  uint64_t *full = bars, *empty = bars + kStages, *acc_full = bars + 2 * kStages, *acc_empty = bars + 2 * kStages + 2;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 4);
+  uint64_t *full = bars, *empty = bars + kStages, *acc_full = bars + 2 * kStages, *acc_empty = bars + 2 * kStages + kAcc;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 2 * kAcc);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -79,7 +83,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { tc::mbar_init(&full[s], 1); tc::mbar_init(&empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { tc::mbar_init(&acc_full[a], 1); tc::mbar_init(&acc_empty[a], 4); }
+    for (int a = 0; a < kAcc; ++a) { tc::mbar_init(&acc_full[a], 1); tc::mbar_init(&acc_empty[a], 8); }
     *abort_flag = 0;
     tc::mbar_fence_init();
   }
@@ -119,7 +123,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       uint32_t it = 0, t_local = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t_local) {
-        const uint32_t acc = t_local & 1u, aph = (t_local >> 1) & 1u;
+        const uint32_t acc = t_local % kAcc, aph = (t_local / kAcc) & 1u;
         if (!tc::mbar_wait(&acc_empty[acc], aph ^ 1u, wc, 102)) { ok = false; break; }
         tc::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
@@ -138,75 +142,70 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       }
     }
   } else {
+    // 8 epilogue warps: two per tensor-memory lane quadrant.  A task is 32 output columns of the warp's 32 rows;
+    // the two warps of a quadrant take alternate tasks, so every scheduler of the SM has two epilogue warps to
+    // interleave (with one, the loop was bound by instruction latency).
     const int q = warp & 3;                       // tensor-memory lane quadrant this warp may read
-    unsigned char *my_out = out_base + (warp - 2) * 2 * 32 * 128;
+    const int half = (warp - 2) >> 2;             // 0 or 1: which of the quadrant's two warps
+    unsigned char *my_out = out_base + (warp - 2) * 2 * 32 * 64;
     uint32_t t_local = 0, obuf = 0;
     bool ok = true;
     const int out_cols = g.epilogue == EPI_SWIGLU ? BN / 2 : BN;     // output columns produced per tile
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t_local) {
-      const uint32_t acc = t_local & 1u, aph = (t_local >> 1) & 1u;
+      const uint32_t acc = t_local % kAcc, aph = (t_local / kAcc) & 1u;
       const int m0 = (tile / n_tiles) * BM, n0 = (tile % n_tiles) * BN;
       if (!tc::mbar_wait(&acc_full[acc], aph, wc, 104)) { ok = false; break; }
       tc::tc_fence_after_sync();
       const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
       const int row = m0 + q * 32 + lane;
-      for (int c0 = 0; c0 < out_cols; c0 += 64) {
-        const int ncol = min(64, out_cols - c0);             // 32 or 64 columns in this chunk
-        float v[64];
-        // runtime switches (bias, activation) are tested once per chunk, never per element
+      for (int c0 = half * 32; c0 < out_cols; c0 += 64) {
+        float v[32];
+        const int oc0 = (g.epilogue == EPI_SWIGLU ? n0 / 2 : n0) + c0;      // first output column of the task
+        // runtime switches (bias, activation) are tested once per task, never per element
         if (g.epilogue == EPI_SWIGLU) {
+          uint32_t r[32], u[32];
+          tc::tmem_ld_32x32b_x32(t_row + c0, r);
+          tc::tmem_ld_32x32b_x32(t_row + BN / 2 + c0, u);
+          tc::tmem_ld_wait();
+          if (g.bias) {
+            const float4 *pg = reinterpret_cast<const float4 *>(g.bias + oc0);
+            const float4 *pu = reinterpret_cast<const float4 *>(g.bias + g.N / 2 + oc0);
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            uint32_t r[32], u[32];
-            tc::tmem_ld_32x32b_x32(t_row + c0 + h * 32, r);
-            tc::tmem_ld_32x32b_x32(t_row + BN / 2 + c0 + h * 32, u);
-            tc::tmem_ld_wait();
-            float bg[32], bu[32];
-            if (g.bias) {
-              const float4 *pg = reinterpret_cast<const float4 *>(g.bias + n0 / 2 + c0 + h * 32);
-              const float4 *pu = reinterpret_cast<const float4 *>(g.bias + g.N / 2 + n0 / 2 + c0 + h * 32);
+            for (int j = 0; j < 8; ++j) {
+              const float4 a4 = __ldg(pg + j), b4 = __ldg(pu + j);
+              const float bg[4] = {a4.x, a4.y, a4.z, a4.w}, bu[4] = {b4.x, b4.y, b4.z, b4.w};
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                float4 a4 = __ldg(pg + j), b4 = __ldg(pu + j);
-                bg[4 * j] = a4.x; bg[4 * j + 1] = a4.y; bg[4 * j + 2] = a4.z; bg[4 * j + 3] = a4.w;
-                bu[4 * j] = b4.x; bu[4 * j + 1] = b4.y; bu[4 * j + 2] = b4.z; bu[4 * j + 3] = b4.w;
+              for (int e = 0; e < 4; ++e) {
+                const float gt = __uint_as_float(r[4 * j + e]) + bg[e], up = __uint_as_float(u[4 * j + e]) + bu[e];
+                v[4 * j + e] = __fdividef(gt, 1.f + __expf(-gt)) * up;
               }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) { bg[j] = 0.f; bu[j] = 0.f; }
             }
+          } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-              float gt = __uint_as_float(r[j]) + bg[j];
-              float up = __uint_as_float(u[j]) + bu[j];
-              v[h * 32 + j] = __fdividef(gt, 1.f + __expf(-gt)) * up;
+              const float gt = __uint_as_float(r[j]), up = __uint_as_float(u[j]);
+              v[j] = __fdividef(gt, 1.f + __expf(-gt)) * up;
             }
           }
         } else {
+          uint32_t r[32];
+          tc::tmem_ld_32x32b_x32(t_row + c0, r);
+          tc::tmem_ld_wait();
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            if (h * 32 < ncol) {
-              uint32_t r[32];
-              tc::tmem_ld_32x32b_x32(t_row + c0 + h * 32, r);
-              tc::tmem_ld_wait();
-#pragma unroll
-              for (int j = 0; j < 32; ++j) v[h * 32 + j] = __uint_as_float(r[j]);
-            }
-          }
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
           if (g.bias) {
-            const int cb = n0 + c0;
-            const float4 *bp = reinterpret_cast<const float4 *>(g.bias + cb);
-            if (ncol == 64 && cb + 64 <= g.N) {                  // common case: no guards inside the loop
+            const float4 *bp = reinterpret_cast<const float4 *>(g.bias + oc0);
+            if (oc0 + 32 <= g.N) {                               // common case: no guards inside the loop
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                float4 b4 = __ldg(bp + j);
+              for (int j = 0; j < 8; ++j) {
+                const float4 b4 = __ldg(bp + j);
                 v[4 * j] += b4.x; v[4 * j + 1] += b4.y; v[4 * j + 2] += b4.z; v[4 * j + 3] += b4.w;
               }
             } else {
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                if (4 * j < ncol && cb + 4 * j < g.N) {          // N is a multiple of 8: groups of 4 are all in or all out
-                  float4 b4 = __ldg(bp + j);
+              for (int j = 0; j < 8; ++j) {
+                if (oc0 + 4 * j < g.N) {                          // N is a multiple of 8: groups of 4 are all in or all out
+                  const float4 b4 = __ldg(bp + j);
                   v[4 * j] += b4.x; v[4 * j + 1] += b4.y; v[4 * j + 2] += b4.z; v[4 * j + 3] += b4.w;
                 }
               }
@@ -214,33 +213,30 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           }
           if (g.epilogue == EPI_GELU) {
 #pragma unroll
-            for (int j = 0; j < 64; ++j) v[j] = gelu_tanh(v[j]);
+            for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
           }
         }
         if (g.residual && row < g.M) {
-          const __nv_bfloat16 *rp = g.residual + (size_t)row * g.ldr + n0 + c0;
-          const bool vec_ok = (n0 + c0 + ncol <= g.N) && ((reinterpret_cast<uintptr_t>(rp) & 15) == 0);
-          if (vec_ok) {
+          const __nv_bfloat16 *rp = g.residual + (size_t)row * g.ldr + oc0;
+          if (oc0 + 32 <= g.N && (reinterpret_cast<uintptr_t>(rp) & 15) == 0) {
 #pragma unroll
-            for (int j = 0; j < 64; j += 8) {
-              if (j < ncol) {
-                uint4 w = __ldg(reinterpret_cast<const uint4 *>(rp + j));
-                const __nv_bfloat162 *h2 = reinterpret_cast<const __nv_bfloat162 *>(&w);
+            for (int j = 0; j < 32; j += 8) {
+              const uint4 w = __ldg(reinterpret_cast<const uint4 *>(rp + j));
+              const __nv_bfloat162 *h2 = reinterpret_cast<const __nv_bfloat162 *>(&w);
 #pragma unroll
-                for (int e = 0; e < 4; ++e) { float2 f = __bfloat1622float2(h2[e]); v[j + 2 * e] += f.x; v[j + 2 * e + 1] += f.y; }
-              }
+              for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h2[e]); v[j + 2 * e] += f.x; v[j + 2 * e + 1] += f.y; }
             }
           } else {
 #pragma unroll
-            for (int j = 0; j < 64; ++j) if (j < ncol && n0 + c0 + j < g.N) v[j] += __bfloat162float(rp[j]);
+            for (int j = 0; j < 32; ++j) if (oc0 + j < g.N) v[j] += __bfloat162float(rp[j]);
           }
         }
         if (g.direct_store) {
           if (row < g.M) {
 #pragma unroll
-            for (int j = 0; j < 64; j += 8) {
-              const int oc = n0 + c0 + j;
-              if (j >= ncol || oc >= g.N) continue;
+            for (int j = 0; j < 32; j += 8) {
+              const int oc = oc0 + j;
+              if (oc >= g.N) continue;
               uint4 w;
               __nv_bfloat162 *h2 = reinterpret_cast<__nv_bfloat162 *>(&w);
 #pragma unroll
@@ -250,24 +246,23 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           }
           continue;
         }
-        // stage 32 rows x 64 columns (128 bytes per row) in the layout the 128-byte-swizzled TMA store reads
-        unsigned char *ob = my_out + obuf * 32 * 128;
-        if (lane == 0) tc::tma_wait_read<1>();    // the store issued two chunks ago has drained this buffer
+        // stage 32 rows x 32 columns (64 bytes per row) in the layout the 64-byte-swizzled TMA store reads:
+        // 16-byte chunk j of row r sits at chunk j ^ ((r >> 1) & 3)
+        unsigned char *ob = my_out + obuf * 32 * 64;
+        if (lane == 0) tc::tma_wait_read<1>();    // the store issued two tasks ago has drained this buffer
         __syncwarp();
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < 4; ++j) {
           uint4 w;
           __nv_bfloat162 *h2 = reinterpret_cast<__nv_bfloat162 *>(&w);
 #pragma unroll
           for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(v[j * 8 + 2 * e], v[j * 8 + 2 * e + 1]);
-          if (j * 8 < ncol) *reinterpret_cast<uint4 *>(ob + lane * 128 + ((j ^ (lane & 7)) * 16)) = w;
+          *reinterpret_cast<uint4 *>(ob + lane * 64 + ((j ^ ((lane >> 1) & 3)) * 16)) = w;
         }
         tc::fence_proxy_async();
         __syncwarp();
         if (lane == 0) {
-          const int oc = (g.epilogue == EPI_SWIGLU ? n0 / 2 : n0) + c0;   // output column
-          const int sp = oc / g.split_n, xc = oc % g.split_n;
-          tc::tma_store_3d(&map_c, ob, xc, m0 + q * 32, sp);
+          tc::tma_store_3d(&map_c, ob, oc0 % g.split_n, m0 + q * 32, oc0 / g.split_n);
           tc::tma_commit();
         }
         obuf ^= 1u;
@@ -328,19 +323,18 @@ int linear_bf16(const void *A, int lda, const void *W, int ldw, const void *bias
   if (split_n % 8) return set_error(F3D_ERR_ARG, "gemm: output row length %d is not a multiple of 8", split_n);
   if (residual && nsplit != 1) return set_error(F3D_ERR_ARG, "gemm: residual needs nsplit == 1");
   int BN = 256;
-  if (epilogue == EPI_SWIGLU) BN = 128;
+  if (epilogue == EPI_SWIGLU) BN = (N % 256 == 0) ? 256 : 128;
   else if (N <= 32) BN = 32;
   else if (N <= 64) BN = 64;
   else if (N <= 128 || (nsplit > 1 && split_n % 256)) BN = 128;
-  const int direct = (nsplit > 1 && split_n % 64) ? 1 : 0;
-  if (nsplit > 1 && !direct && split_n % BN) BN = 64;
+  const int direct = (nsplit > 1 && split_n % 32) ? 1 : 0;      // a 32-column task must not straddle two outputs
   if (reinterpret_cast<uintptr_t>(C) % 16) return set_error(F3D_ERR_ARG, "gemm: output pointer is not 16-byte aligned");
   CUtensorMap ma, mb, mc;
   F3D_TRY(encode_tmap_2d(&ma, 0, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, BM, 128));
   int b_box_rows = epilogue == EPI_SWIGLU ? BN / 2 : BN;
   F3D_TRY(encode_tmap_2d(&mb, 0, W, (uint64_t)K, (uint64_t)N, (uint64_t)ldw * 2, BK, b_box_rows, 128));
   F3D_TRY(encode_tmap_3d(&mc, 0, C, (uint64_t)split_n, (uint64_t)M, (uint64_t)nsplit, (uint64_t)split_n * 2,
-                         (uint64_t)split_stride * 2, 64, 32, 1, 128));
+                         (uint64_t)split_stride * 2, 32, 32, 1, 64));
   GemmArgs g{M, N, K, nsplit, split_n, static_cast<const float *>(bias), static_cast<const __nv_bfloat16 *>(residual), ldr,
              epilogue, direct, static_cast<__nv_bfloat16 *>(C), split_stride, status_word(device)};
   if (!g.status) return F3D_ERR_CUDA;
