@@ -14,11 +14,14 @@
 //   warp 1     owns tensor memory, issues S = Q K^T (M=128, N=64) and O += P V (A operand P read from tensor
 //              memory, V as MN-major B operand), commits mbarriers
 //   warps 2-5  softmax: one thread per query row; S is read with tcgen05.ld, the running maximum and sum are kept
-//              in the base-2 domain, P is written back as bf16 over the S columns with tcgen05.st, O is rescaled
-//              in tensor memory only when the row maximum moved, and the epilogue normalises and stores O and LSE
-// Tensor memory per CTA is 128 columns (256 for D = 128) and shared memory 40 KB at D = 32, so four CTAs share
-// an SM and their softmax phases overlap each other's MMAs; at D = 32 the kernel is bound by exp throughput
-// (one ex2 per score against 4*D = 128 tensor FLOPs), not by the tensor pipe.
+//              in the base-2 domain, P is written as bf16 with tcgen05.st, O is rescaled in tensor memory only
+//              when the row maximum moved, and the epilogue normalises and stores O and LSE
+// Tensor memory holds S (64 columns), P (32) and O (D) side by side: because P does not overwrite S, the MMA warp
+// issues the next tile's Q K^T as soon as the softmax threads have pulled S into registers, so the tensor pipe
+// computes S(j+1) while the warps exponentiate tile j, and the per-tile chain is the softmax arithmetic alone.
+// 128 columns (256 for D >= 64) and 40 KB of shared memory per CTA at D = 32 put four CTAs on an SM.  At D = 32
+// the kernel is bound by the special-function unit (one ex2 per score against 4*D = 128 tensor FLOPs) and by
+// instruction issue of the softmax warps, not by the tensor pipe.
 #include "f3d_common.cuh"
 #include "tc_sm100.cuh"
 #include "../../include/f3d_b200.h"
@@ -31,6 +34,9 @@ constexpr int kAttnThreads = 192;
 constexpr int kBQ = 128;      // query rows per CTA
 constexpr int kBKV = 64;      // keys per tile
 constexpr int kKvStages = 4;
+// The producer runs three stages ahead of the MMAs; sleeping between its polls costs nothing and leaves the
+// issue slots to the softmax warps.
+constexpr uint32_t kProducerSleepNs = 500;
 
 struct AttnFwdArgs {
   __nv_bfloat16 *O; float *lse; const uint32_t *scopes;
@@ -69,32 +75,37 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
   return r;
 }
 
-template <int D> struct AttnCfg {
+template <int D, int BKV> struct AttnCfg {
   static constexpr int DCH = D < 64 ? D : 64;       // columns per swizzled row
   static constexpr int NDCH = D / DCH;
   static constexpr int RB = DCH * 2;                // bytes per swizzled row
   static constexpr uint64_t SWZ = RB == 128 ? tc::kSwizzle128 : (RB == 64 ? tc::kSwizzle64 : tc::kSwizzle32);
   static constexpr int kQBytes = kBQ * D * 2;
-  static constexpr int kTileBytes = kBKV * D * 2;   // one K or V tile
+  static constexpr int kTileBytes = BKV * D * 2;    // one K or V tile
   static constexpr int kStageBytes = 2 * kTileBytes;
   static constexpr int kSmem = kQBytes + kKvStages * kStageBytes + 256 + 1024;
-  static constexpr uint32_t kTmemCols = (kBKV + D) <= 128 ? 128 : 256;
-  static constexpr uint32_t kOCol = kBKV;           // O accumulator starts after the S columns
+  // Tensor memory columns: S (fp32 scores, BKV), P (bf16 probabilities, two per column, BKV / 2), O (fp32, D).
+  // P has columns of its own so that the next tile's S = Q K^T can be issued as soon as the softmax warps have
+  // read S, while they are still computing P.
+  static constexpr uint32_t kPCol = BKV;
+  static constexpr uint32_t kOCol = BKV + BKV / 2;
+  static constexpr uint32_t kTmemCols = (kOCol + D) <= 128 ? 128u : 256u;
+  static constexpr int kMinCtas = D <= 32 ? 4 : 2;
 };
 
-template <int D>
-__global__ void __launch_bounds__(kAttnThreads)
+template <int D, int BKV>
+__global__ void __launch_bounds__(kAttnThreads, (AttnCfg<D, BKV>::kMinCtas))
 attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, AttnFwdArgs a) {
-  using C = AttnCfg<D>;
+  using C = AttnCfg<D, BKV>;
   extern __shared__ unsigned char smem_raw[];
   unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char *sq = smem;
   unsigned char *skv = smem + C::kQBytes;
   uint64_t *bars = reinterpret_cast<uint64_t *>(skv + kKvStages * C::kStageBytes);
   uint64_t *q_full = bars, *kv_full = bars + 1, *kv_empty = kv_full + kKvStages, *s_full = kv_empty + kKvStages;
-  uint64_t *p_full = s_full + 1, *o_full = p_full + 1;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(o_full + 1);
+  uint64_t *p_full = s_full + 1, *o_full = p_full + 1, *s_free = o_full + 1;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(s_free + 1);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -105,14 +116,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const int scope = qb_lin / (a.q_blocks_per_bucket * a.k);
   const int head = blockIdx.y, brow = blockIdx.z;
   const uint32_t *my_scope = a.scopes + (size_t)scope * a.k;
-  const int tiles_per_bucket = a.bucket / kBKV;
+  const int tiles_per_bucket = a.bucket / BKV;
   const int num_tiles = a.k * tiles_per_bucket;
   const int q_tok = (int)my_scope[bj] * a.bucket + qb * kBQ;      // first query token (inside batch row)
 
   if (threadIdx.x == 0) {
     tc::mbar_init(q_full, 1);
     for (int s = 0; s < kKvStages; ++s) { tc::mbar_init(&kv_full[s], 1); tc::mbar_init(&kv_empty[s], 1); }
-    tc::mbar_init(s_full, 1); tc::mbar_init(p_full, 128); tc::mbar_init(o_full, 1);
+    tc::mbar_init(s_full, 1); tc::mbar_init(p_full, 128); tc::mbar_init(o_full, 1); tc::mbar_init(s_free, 128);
     *abort_flag = 0;
     tc::mbar_fence_init();
   }
@@ -133,51 +144,60 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       for (int j = 0; j < num_tiles; ++j) {
         const int s = j % kKvStages;
         const uint32_t ph = (uint32_t)(j / kKvStages) & 1u;
-        if (!tc::mbar_wait(&kv_empty[s], ph ^ 1u, wc, 201)) break;
-        const int key_tok = (int)my_scope[j / tiles_per_bucket] * a.bucket + (j % tiles_per_bucket) * kBKV;
+        if (!tc::mbar_wait(&kv_empty[s], ph ^ 1u, wc, 201, kProducerSleepNs)) break;
+        const int key_tok = (int)my_scope[j / tiles_per_bucket] * a.bucket + (j % tiles_per_bucket) * BKV;
         unsigned char *sk = skv + s * C::kStageBytes, *sv = sk + C::kTileBytes;
         tc::mbar_expect_tx(&kv_full[s], C::kStageBytes);
 #pragma unroll
         for (int c = 0; c < C::NDCH; ++c) {
-          tc::tma_load_3d(sk + c * kBKV * C::RB, &map_k, &kv_full[s], c * C::DCH, head, brow * a.L + key_tok);
-          tc::tma_load_3d(sv + c * kBKV * C::RB, &map_v, &kv_full[s], c * C::DCH, head, brow * a.L + key_tok);
+          tc::tma_load_3d(sk + c * BKV * C::RB, &map_k, &kv_full[s], c * C::DCH, head, brow * a.L + key_tok);
+          tc::tma_load_3d(sv + c * BKV * C::RB, &map_v, &kv_full[s], c * C::DCH, head, brow * a.L + key_tok);
         }
       }
     }
   } else if (warp == 1) {
     if (tc::elect_one()) {
-      constexpr uint32_t idesc_s = tc::make_idesc_f16(kBQ, kBKV, true, false, false);
+      constexpr uint32_t idesc_s = tc::make_idesc_f16(kBQ, BKV, true, false, false);
       constexpr uint32_t idesc_o = tc::make_idesc_f16(kBQ, C::DCH, true, false, true);    // B (= V) is MN-major
-      const uint32_t s_tmem = tmem_base, o_tmem = tmem_base + C::kOCol;
-      bool ok = tc::mbar_wait(q_full, 0, wc, 202);
-      for (int j = 0; j < num_tiles && ok; ++j) {
-        const int s = j % kKvStages;
-        const uint32_t ph = (uint32_t)(j / kKvStages) & 1u;
-        if (!tc::mbar_wait(&kv_full[s], ph, wc, 203)) { ok = false; break; }
+      const uint32_t s_tmem = tmem_base, p_tmem = tmem_base + C::kPCol, o_tmem = tmem_base + C::kOCol;
+      const uint32_t q_addr = tc::smem_u32(sq);
+      // S_t = Q K_t^T: K-major operands, 8-row groups are 8*RB bytes apart
+      auto issue_s = [&](int t) -> bool {
+        const int s = t % kKvStages;
+        if (!tc::mbar_wait(&kv_full[s], (uint32_t)(t / kKvStages) & 1u, wc, 203)) return false;
         tc::tc_fence_after_sync();
-        const uint32_t q_addr = tc::smem_u32(sq), k_addr = tc::smem_u32(skv + s * C::kStageBytes);
-        const uint32_t v_addr = k_addr + C::kTileBytes;
-        // S = Q K^T: K-major operands, 8-row groups are 8*RB bytes apart
+        const uint32_t k_addr = tc::smem_u32(skv + s * C::kStageBytes);
 #pragma unroll
         for (int c = 0; c < C::NDCH; ++c) {
 #pragma unroll
           for (int kk = 0; kk < C::DCH / 16; ++kk) {
             uint64_t ad = tc::make_smem_desc(q_addr + c * kBQ * C::RB + kk * 32, 16, 8 * C::RB, C::SWZ);
-            uint64_t bd = tc::make_smem_desc(k_addr + c * kBKV * C::RB + kk * 32, 16, 8 * C::RB, C::SWZ);
+            uint64_t bd = tc::make_smem_desc(k_addr + c * BKV * C::RB + kk * 32, 16, 8 * C::RB, C::SWZ);
             tc::mma_f16_ss(s_tmem, ad, bd, idesc_s, (c | kk) != 0 ? 1u : 0u);
           }
         }
         tc::mma_commit(s_full);
-        // O += P V once the softmax warps have written P over the S columns
+        return true;
+      };
+      bool ok = tc::mbar_wait(q_full, 0, wc, 202) && issue_s(0);
+      for (int j = 0; j < num_tiles && ok; ++j) {
+        const int s = j % kKvStages;
+        if (j + 1 < num_tiles) {
+          // the next scores may overwrite S once every softmax thread has read tile j
+          if (!tc::mbar_wait(s_free, (uint32_t)j & 1u, wc, 208)) { ok = false; break; }
+          if (!issue_s(j + 1)) { ok = false; break; }
+        }
+        // O += P V once the softmax warps have written P
         if (!tc::mbar_wait(p_full, (uint32_t)j & 1u, wc, 204)) { ok = false; break; }
         tc::tc_fence_after_sync();
+        const uint32_t v_addr = tc::smem_u32(skv + s * C::kStageBytes) + C::kTileBytes;
 #pragma unroll
         for (int c = 0; c < C::NDCH; ++c) {
 #pragma unroll
-          for (int kk = 0; kk < kBKV / 16; ++kk) {
+          for (int kk = 0; kk < BKV / 16; ++kk) {
             // 16 keys per MMA: V rows kk*16.. ; P columns kk*8.. (two bf16 per 32-bit column)
-            uint64_t bd = tc::make_smem_desc(v_addr + c * kBKV * C::RB + kk * 16 * C::RB, 16, 8 * C::RB, C::SWZ);
-            tc::mma_f16_ts(o_tmem + c * C::DCH, s_tmem + kk * 8, bd, idesc_o, (j | kk) != 0 ? 1u : 0u);
+            uint64_t bd = tc::make_smem_desc(v_addr + c * BKV * C::RB + kk * 16 * C::RB, 16, 8 * C::RB, C::SWZ);
+            tc::mma_f16_ts(o_tmem + c * C::DCH, p_tmem + kk * 8, bd, idesc_o, (j | kk) != 0 ? 1u : 0u);
           }
         }
         tc::mma_commit(&kv_empty[s]);
@@ -188,8 +208,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const int q = warp & 3;
     const int row = q * 32 + lane;                              // query row inside the tile = tensor-memory lane
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
-    const uint32_t s_tmem = tmem_base + lane_off, o_tmem = tmem_base + C::kOCol + lane_off;
+    const uint32_t s_tmem = tmem_base + lane_off, p_tmem = tmem_base + C::kPCol + lane_off;
+    const uint32_t o_tmem = tmem_base + C::kOCol + lane_off;
     float m_run = -INFINITY, l_run = 0.f;
+    const uint64_t c2 = pack2(a.scale_log2, a.scale_log2);
     bool ok = true;
     for (int j = 0; j < num_tiles && ok; ++j) {
       if (!tc::mbar_wait(s_full, (uint32_t)j & 1u, wc, 205)) { ok = false; break; }
@@ -198,6 +220,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       tc::tmem_ld_32x32b_x32(s_tmem, r0);
       tc::tmem_ld_32x32b_x32(s_tmem + 32, r1);
       tc::tmem_ld_wait();
+      // the scores are in registers: the MMA warp may start the next tile's Q K^T over them
+      tc::tc_fence_before_sync();
+      tc::mbar_arrive(s_free);
       float mx = -INFINITY;
 #pragma unroll
       for (int i = 0; i < 32; ++i) mx = max3(mx, __uint_as_float(r0[i]), __uint_as_float(r1[i]));
@@ -205,48 +230,50 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const float alpha = fast_exp2(m_run - m_new);                 // 0 on the first tile (m_run = -inf)
       // x = s * c - m and the row sum run on packed fp32 pairs; the sum adds the unrounded probabilities (the
       // bf16 rounding of P is unbiased, so the normaliser stays consistent with what the MMA reads)
-      const uint64_t c2 = pack2(a.scale_log2, a.scale_log2), m2 = pack2(-m_new, -m_new);
+      const uint64_t m2 = pack2(-m_new, -m_new);
       uint64_t sum2 = pack2(0.f, 0.f);
       uint32_t p[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
+        const uint64_t xx = fma2(pack2(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1])), c2, m2);
         float x0, x1;
-        unpack2(fma2(pack2(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1])), c2, m2), x0, x1);
+        unpack2(xx, x0, x1);
         const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
         sum2 = add2(sum2, pack2(e0, e1));
-        __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
-        p[i] = *reinterpret_cast<uint32_t *>(&h);
+        __nv_bfloat162 hh = __floats2bfloat162_rn(e0, e1);
+        p[i] = *reinterpret_cast<uint32_t *>(&hh);
       }
-      tc::tmem_st_32x32b_x16(s_tmem, p);
+      if (j > 0) {
+        // P of the previous tile has been consumed and O is complete up to it: P may be overwritten, O rescaled
+        if (!tc::mbar_wait(o_full, (uint32_t)(j - 1) & 1u, wc, 206)) { ok = false; break; }
+        tc::tc_fence_after_sync();
+      }
+      tc::tmem_st_32x32b_x16(p_tmem, p);
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
+        const uint64_t xx = fma2(pack2(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1])), c2, m2);
         float x0, x1;
-        unpack2(fma2(pack2(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1])), c2, m2), x0, x1);
+        unpack2(xx, x0, x1);
         const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
         sum2 = add2(sum2, pack2(e0, e1));
-        __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
-        p[i] = *reinterpret_cast<uint32_t *>(&h);
+        __nv_bfloat162 hh = __floats2bfloat162_rn(e0, e1);
+        p[i] = *reinterpret_cast<uint32_t *>(&hh);
       }
-      tc::tmem_st_32x32b_x16(s_tmem + 16, p);
+      tc::tmem_st_32x32b_x16(p_tmem + 16, p);
       float sum, sum_hi;
       unpack2(sum2, sum, sum_hi);
       sum += sum_hi;
       l_run = l_run * alpha + sum;
       m_run = m_new;
-      if (j > 0) {
-        // O of the previous tiles must be complete before it is rescaled
-        if (!tc::mbar_wait(o_full, (uint32_t)(j - 1) & 1u, wc, 206)) { ok = false; break; }
-        tc::tc_fence_after_sync();
-        if (__any_sync(0xFFFFFFFFu, alpha != 1.f)) {
+      if (j > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.f)) {
 #pragma unroll
-          for (int c = 0; c < D; c += 16) {
-            uint32_t o[16];
-            tc::tmem_ld_32x32b_x16(o_tmem + c, o);
-            tc::tmem_ld_wait();
+        for (int c = 0; c < D; c += 16) {
+          uint32_t o[16];
+          tc::tmem_ld_32x32b_x16(o_tmem + c, o);
+          tc::tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tc::tmem_st_32x32b_x16(o_tmem + c, o);
-          }
+          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tc::tmem_st_32x32b_x16(o_tmem + c, o);
         }
       }
       tc::tmem_st_wait();
@@ -283,11 +310,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   if (warp == 1) { tc::tc_fence_after_sync(); tc::tmem_dealloc(tmem_base, C::kTmemCols); }
 }
 
-template <int D>
+template <int D, int BKV>
 static int launch_attn_fwd(const void *Q, const void *K, const void *V, AttnFwdArgs a, int device, cudaStream_t st) {
-  using C = AttnCfg<D>;
+  using C = AttnCfg<D, BKV>;
   static bool attr[16] = {false};
-  auto kern = attn_fwd_kernel<D>;
+  auto kern = attn_fwd_kernel<D, BKV>;
   if (device < 16 && !attr[device]) {
     F3D_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem));
     attr[device] = true;
@@ -296,8 +323,8 @@ static int launch_attn_fwd(const void *Q, const void *K, const void *V, AttnFwdA
   const uint64_t rows = (uint64_t)a.B * a.L;
   const uint64_t s1 = (uint64_t)D * 2, s2 = (uint64_t)a.H * D * 2;
   F3D_TRY(encode_tmap_3d(&mq, 0, Q, D, a.H, rows, s1, s2, C::DCH, 1, kBQ, C::RB));
-  F3D_TRY(encode_tmap_3d(&mk, 0, K, D, a.H, rows, s1, s2, C::DCH, 1, kBKV, C::RB));
-  F3D_TRY(encode_tmap_3d(&mv, 0, V, D, a.H, rows, s1, s2, C::DCH, 1, kBKV, C::RB));
+  F3D_TRY(encode_tmap_3d(&mk, 0, K, D, a.H, rows, s1, s2, C::DCH, 1, BKV, C::RB));
+  F3D_TRY(encode_tmap_3d(&mv, 0, V, D, a.H, rows, s1, s2, C::DCH, 1, BKV, C::RB));
   dim3 grid(a.num_scopes * a.k * a.q_blocks_per_bucket, a.H, a.B);
   kern<<<grid, kAttnThreads, C::kSmem, st>>>(mq, mk, mv, a);
   return check_launch("buck_swin_fwd");
@@ -326,10 +353,10 @@ extern "C" int f3d_buck_swin_fwd(const void *Q, const void *K, const void *V, vo
   if (!a.status) return F3D_ERR_CUDA;
   int rc;
   switch (D) {
-    case 16: rc = launch_attn_fwd<16>(Q, K, V, a, device, st); break;
-    case 32: rc = launch_attn_fwd<32>(Q, K, V, a, device, st); break;
-    case 64: rc = launch_attn_fwd<64>(Q, K, V, a, device, st); break;
-    default: rc = launch_attn_fwd<128>(Q, K, V, a, device, st); break;
+    case 16: rc = launch_attn_fwd<16, 64>(Q, K, V, a, device, st); break;
+    case 32: rc = launch_attn_fwd<32, 64>(Q, K, V, a, device, st); break;
+    case 64: rc = launch_attn_fwd<64, 64>(Q, K, V, a, device, st); break;
+    default: rc = launch_attn_fwd<128, 64>(Q, K, V, a, device, st); break;
   }
   F3D_TRY(rc);
   return maybe_sync(st, "buck_swin_fwd");

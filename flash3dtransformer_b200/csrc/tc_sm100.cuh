@@ -56,11 +56,14 @@ struct WaitCtx {
 };
 
 // Returns false when the wait was abandoned.  `code` identifies the waiting site in the status word.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, const WaitCtx &ctx, int code) {
+// `sleep_ns` > 0 puts the thread to sleep between polls: for waits with slack (a producer running stages ahead),
+// so that the polling loop does not take issue slots from the warps doing arithmetic.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, const WaitCtx &ctx, int code, uint32_t sleep_ns = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = globaltimer();
   uint32_t polls = 0;
   while (true) {
+    if (sleep_ns) __nanosleep(sleep_ns);
     if (mbar_try_wait(bar, parity)) return true;
     if ((++polls & 63u) == 0u) {
       if (*ctx.abort_flag) return false;
