@@ -4,11 +4,11 @@
 // flash3dxfmr/layers/buck_swin.py:159,163,185-194) and the toy mma.sync kernel gemm_sm_bf16_ker
 // (src/psh/gemm.cuh:30-85, host src/psh/gemm_dispatcher.cu:26-80, which demands M == 128 and synchronises).
 //
-// Structure (one persistent CTA per SM, 320 threads):
+// Structure (one persistent CTA per SM, 576 threads):
 //   warp 0      TMA producer: A tile 128x64 and W tile BNx64 per stage, 128-byte swizzle, mbarrier completion
 //   warp 1      owns tensor memory; one elected lane issues tcgen05.mma (M=128, N=BN, K=16) four times per
 //               stage and commits the stage's "empty" barrier; after the last k-block it commits "accumulator full"
-//   warps 2-9   epilogue: two warps per 32-lane quadrant of the 128xBN fp32 accumulator; a warp takes 32 columns at
+//   warps 2-17  epilogue: four warps per 32-lane quadrant of the 128xBN fp32 accumulator; a warp takes 32 columns at
 //               a time (tcgen05.ld), adds bias / residual, applies GELU / SwiGLU, converts to bf16, stages the
 //               32x32 block in swizzled shared memory and writes it with a TMA store
 // Up to four accumulators (at most 512 tensor-memory columns) let the epilogues of earlier tiles overlap the MMAs of
@@ -22,7 +22,8 @@
 
 namespace f3d {
 
-constexpr int kGemmThreads = 320;     // TMA warp, MMA warp, 8 epilogue warps
+constexpr int kEpiWarps = 16;         // four per tensor-memory lane quadrant
+constexpr int kGemmThreads = 64 + 32 * kEpiWarps;     // TMA warp, MMA warp, epilogue warps
 constexpr int BM = 128;
 constexpr int BK = 64;
 
@@ -47,7 +48,7 @@ template <int BN> struct GemmSmem {
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kOutBytes = 8 /*warps*/ * 2 /*buffers*/ * 32 * 64;    // 32 rows x 32 bf16 per buffer
+  static constexpr int kOutBytes = kEpiWarps * 2 /*buffers*/ * 32 * 64;    // 32 rows x 32 bf16 per buffer
   static constexpr int kAcc = BN >= 256 ? 2 : 4;        // accumulator buffers in tensor memory (kAcc * BN <= 512 columns)
   static constexpr int kBarBytes = 256;
   static constexpr int kTotal = kStages * kStageBytes + kOutBytes + kBarBytes + 1024 /*alignment slack*/;
@@ -57,6 +58,15 @@ __device__ __forceinline__ float gelu_tanh(float x) {
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;
   float u = k0 * (x + k1 * x * x * x);
   return 0.5f * x * (1.f + tanhf(u));
+}
+
+// x * sigmoid(x) with one special-function instruction: sigmoid(x) = 0.5 + 0.5 * tanh(x / 2); tanh.approx has a
+// relative error near 5e-4, an order of magnitude below the bf16 rounding of the result.
+__device__ __forceinline__ float silu_fast(float x) {
+  const float h = 0.5f * x;
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(h));
+  return fmaf(h, t, h);
 }
 
 template <int BN>
@@ -83,7 +93,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { tc::mbar_init(&full[s], 1); tc::mbar_init(&empty[s], 1); }
-    for (int a = 0; a < kAcc; ++a) { tc::mbar_init(&acc_full[a], 1); tc::mbar_init(&acc_empty[a], 8); }
+    for (int a = 0; a < kAcc; ++a) { tc::mbar_init(&acc_full[a], 1); tc::mbar_init(&acc_empty[a], kEpiWarps); }
     *abort_flag = 0;
     tc::mbar_fence_init();
   }
@@ -142,13 +152,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       }
     }
   } else {
-    // 8 epilogue warps: two per tensor-memory lane quadrant.  A task is 32 output columns of the warp's 32 rows;
-    // the two warps of a quadrant take alternate tasks, so every scheduler of the SM has two epilogue warps to
-    // interleave (with one, the loop was bound by instruction latency).
+    // 16 epilogue warps: four per tensor-memory lane quadrant.  A task is 32 output columns of the warp's 32
+    // rows; the tasks of a quadrant are numbered across tiles and dealt round-robin to its four warps, so narrow
+    // tiles (one or two tasks) still keep all warps busy, each on a different accumulator buffer.
     const int q = warp & 3;                       // tensor-memory lane quadrant this warp may read
-    const int half = (warp - 2) >> 2;             // 0 or 1: which of the quadrant's two warps
+    const uint32_t sub = (uint32_t)(warp - 2) >> 2;     // which of the quadrant's warps
+    constexpr uint32_t kSub = kEpiWarps / 4;
     unsigned char *my_out = out_base + (warp - 2) * 2 * 32 * 64;
-    uint32_t t_local = 0, obuf = 0;
+    uint32_t t_local = 0, obuf = 0, task = 0;
     bool ok = true;
     const int out_cols = g.epilogue == EPI_SWIGLU ? BN / 2 : BN;     // output columns produced per tile
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t_local) {
@@ -158,7 +169,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       tc::tc_fence_after_sync();
       const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
       const int row = m0 + q * 32 + lane;
-      for (int c0 = half * 32; c0 < out_cols; c0 += 64) {
+      for (int c0 = 0; c0 < out_cols; c0 += 32, ++task) {
+        if (task % kSub != sub) continue;
         float v[32];
         const int oc0 = (g.epilogue == EPI_SWIGLU ? n0 / 2 : n0) + c0;      // first output column of the task
         // runtime switches (bias, activation) are tested once per task, never per element
@@ -177,14 +189,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
                 const float gt = __uint_as_float(r[4 * j + e]) + bg[e], up = __uint_as_float(u[4 * j + e]) + bu[e];
-                v[4 * j + e] = __fdividef(gt, 1.f + __expf(-gt)) * up;
+                v[4 * j + e] = silu_fast(gt) * up;
               }
             }
           } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               const float gt = __uint_as_float(r[j]), up = __uint_as_float(u[j]);
-              v[j] = __fdividef(gt, 1.f + __expf(-gt)) * up;
+              v[j] = silu_fast(gt) * up;
             }
           }
         } else {
