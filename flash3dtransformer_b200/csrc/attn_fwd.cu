@@ -223,9 +223,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       // the scores are in registers: the MMA warp may start the next tile's Q K^T over them
       tc::tc_fence_before_sync();
       tc::mbar_arrive(s_free);
-      float mx = -INFINITY;
+      // four independent chains of 3-input maxima instead of one 32 deep
+      float mxa = -INFINITY, mxb = -INFINITY, mxc = -INFINITY, mxd = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) mx = max3(mx, __uint_as_float(r0[i]), __uint_as_float(r1[i]));
+      for (int i = 0; i < 32; i += 4) {
+        mxa = max3(mxa, __uint_as_float(r0[i]), __uint_as_float(r1[i]));
+        mxb = max3(mxb, __uint_as_float(r0[i + 1]), __uint_as_float(r1[i + 1]));
+        mxc = max3(mxc, __uint_as_float(r0[i + 2]), __uint_as_float(r1[i + 2]));
+        mxd = max3(mxd, __uint_as_float(r0[i + 3]), __uint_as_float(r1[i + 3]));
+      }
+      const float mx = fmaxf(max3(mxa, mxb, mxc), mxd);
       const float m_new = fmaxf(m_run, mx * a.scale_log2);
       const float alpha = fast_exp2(m_run - m_new);                 // 0 on the first tile (m_run = -inf)
       // x = s * c - m and the row sum run on packed fp32 pairs; the sum adds the unrounded probabilities (the
