@@ -28,7 +28,7 @@ namespace f3d {
 
 int *status_word(int device);
 
-constexpr int kBwdThreads = 320;       // producer warp, MMA warp, 8 compute warps
+constexpr int kBwdThreads = 448;       // producer warp, MMA warp, 8 compute warps, 4 dQ read-out warps
 constexpr int kBK = 128;               // keys per CTA (tensor-memory lanes)
 
 struct AttnBwdArgs {
@@ -43,6 +43,28 @@ __device__ __forceinline__ float bwd_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// packed fp32 pairs
+__device__ __forceinline__ uint64_t bpack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void bunpack2(uint64_t v, float &lo, float &hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t bfma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t badd2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t bmul2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
 
 template <int D> struct BwdCfg {
   static constexpr int BQ = D == 128 ? 64 : 128;                 // queries per inner tile
@@ -53,14 +75,15 @@ template <int D> struct BwdCfg {
   static constexpr int kKVBytes = kBK * D * 2;                   // one of K_j, V_j
   static constexpr int kQBytes = BQ * D * 2;                     // one of Q_i, dO_i
   static constexpr int kQStage = 2 * kQBytes;
-  static constexpr int QCH = BQ / 64 ? BQ / 64 : 1;              // 64-query column chunks of the P^T / dS^T tiles
+  static constexpr int QS = D <= 32 ? 3 : 2;                     // Q / dO stages
+  static constexpr int PB = D == 64 ? 1 : 2;                     // P^T / dS^T shared-memory buffers (what fits in 227 KB)
   static constexpr int kPBytes = kBK * BQ * 2;                   // P^T or dS^T tile
   static constexpr int kLsdBytes = 2 /*stages*/ * 2 * BQ * 4;
-  static constexpr int kSmem = 2 * kKVBytes + 2 * kQStage + 2 * kPBytes + kLsdBytes + 256 + 1024;
-  // tensor-memory columns: S^T, dP^T, dV, dK, dQ (dQ shares the S^T columns when 512 would be exceeded)
-  static constexpr bool kAliasDq = (2 * BQ + 3 * D) > 512;
-  static constexpr uint32_t kSCol = 0, kDpCol = BQ, kDvCol = 2 * BQ, kDkCol = 2 * BQ + D;
-  static constexpr uint32_t kDqCol = kAliasDq ? 0 : 2 * BQ + 2 * D;
+  static constexpr int kSmem = 2 * kKVBytes + QS * kQStage + PB * 2 * kPBytes + kLsdBytes + 256 + 1024;
+  static_assert(kSmem <= 227 * 1024, "shared memory budget");
+  // tensor-memory columns: S^T, dP^T, dV, dK, dQ
+  static constexpr uint32_t kSCol = 0, kDpCol = BQ, kDvCol = 2 * BQ, kDkCol = 2 * BQ + D, kDqCol = 2 * BQ + 2 * D;
+  static_assert(2 * BQ + 3 * D <= 512, "tensor-memory budget");
 };
 
 template <int D>
@@ -68,20 +91,20 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, AttnBwdArgs a) {
   using C = BwdCfg<D>;
-  constexpr int BQ = C::BQ;
+  constexpr int BQ = C::BQ, QS = C::QS, PB = C::PB;
   extern __shared__ unsigned char smem_raw[];
   unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char *sk = smem, *sv = sk + C::kKVBytes;
-  unsigned char *sqdo = sv + C::kKVBytes;                         // [2 stages][Q | dO]
-  // dS^T sits in front of P^T: with 64-query tiles the dQ MMA (M = 128) reads one 64-row atom past the dS^T tile,
-  // which then falls inside the P^T tile (rows 64..127 of that product are never used)
-  unsigned char *sds = sqdo + 2 * C::kQStage, *spt = sds + C::kPBytes;
-  float *slsd = reinterpret_cast<float *>(spt + C::kPBytes);      // [stage][lse2 | delta][BQ]
+  unsigned char *sqdo = sv + C::kKVBytes;                         // [QS stages][Q | dO]
+  // per buffer dS^T sits in front of P^T: with 64-query tiles the dQ MMA (M = 128) reads one 64-row atom past the
+  // dS^T tile, which then falls inside the P^T tile of the same buffer (rows 64..127 of that product are never used)
+  unsigned char *spds = sqdo + QS * C::kQStage;                   // [PB buffers][dS^T | P^T]
+  float *slsd = reinterpret_cast<float *>(spds + PB * 2 * C::kPBytes);      // [stage][-lse2 | -delta][BQ]
   uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<unsigned char *>(slsd) + C::kLsdBytes);
-  uint64_t *kv_full = bars, *qdo_full = bars + 1, *qdo_empty = bars + 3, *s_full = bars + 5, *dp_full = bars + 6;
-  uint64_t *pds_full = bars + 7, *pds_empty = bars + 8, *dq_full = bars + 9, *dq_read = bars + 10, *dkv_full = bars + 11;
-  uint64_t *lsd_full = bars + 12;                                 // [2]
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 14);
+  uint64_t *kv_full = bars, *qdo_full = bars + 1, *qdo_empty = qdo_full + QS, *s_full = qdo_empty + QS, *dp_full = s_full + 1;
+  uint64_t *pds_full = dp_full + 1, *pds_empty = pds_full + 1 /*[PB]*/, *dq_full = pds_empty + PB, *dq_read = dq_full + 1;
+  uint64_t *dkv_full = dq_read + 1, *lsd_full = dkv_full + 1 /*[2]*/;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(lsd_full + 2);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -97,9 +120,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 
   if (threadIdx.x == 0) {
     tc::mbar_init(kv_full, 1);
-    for (int s = 0; s < 2; ++s) { tc::mbar_init(&qdo_full[s], 1); tc::mbar_init(&qdo_empty[s], 1); }
-    tc::mbar_init(s_full, 1); tc::mbar_init(dp_full, 1); tc::mbar_init(pds_full, 256); tc::mbar_init(pds_empty, 1);
-    tc::mbar_init(dq_full, 1); tc::mbar_init(dq_read, 256); tc::mbar_init(dkv_full, 1);
+    for (int s = 0; s < QS; ++s) { tc::mbar_init(&qdo_full[s], 1); tc::mbar_init(&qdo_empty[s], 1); }
+    tc::mbar_init(s_full, 1); tc::mbar_init(dp_full, 1); tc::mbar_init(pds_full, 256);
+    for (int b = 0; b < PB; ++b) tc::mbar_init(&pds_empty[b], 1);
+    tc::mbar_init(dq_full, 1); tc::mbar_init(dq_read, 128); tc::mbar_init(dkv_full, 1);
     tc::mbar_init(&lsd_full[0], BQ); tc::mbar_init(&lsd_full[1], BQ);
     *abort_flag = 0;
     tc::mbar_fence_init();
@@ -121,9 +145,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         tc::tma_load_3d(sv + c * kBK * C::RB, &map_v, kv_full, c * C::DCH, head, brow * a.L + key_tok);
       }
       for (int i = 0; i < num_qtiles; ++i) {
-        const int s = i & 1;
-        const uint32_t ph = (uint32_t)(i >> 1) & 1u;
-        if (!tc::mbar_wait(&qdo_empty[s], ph ^ 1u, wc, 301)) break;
+        const int s = i % QS;
+        const uint32_t ph = (uint32_t)(i / QS) & 1u;
+        if (!tc::mbar_wait(&qdo_empty[s], ph ^ 1u, wc, 301, 200)) break;
         const int q_tok = (int)my_scope[i / qtiles_per_bucket] * a.bucket + (i % qtiles_per_bucket) * BQ;
         unsigned char *sq = sqdo + s * C::kQStage, *sdo = sq + C::kQBytes;
         tc::mbar_expect_tx(&qdo_full[s], C::kQStage);
@@ -140,14 +164,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       constexpr uint32_t idesc_kv = tc::make_idesc_f16(kBK, C::DCH, true, false, true);      // dV, dK: B MN-major
       constexpr uint32_t idesc_dq = tc::make_idesc_f16(128, C::DCH, true, true, true);       // dQ: A and B MN-major
       const uint32_t k_addr = tc::smem_u32(sk), v_addr = tc::smem_u32(sv);
-      const uint32_t pt_addr = tc::smem_u32(spt), ds_addr = tc::smem_u32(sds);
       bool ok = tc::mbar_wait(kv_full, 0, wc, 302);
 
       auto issue_s_dp = [&](int i) -> bool {
-        const int s = i & 1;
-        const uint32_t ph = (uint32_t)(i >> 1) & 1u;
-        if (!tc::mbar_wait(&qdo_full[s], ph, wc, 303)) return false;
-        if (C::kAliasDq && i > 0 && !tc::mbar_wait(dq_read, (uint32_t)(i - 1) & 1u, wc, 304)) return false;
+        const int s = i % QS;
+        if (!tc::mbar_wait(&qdo_full[s], (uint32_t)(i / QS) & 1u, wc, 303)) return false;
         tc::tc_fence_after_sync();
         const uint32_t q_addr = tc::smem_u32(sqdo + s * C::kQStage), do_addr = q_addr + C::kQBytes;
 #pragma unroll
@@ -169,10 +190,26 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 
       if (ok) ok = issue_s_dp(0);
       for (int i = 0; i < num_qtiles && ok; ++i) {
-        const int s = i & 1;
+        const int s = i % QS, pb = i % PB;
+        // P^T and dS^T of tile i are in shared memory, and every compute thread has read S^T and dP^T
         if (!tc::mbar_wait(pds_full, (uint32_t)i & 1u, wc, 305)) { ok = false; break; }
+        // the next tile's scores first: the compute warps work on them while the tensor pipe runs this tile's
+        // three gradient products
+        if (i + 1 < num_qtiles && !issue_s_dp(i + 1)) { ok = false; break; }
         tc::tc_fence_after_sync();
         const uint32_t q_addr = tc::smem_u32(sqdo + s * C::kQStage), do_addr = q_addr + C::kQBytes;
+        const uint32_t ds_addr = tc::smem_u32(spds + pb * 2 * C::kPBytes), pt_addr = ds_addr + C::kPBytes;
+        // dQ_i = dS K_j: A = the dS^T tile read M-major (queries contiguous), K = keys in steps of 16 rows
+        if (i > 0 && !tc::mbar_wait(dq_read, (uint32_t)(i - 1) & 1u, wc, 306)) { ok = false; break; }
+        tc::tc_fence_after_sync();
+#pragma unroll
+        for (int c = 0; c < C::NDCH; ++c)
+#pragma unroll
+          for (int ks = 0; ks < kBK / 16; ++ks)
+            tc::mma_f16_ss(tmem_base + C::kDqCol + c * C::DCH,
+                           tc::make_smem_desc(ds_addr + ks * 16 * 128, kBK * 128, 1024, tc::kSwizzle128),
+                           tc::make_smem_desc(k_addr + c * kBK * C::RB + ks * 16 * C::RB, 16, 8 * C::RB, C::SWZ), idesc_dq, ks != 0);
+        tc::mma_commit(dq_full);
         // dV += P^T dO and dK += dS^T Q: A = [keys x queries] tiles in shared memory (128-byte rows of 64 queries)
 #pragma unroll
         for (int c = 0; c < C::NDCH; ++c) {
@@ -187,53 +224,36 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           }
         }
         tc::mma_commit(&qdo_empty[s]);
-        // dQ_i = dS K_j: A = the dS^T tile read M-major (queries contiguous), K = keys in steps of 16 rows
-        if (i > 0 && !C::kAliasDq && !tc::mbar_wait(dq_read, (uint32_t)(i - 1) & 1u, wc, 306)) { ok = false; break; }
-        tc::tc_fence_after_sync();
-#pragma unroll
-        for (int c = 0; c < C::NDCH; ++c)
-#pragma unroll
-          for (int ks = 0; ks < kBK / 16; ++ks)
-            tc::mma_f16_ss(tmem_base + C::kDqCol + c * C::DCH,
-                           tc::make_smem_desc(ds_addr + ks * 16 * 128, kBK * 128, 1024, tc::kSwizzle128),
-                           tc::make_smem_desc(k_addr + c * kBK * C::RB + ks * 16 * C::RB, 16, 8 * C::RB, C::SWZ), idesc_dq, ks != 0);
-        tc::mma_commit(pds_empty);
-        tc::mma_commit(dq_full);
-        if (i + 1 < num_qtiles) {
-          if (C::kAliasDq) {
-            // S^T of the next tile overwrites the dQ columns: it is issued after the compute warps have read them
-            ok = issue_s_dp(i + 1);
-          } else {
-            ok = issue_s_dp(i + 1);
-          }
-        } else {
-          tc::mma_commit(dkv_full);
-        }
+        tc::mma_commit(&pds_empty[pb]);
+        if (i + 1 == num_qtiles) tc::mma_commit(dkv_full);
       }
     }
-  } else {
+  } else if (warp < 10) {
     const int cw = warp - 2;                          // 0..7
     const int q4 = warp & 3;                          // tensor-memory lane quadrant of this warp
     const int wg = cw >> 2;                           // which half of the columns
     const int ctid = cw * 32 + lane;                  // 0..255
-    const int row = q4 * 32 + lane;                   // key row (S^T, dP^T, dK, dV) or query row (dQ)
+    const int row = q4 * 32 + lane;                   // key row (S^T, dP^T, dK, dV)
     const uint32_t lane_off = (uint32_t)(q4 * 32) << 16;
     constexpr int HALF = BQ / 2;                      // query columns per compute thread
+    const uint64_t c2 = bpack2(a.scale_log2, a.scale_log2);
     bool ok = true;
     for (int i = 0; i < num_qtiles && ok; ++i) {
-      const int s = i & 1;
+      const int s2 = i & 1, pb = i % PB;
       const int q_tok = (int)my_scope[i / qtiles_per_bucket] * a.bucket + (i % qtiles_per_bucket) * BQ;
-      float *lse2 = slsd + s * 2 * BQ, *dl = lse2 + BQ;
+      const uint32_t nlse2 = tc::smem_u32(slsd + s2 * 2 * BQ), ndl = nlse2 + BQ * 4;       // negated: used as addends
       if (ctid < BQ) {
         const size_t idx = ((size_t)brow * a.L + q_tok + ctid) * a.H + head;
-        lse2[ctid] = a.lse[idx] * 1.4426950408889634f;
-        dl[ctid] = a.delta[idx];
-        tc::mbar_arrive(&lsd_full[s]);
+        tc::sts32(nlse2 + ctid * 4, a.lse[idx] * -1.4426950408889634f);
+        tc::sts32(ndl + ctid * 4, -a.delta[idx]);
+        tc::mbar_arrive(&lsd_full[s2]);
       }
-      if (!tc::mbar_wait(&lsd_full[s], (uint32_t)(i >> 1) & 1u, wc, 312)) { ok = false; break; }
+      if (!tc::mbar_wait(&lsd_full[s2], (uint32_t)(i >> 1) & 1u, wc, 312)) { ok = false; break; }
       if (!tc::mbar_wait(s_full, (uint32_t)i & 1u, wc, 307) || !tc::mbar_wait(dp_full, (uint32_t)i & 1u, wc, 308)) { ok = false; break; }
-      if (i > 0 && !tc::mbar_wait(pds_empty, (uint32_t)(i - 1) & 1u, wc, 309)) { ok = false; break; }
+      // the MMAs that read this shared-memory buffer (tile i - PB) must have finished
+      if (i >= PB && !tc::mbar_wait(&pds_empty[pb], (uint32_t)(i / PB - 1) & 1u, wc, 309)) { ok = false; break; }
       tc::tc_fence_after_sync();
+      const uint32_t sds = tc::smem_u32(spds + pb * 2 * C::kPBytes), spt = sds + C::kPBytes;
 #pragma unroll
       for (int ch = 0; ch < HALF / 32; ++ch) {
         const int col0 = wg * HALF + ch * 32;
@@ -241,50 +261,39 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         tc::tmem_ld_32x32b_x32(tmem_base + lane_off + C::kSCol + col0, sr);
         tc::tmem_ld_32x32b_x32(tmem_base + lane_off + C::kDpCol + col0, dr);
         tc::tmem_ld_wait();
-        unsigned char *prow = spt + (col0 / 64) * (kBK * 128) + row * 128;
-        unsigned char *drow = sds + (col0 / 64) * (kBK * 128) + row * 128;
+        const uint32_t prow = spt + (col0 / 64) * (kBK * 128) + row * 128;
+        const uint32_t drow = sds + (col0 / 64) * (kBK * 128) + row * 128;
 #pragma unroll
         for (int v8 = 0; v8 < 4; ++v8) {
           uint4 pw, dw;
-          __nv_bfloat162 *ph2 = reinterpret_cast<__nv_bfloat162 *>(&pw), *dh2 = reinterpret_cast<__nv_bfloat162 *>(&dw);
-          const float4 l0 = *reinterpret_cast<const float4 *>(lse2 + col0 + v8 * 8), l1 = *reinterpret_cast<const float4 *>(lse2 + col0 + v8 * 8 + 4);
-          const float4 d0 = *reinterpret_cast<const float4 *>(dl + col0 + v8 * 8), d1 = *reinterpret_cast<const float4 *>(dl + col0 + v8 * 8 + 4);
-          const float ls[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
-          const float dd[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
-          float p[8], g[8];
+          uint32_t *pw32 = reinterpret_cast<uint32_t *>(&pw), *dw32 = reinterpret_cast<uint32_t *>(&dw);
+          // -lse2 and -delta of 8 queries (the same for every key row: broadcast reads)
+          uint64_t nl[4], nd[4];
+          tc::lds64x2(nlse2 + (col0 + v8 * 8) * 4, nl[0], nl[1]);
+          tc::lds64x2(nlse2 + (col0 + v8 * 8 + 4) * 4, nl[2], nl[3]);
+          tc::lds64x2(ndl + (col0 + v8 * 8) * 4, nd[0], nd[1]);
+          tc::lds64x2(ndl + (col0 + v8 * 8 + 4) * 4, nd[2], nd[3]);
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            p[e] = bwd_exp2(fmaf(__uint_as_float(sr[v8 * 8 + e]), a.scale_log2, -ls[e]));
-            g[e] = p[e] * (__uint_as_float(dr[v8 * 8 + e]) - dd[e]);
+          for (int e = 0; e < 4; ++e) {
+            // p = 2^(s c - lse2), ds = p (dp - delta), two queries per instruction
+            float x0, x1;
+            bunpack2(bfma2(bpack2(__uint_as_float(sr[v8 * 8 + 2 * e]), __uint_as_float(sr[v8 * 8 + 2 * e + 1])), c2, nl[e]), x0, x1);
+            const float p0 = bwd_exp2(x0), p1 = bwd_exp2(x1);
+            const uint64_t t = badd2(bpack2(__uint_as_float(dr[v8 * 8 + 2 * e]), __uint_as_float(dr[v8 * 8 + 2 * e + 1])), nd[e]);
+            float g0, g1;
+            bunpack2(bmul2(bpack2(p0, p1), t), g0, g1);
+            const __nv_bfloat162 ph = __floats2bfloat162_rn(p0, p1), gh = __floats2bfloat162_rn(g0, g1);
+            pw32[e] = *reinterpret_cast<const uint32_t *>(&ph);
+            dw32[e] = *reinterpret_cast<const uint32_t *>(&gh);
           }
-#pragma unroll
-          for (int e = 0; e < 4; ++e) { ph2[e] = __floats2bfloat162_rn(p[2 * e], p[2 * e + 1]); dh2[e] = __floats2bfloat162_rn(g[2 * e], g[2 * e + 1]); }
           const int chunk16 = ((col0 % 64) / 8 + v8) ^ (row & 7);
-          *reinterpret_cast<uint4 *>(prow + chunk16 * 16) = pw;
-          *reinterpret_cast<uint4 *>(drow + chunk16 * 16) = dw;
+          tc::sts128(prow + chunk16 * 16, pw);
+          tc::sts128(drow + chunk16 * 16, dw);
         }
       }
       tc::fence_proxy_async();
       tc::tc_fence_before_sync();
       tc::mbar_arrive(pds_full);
-      // dQ_i: queries on the lanes; this warpgroup takes half of the D columns
-      if (!tc::mbar_wait(dq_full, (uint32_t)i & 1u, wc, 310)) { ok = false; break; }
-      tc::tc_fence_after_sync();
-      if (row < BQ && q_tok + row < a.L) {
-        float *dst = a.dq_acc + (((size_t)brow * a.L + q_tok + row) * a.H + head) * D + wg * (D / 2);
-#pragma unroll
-        for (int c = 0; c < D / 2; c += 8) {
-          uint32_t o[8];
-          asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                       : "=r"(o[0]), "=r"(o[1]), "=r"(o[2]), "=r"(o[3]), "=r"(o[4]), "=r"(o[5]), "=r"(o[6]), "=r"(o[7])
-                       : "r"(tmem_base + lane_off + C::kDqCol + wg * (D / 2) + c) : "memory");
-          tc::tmem_ld_wait();
-          atomicAdd(reinterpret_cast<float4 *>(dst + c), make_float4(__uint_as_float(o[0]), __uint_as_float(o[1]), __uint_as_float(o[2]), __uint_as_float(o[3])));
-          atomicAdd(reinterpret_cast<float4 *>(dst + c + 4), make_float4(__uint_as_float(o[4]), __uint_as_float(o[5]), __uint_as_float(o[6]), __uint_as_float(o[7])));
-        }
-      }
-      tc::tc_fence_before_sync();
-      tc::mbar_arrive(dq_read);
     }
     if (ok && tc::mbar_wait(dkv_full, 0, wc, 311) && key_tok + row < a.L) {
       tc::tc_fence_after_sync();
@@ -309,6 +318,32 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         *reinterpret_cast<uint4 *>(a.dK + base + c) = kw;
         *reinterpret_cast<uint4 *>(a.dV + base + c) = vw;
       }
+    }
+  } else {
+    // dQ read-out warps: queries on the lanes, one warp per lane quadrant; each tile's product is added to the
+    // fp32 scratch with vector reductions while the compute warps are already on the next tile
+    const int q4 = warp & 3;
+    const int row = q4 * 32 + lane;                   // query row of the tile
+    const uint32_t lane_off = (uint32_t)(q4 * 32) << 16;
+    for (int i = 0; i < num_qtiles; ++i) {
+      const int q_tok = (int)my_scope[i / qtiles_per_bucket] * a.bucket + (i % qtiles_per_bucket) * BQ;
+      if (!tc::mbar_wait(dq_full, (uint32_t)i & 1u, wc, 310)) break;
+      tc::tc_fence_after_sync();
+      float *dst = a.dq_acc + (((size_t)brow * a.L + q_tok + row) * a.H + head) * D;
+      const bool live = row < BQ && q_tok + row < a.L;
+#pragma unroll
+      for (int c = 0; c < D; c += 16) {
+        uint32_t o[16];
+        tc::tmem_ld_32x32b_x16(tmem_base + lane_off + C::kDqCol + c, o);
+        tc::tmem_ld_wait();
+        if (live) {
+#pragma unroll
+          for (int e = 0; e < 16; e += 4)
+            atomicAdd(reinterpret_cast<float4 *>(dst + c + e), make_float4(__uint_as_float(o[e]), __uint_as_float(o[e + 1]), __uint_as_float(o[e + 2]), __uint_as_float(o[e + 3])));
+        }
+      }
+      tc::tc_fence_before_sync();
+      tc::mbar_arrive(dq_read);
     }
   }
 

@@ -269,7 +269,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           __nv_bfloat162 *h2 = reinterpret_cast<__nv_bfloat162 *>(&w);
 #pragma unroll
           for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(v[j * 8 + 2 * e], v[j * 8 + 2 * e + 1]);
-          *reinterpret_cast<uint4 *>(ob + lane * 64 + ((j ^ ((lane >> 1) & 3)) * 16)) = w;
+          tc::sts128(tc::smem_u32(ob) + lane * 64 + ((j ^ ((lane >> 1) & 3)) * 16), w);
         }
         tc::fence_proxy_async();
         __syncwarp();
