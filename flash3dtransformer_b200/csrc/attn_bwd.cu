@@ -28,7 +28,8 @@ namespace f3d {
 
 int *status_word(int device);
 
-constexpr int kBwdThreads = 448;       // producer warp, MMA warp, 8 compute warps, 4 dQ read-out warps
+constexpr int kBwdComputeWarps = 16;
+constexpr int kBwdThreads = 64 + 32 * kBwdComputeWarps;       // producer warp, MMA warp, compute warps
 constexpr int kBK = 128;               // keys per CTA (tensor-memory lanes)
 
 struct AttnBwdArgs {
@@ -78,12 +79,18 @@ template <int D> struct BwdCfg {
   static constexpr int QS = D <= 32 ? 3 : 2;                     // Q / dO stages
   static constexpr int PB = D == 64 ? 1 : 2;                     // P^T / dS^T shared-memory buffers (what fits in 227 KB)
   static constexpr int kPBytes = kBK * BQ * 2;                   // P^T or dS^T tile
+  // With D <= 32 the bf16 P^T and dS^T tiles also fit in tensor memory (64 columns each): dV and dK then take
+  // their A operand from there and only dS^T, which dQ = dS K reads transposed, goes through shared memory.  That
+  // halves the shared-memory traffic per tile, which was what bounded the kernel.
+  static constexpr bool kTS = D <= 32;
+  static constexpr int kBufBytes = kTS ? kPBytes : 2 * kPBytes;  // per buffer: dS^T (| P^T)
   static constexpr int kLsdBytes = 2 /*stages*/ * 2 * BQ * 4;
-  static constexpr int kSmem = 2 * kKVBytes + QS * kQStage + PB * 2 * kPBytes + kLsdBytes + 256 + 1024;
+  static constexpr int kSmem = 2 * kKVBytes + QS * kQStage + PB * kBufBytes + kLsdBytes + 256 + 1024;
   static_assert(kSmem <= 227 * 1024, "shared memory budget");
-  // tensor-memory columns: S^T, dP^T, dV, dK, dQ
-  static constexpr uint32_t kSCol = 0, kDpCol = BQ, kDvCol = 2 * BQ, kDkCol = 2 * BQ + D, kDqCol = 2 * BQ + 2 * D;
-  static_assert(2 * BQ + 3 * D <= 512, "tensor-memory budget");
+  // tensor-memory columns: S^T, dP^T, (P^T, dS^T as bf16 pairs), dV, dK, dQ
+  static constexpr uint32_t kSCol = 0, kDpCol = BQ, kPtCol = 2 * BQ, kDsCol = 2 * BQ + BQ / 2;
+  static constexpr uint32_t kDvCol = kTS ? 3 * BQ : 2 * BQ, kDkCol = kDvCol + D, kDqCol = kDkCol + D;
+  static_assert(kDqCol + D <= 512, "tensor-memory budget");
 };
 
 template <int D>
@@ -99,12 +106,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   // per buffer dS^T sits in front of P^T: with 64-query tiles the dQ MMA (M = 128) reads one 64-row atom past the
   // dS^T tile, which then falls inside the P^T tile of the same buffer (rows 64..127 of that product are never used)
   unsigned char *spds = sqdo + QS * C::kQStage;                   // [PB buffers][dS^T | P^T]
-  float *slsd = reinterpret_cast<float *>(spds + PB * 2 * C::kPBytes);      // [stage][-lse2 | -delta][BQ]
+  float *slsd = reinterpret_cast<float *>(spds + PB * C::kBufBytes);      // [stage][-lse2 | -delta][BQ]
   uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<unsigned char *>(slsd) + C::kLsdBytes);
   uint64_t *kv_full = bars, *qdo_full = bars + 1, *qdo_empty = qdo_full + QS, *s_full = qdo_empty + QS, *dp_full = s_full + 1;
   uint64_t *pds_full = dp_full + 1, *pds_empty = pds_full + 1 /*[PB]*/, *dq_full = pds_empty + PB, *dq_read = dq_full + 1;
   uint64_t *dkv_full = dq_read + 1, *lsd_full = dkv_full + 1 /*[2]*/;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(lsd_full + 2);
+  uint64_t *pt_free = lsd_full + 2;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(pt_free + 1);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -121,10 +129,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   if (threadIdx.x == 0) {
     tc::mbar_init(kv_full, 1);
     for (int s = 0; s < QS; ++s) { tc::mbar_init(&qdo_full[s], 1); tc::mbar_init(&qdo_empty[s], 1); }
-    tc::mbar_init(s_full, 1); tc::mbar_init(dp_full, 1); tc::mbar_init(pds_full, 256);
+    tc::mbar_init(s_full, 1); tc::mbar_init(dp_full, 1); tc::mbar_init(pds_full, 32 * kBwdComputeWarps);
     for (int b = 0; b < PB; ++b) tc::mbar_init(&pds_empty[b], 1);
-    tc::mbar_init(dq_full, 1); tc::mbar_init(dq_read, 128); tc::mbar_init(dkv_full, 1);
-    tc::mbar_init(&lsd_full[0], BQ); tc::mbar_init(&lsd_full[1], BQ);
+    tc::mbar_init(dq_full, 1); tc::mbar_init(dq_read, 32 * kBwdComputeWarps); tc::mbar_init(dkv_full, 1);
+    tc::mbar_init(&lsd_full[0], BQ); tc::mbar_init(&lsd_full[1], BQ); tc::mbar_init(pt_free, 1);
     *abort_flag = 0;
     tc::mbar_fence_init();
   }
@@ -189,16 +197,38 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       };
 
       if (ok) ok = issue_s_dp(0);
+      constexpr uint32_t idesc_kv_ts = tc::make_idesc_f16(kBK, C::DCH, true, false, true);   // A from tensor memory
       for (int i = 0; i < num_qtiles && ok; ++i) {
         const int s = i % QS, pb = i % PB;
-        // P^T and dS^T of tile i are in shared memory, and every compute thread has read S^T and dP^T
+        // P^T and dS^T of tile i are published, and every compute thread has read S^T and dP^T
         if (!tc::mbar_wait(pds_full, (uint32_t)i & 1u, wc, 305)) { ok = false; break; }
         // the next tile's scores first: the compute warps work on them while the tensor pipe runs this tile's
         // three gradient products
         if (i + 1 < num_qtiles && !issue_s_dp(i + 1)) { ok = false; break; }
         tc::tc_fence_after_sync();
         const uint32_t q_addr = tc::smem_u32(sqdo + s * C::kQStage), do_addr = q_addr + C::kQBytes;
-        const uint32_t ds_addr = tc::smem_u32(spds + pb * 2 * C::kPBytes), pt_addr = ds_addr + C::kPBytes;
+        const uint32_t ds_addr = tc::smem_u32(spds + pb * C::kBufBytes), pt_addr = ds_addr + C::kPBytes;
+        // dV += P^T dO and dK += dS^T Q, 16 queries per instruction.  A = [keys x queries]: tensor memory (two
+        // bf16 per column) when it fits, else shared-memory tiles with 128-byte rows of 64 queries
+#pragma unroll
+        for (int c = 0; c < C::NDCH; ++c) {
+#pragma unroll
+          for (int qk = 0; qk < BQ / 16; ++qk) {
+            const uint32_t b_off = c * BQ * C::RB + qk * 16 * C::RB;
+            const uint64_t b_do = tc::make_smem_desc(do_addr + b_off, 16, 8 * C::RB, C::SWZ);
+            const uint64_t b_q = tc::make_smem_desc(q_addr + b_off, 16, 8 * C::RB, C::SWZ);
+            if (C::kTS) {
+              tc::mma_f16_ts(tmem_base + C::kDvCol + c * C::DCH, tmem_base + C::kPtCol + qk * 8, b_do, idesc_kv_ts, (i | qk) != 0);
+              tc::mma_f16_ts(tmem_base + C::kDkCol + c * C::DCH, tmem_base + C::kDsCol + qk * 8, b_q, idesc_kv_ts, (i | qk) != 0);
+            } else {
+              const uint32_t a_off = (qk / 4) * (kBK * 128) + (qk % 4) * 32;
+              tc::mma_f16_ss(tmem_base + C::kDvCol + c * C::DCH, tc::make_smem_desc(pt_addr + a_off, 16, 1024, tc::kSwizzle128), b_do, idesc_kv, (i | qk) != 0);
+              tc::mma_f16_ss(tmem_base + C::kDkCol + c * C::DCH, tc::make_smem_desc(ds_addr + a_off, 16, 1024, tc::kSwizzle128), b_q, idesc_kv, (i | qk) != 0);
+            }
+          }
+        }
+        tc::mma_commit(&qdo_empty[s]);
+        if (C::kTS) tc::mma_commit(pt_free);
         // dQ_i = dS K_j: A = the dS^T tile read M-major (queries contiguous), K = keys in steps of 16 rows
         if (i > 0 && !tc::mbar_wait(dq_read, (uint32_t)(i - 1) & 1u, wc, 306)) { ok = false; break; }
         tc::tc_fence_after_sync();
@@ -210,93 +240,145 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                            tc::make_smem_desc(ds_addr + ks * 16 * 128, kBK * 128, 1024, tc::kSwizzle128),
                            tc::make_smem_desc(k_addr + c * kBK * C::RB + ks * 16 * C::RB, 16, 8 * C::RB, C::SWZ), idesc_dq, ks != 0);
         tc::mma_commit(dq_full);
-        // dV += P^T dO and dK += dS^T Q: A = [keys x queries] tiles in shared memory (128-byte rows of 64 queries)
-#pragma unroll
-        for (int c = 0; c < C::NDCH; ++c) {
-#pragma unroll
-          for (int qk = 0; qk < BQ / 16; ++qk) {
-            const uint32_t a_off = (qk / 4) * (kBK * 128) + (qk % 4) * 32;
-            const uint32_t b_off = c * BQ * C::RB + qk * 16 * C::RB;
-            tc::mma_f16_ss(tmem_base + C::kDvCol + c * C::DCH, tc::make_smem_desc(pt_addr + a_off, 16, 1024, tc::kSwizzle128),
-                           tc::make_smem_desc(do_addr + b_off, 16, 8 * C::RB, C::SWZ), idesc_kv, (i | qk) != 0);
-            tc::mma_f16_ss(tmem_base + C::kDkCol + c * C::DCH, tc::make_smem_desc(ds_addr + a_off, 16, 1024, tc::kSwizzle128),
-                           tc::make_smem_desc(q_addr + b_off, 16, 8 * C::RB, C::SWZ), idesc_kv, (i | qk) != 0);
-          }
-        }
-        tc::mma_commit(&qdo_empty[s]);
         tc::mma_commit(&pds_empty[pb]);
         if (i + 1 == num_qtiles) tc::mma_commit(dkv_full);
       }
     }
-  } else if (warp < 10) {
-    const int cw = warp - 2;                          // 0..7
+  } else {
+    // Compute warps: four per tensor-memory lane quadrant; a thread owns one key row and, per query tile, the
+    // BQ / 4 query columns of its warp.  After publishing tile i the warps read out dQ of tile i - 1 (queries on
+    // the lanes) and add it to the fp32 scratch with vector reductions.
+    const int cw = warp - 2;                          // 0..15
     const int q4 = warp & 3;                          // tensor-memory lane quadrant of this warp
-    const int wg = cw >> 2;                           // which half of the columns
-    const int ctid = cw * 32 + lane;                  // 0..255
-    const int row = q4 * 32 + lane;                   // key row (S^T, dP^T, dK, dV)
+    const int cidx = cw >> 2;                         // which quarter of the query columns
+    const int ctid = cw * 32 + lane;                  // 0..511
+    const int row = q4 * 32 + lane;                   // key row (S^T, dP^T, dK, dV) or query row (dQ)
     const uint32_t lane_off = (uint32_t)(q4 * 32) << 16;
-    constexpr int HALF = BQ / 2;                      // query columns per compute thread
+    constexpr int QCOLS = BQ / 4;                     // query columns per compute thread (32 or 16)
+    const int col0 = cidx * QCOLS;
     const uint64_t c2 = bpack2(a.scale_log2, a.scale_log2);
     bool ok = true;
+    // -lse2 and -delta of a query tile are staged in shared memory one tile ahead: the global loads for tile
+    // i + 1 are issued before the arithmetic of tile i and land in registers while it runs
+    auto lsd_index = [&](int i) {
+      const int q_tok = (int)my_scope[i / qtiles_per_bucket] * a.bucket + (i % qtiles_per_bucket) * BQ;
+      return ((size_t)brow * a.L + q_tok + ctid) * a.H + head;
+    };
+    auto lsd_publish = [&](int i, float l, float d) {
+      const uint32_t base = tc::smem_u32(slsd + (i & 1) * 2 * BQ);
+      tc::sts32(base + ctid * 4, l * -1.4426950408889634f);
+      tc::sts32(base + BQ * 4 + ctid * 4, -d);
+      tc::mbar_arrive(&lsd_full[i & 1]);
+    };
+    // dQ of tile i: two warps per quadrant take half of the D columns each
+    auto read_out_dq = [&](int i) -> bool {
+      if (!tc::mbar_wait(dq_full, (uint32_t)i & 1u, wc, 310)) return false;
+      tc::tc_fence_after_sync();
+      if (cidx < 2) {
+        const int q_tok = (int)my_scope[i / qtiles_per_bucket] * a.bucket + (i % qtiles_per_bucket) * BQ;
+        float *dst = a.dq_acc + (((size_t)brow * a.L + q_tok + row) * a.H + head) * D + cidx * (D / 2);
+        const bool live = row < BQ && q_tok + row < a.L;
+#pragma unroll
+        for (int c = 0; c < D / 2; c += 8) {
+          uint32_t o[8];
+          asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                       : "=r"(o[0]), "=r"(o[1]), "=r"(o[2]), "=r"(o[3]), "=r"(o[4]), "=r"(o[5]), "=r"(o[6]), "=r"(o[7])
+                       : "r"(tmem_base + lane_off + C::kDqCol + cidx * (D / 2) + c) : "memory");
+          tc::tmem_ld_wait();
+          if (live) {
+            atomicAdd(reinterpret_cast<float4 *>(dst + c), make_float4(__uint_as_float(o[0]), __uint_as_float(o[1]), __uint_as_float(o[2]), __uint_as_float(o[3])));
+            atomicAdd(reinterpret_cast<float4 *>(dst + c + 4), make_float4(__uint_as_float(o[4]), __uint_as_float(o[5]), __uint_as_float(o[6]), __uint_as_float(o[7])));
+          }
+        }
+      }
+      tc::tc_fence_before_sync();
+      tc::mbar_arrive(dq_read);
+      return true;
+    };
+    if (ctid < BQ) { const size_t idx = lsd_index(0); lsd_publish(0, a.lse[idx], a.delta[idx]); }
     for (int i = 0; i < num_qtiles && ok; ++i) {
       const int s2 = i & 1, pb = i % PB;
-      const int q_tok = (int)my_scope[i / qtiles_per_bucket] * a.bucket + (i % qtiles_per_bucket) * BQ;
       const uint32_t nlse2 = tc::smem_u32(slsd + s2 * 2 * BQ), ndl = nlse2 + BQ * 4;       // negated: used as addends
-      if (ctid < BQ) {
-        const size_t idx = ((size_t)brow * a.L + q_tok + ctid) * a.H + head;
-        tc::sts32(nlse2 + ctid * 4, a.lse[idx] * -1.4426950408889634f);
-        tc::sts32(ndl + ctid * 4, -a.delta[idx]);
-        tc::mbar_arrive(&lsd_full[s2]);
-      }
+      float next_l = 0.f, next_d = 0.f;
+      const bool prefetch = ctid < BQ && i + 1 < num_qtiles;
+      if (prefetch) { const size_t idx = lsd_index(i + 1); next_l = a.lse[idx]; next_d = a.delta[idx]; }
       if (!tc::mbar_wait(&lsd_full[s2], (uint32_t)(i >> 1) & 1u, wc, 312)) { ok = false; break; }
       if (!tc::mbar_wait(s_full, (uint32_t)i & 1u, wc, 307) || !tc::mbar_wait(dp_full, (uint32_t)i & 1u, wc, 308)) { ok = false; break; }
       // the MMAs that read this shared-memory buffer (tile i - PB) must have finished
       if (i >= PB && !tc::mbar_wait(&pds_empty[pb], (uint32_t)(i / PB - 1) & 1u, wc, 309)) { ok = false; break; }
       tc::tc_fence_after_sync();
-      const uint32_t sds = tc::smem_u32(spds + pb * 2 * C::kPBytes), spt = sds + C::kPBytes;
-#pragma unroll
-      for (int ch = 0; ch < HALF / 32; ++ch) {
-        const int col0 = wg * HALF + ch * 32;
-        uint32_t sr[32], dr[32];
-        tc::tmem_ld_32x32b_x32(tmem_base + lane_off + C::kSCol + col0, sr);
-        tc::tmem_ld_32x32b_x32(tmem_base + lane_off + C::kDpCol + col0, dr);
-        tc::tmem_ld_wait();
-        const uint32_t prow = spt + (col0 / 64) * (kBK * 128) + row * 128;
-        const uint32_t drow = sds + (col0 / 64) * (kBK * 128) + row * 128;
-#pragma unroll
-        for (int v8 = 0; v8 < 4; ++v8) {
-          uint4 pw, dw;
-          uint32_t *pw32 = reinterpret_cast<uint32_t *>(&pw), *dw32 = reinterpret_cast<uint32_t *>(&dw);
-          // -lse2 and -delta of 8 queries (the same for every key row: broadcast reads)
-          uint64_t nl[4], nd[4];
-          tc::lds64x2(nlse2 + (col0 + v8 * 8) * 4, nl[0], nl[1]);
-          tc::lds64x2(nlse2 + (col0 + v8 * 8 + 4) * 4, nl[2], nl[3]);
-          tc::lds64x2(ndl + (col0 + v8 * 8) * 4, nd[0], nd[1]);
-          tc::lds64x2(ndl + (col0 + v8 * 8 + 4) * 4, nd[2], nd[3]);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            // p = 2^(s c - lse2), ds = p (dp - delta), two queries per instruction
-            float x0, x1;
-            bunpack2(bfma2(bpack2(__uint_as_float(sr[v8 * 8 + 2 * e]), __uint_as_float(sr[v8 * 8 + 2 * e + 1])), c2, nl[e]), x0, x1);
-            const float p0 = bwd_exp2(x0), p1 = bwd_exp2(x1);
-            const uint64_t t = badd2(bpack2(__uint_as_float(dr[v8 * 8 + 2 * e]), __uint_as_float(dr[v8 * 8 + 2 * e + 1])), nd[e]);
-            float g0, g1;
-            bunpack2(bmul2(bpack2(p0, p1), t), g0, g1);
-            const __nv_bfloat162 ph = __floats2bfloat162_rn(p0, p1), gh = __floats2bfloat162_rn(g0, g1);
-            pw32[e] = *reinterpret_cast<const uint32_t *>(&ph);
-            dw32[e] = *reinterpret_cast<const uint32_t *>(&gh);
-          }
-          const int chunk16 = ((col0 % 64) / 8 + v8) ^ (row & 7);
-          tc::sts128(prow + chunk16 * 16, pw);
-          tc::sts128(drow + chunk16 * 16, dw);
-        }
+      const uint32_t sds = tc::smem_u32(spds + pb * C::kBufBytes), spt = sds + C::kPBytes;
+      uint32_t sr[QCOLS], dr[QCOLS];
+      if (QCOLS == 32) {
+        tc::tmem_ld_32x32b_x32(tmem_base + lane_off + C::kSCol + col0, reinterpret_cast<uint32_t (&)[32]>(sr));
+        tc::tmem_ld_32x32b_x32(tmem_base + lane_off + C::kDpCol + col0, reinterpret_cast<uint32_t (&)[32]>(dr));
+      } else {
+        tc::tmem_ld_32x32b_x16(tmem_base + lane_off + C::kSCol + col0, reinterpret_cast<uint32_t (&)[16]>(sr));
+        tc::tmem_ld_32x32b_x16(tmem_base + lane_off + C::kDpCol + col0, reinterpret_cast<uint32_t (&)[16]>(dr));
       }
+      // -lse2 and -delta of the first 8 queries (the same for every key row: broadcast reads); the next group's are
+      // fetched while the current one is worked on
+      uint64_t nl[4], nd[4];
+      tc::lds64x2(nlse2 + col0 * 4, nl[0], nl[1]);
+      tc::lds64x2(nlse2 + (col0 + 4) * 4, nl[2], nl[3]);
+      tc::lds64x2(ndl + col0 * 4, nd[0], nd[1]);
+      tc::lds64x2(ndl + (col0 + 4) * 4, nd[2], nd[3]);
+      tc::tmem_ld_wait();
+      if (C::kTS && i > 0) {
+        // the previous tile's dV / dK MMAs must have consumed the tensor-memory copies of P^T and dS^T
+        if (!tc::mbar_wait(pt_free, (uint32_t)(i - 1) & 1u, wc, 313)) { ok = false; break; }
+        tc::tc_fence_after_sync();
+      }
+      const uint32_t prow = spt + (col0 / 64) * (kBK * 128) + row * 128;
+      const uint32_t drow = sds + (col0 / 64) * (kBK * 128) + row * 128;
+#pragma unroll
+      for (int v8 = 0; v8 < QCOLS / 8; ++v8) {
+        uint64_t nl_next[4] = {0, 0, 0, 0}, nd_next[4] = {0, 0, 0, 0};
+        if (v8 + 1 < QCOLS / 8) {
+          tc::lds64x2(nlse2 + (col0 + v8 * 8 + 8) * 4, nl_next[0], nl_next[1]);
+          tc::lds64x2(nlse2 + (col0 + v8 * 8 + 12) * 4, nl_next[2], nl_next[3]);
+          tc::lds64x2(ndl + (col0 + v8 * 8 + 8) * 4, nd_next[0], nd_next[1]);
+          tc::lds64x2(ndl + (col0 + v8 * 8 + 12) * 4, nd_next[2], nd_next[3]);
+        }
+        uint4 pw, dw;
+        uint32_t *pw32 = reinterpret_cast<uint32_t *>(&pw), *dw32 = reinterpret_cast<uint32_t *>(&dw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          // p = 2^(s c - lse2), ds = p (dp - delta), two queries per instruction
+          float x0, x1;
+          bunpack2(bfma2(bpack2(__uint_as_float(sr[v8 * 8 + 2 * e]), __uint_as_float(sr[v8 * 8 + 2 * e + 1])), c2, nl[e]), x0, x1);
+          const float p0 = bwd_exp2(x0), p1 = bwd_exp2(x1);
+          const uint64_t t = badd2(bpack2(__uint_as_float(dr[v8 * 8 + 2 * e]), __uint_as_float(dr[v8 * 8 + 2 * e + 1])), nd[e]);
+          float g0, g1;
+          bunpack2(bmul2(bpack2(p0, p1), t), g0, g1);
+          const __nv_bfloat162 ph = __floats2bfloat162_rn(p0, p1), gh = __floats2bfloat162_rn(g0, g1);
+          pw32[e] = *reinterpret_cast<const uint32_t *>(&ph);
+          dw32[e] = *reinterpret_cast<const uint32_t *>(&gh);
+        }
+        const int chunk16 = ((col0 % 64) / 8 + v8) ^ (row & 7);
+        tc::sts128(drow + chunk16 * 16, dw);
+        if (C::kTS) {
+          tc::tmem_st_32x32b_x4(tmem_base + lane_off + C::kPtCol + col0 / 2 + v8 * 4, pw.x, pw.y, pw.z, pw.w);
+          tc::tmem_st_32x32b_x4(tmem_base + lane_off + C::kDsCol + col0 / 2 + v8 * 4, dw.x, dw.y, dw.z, dw.w);
+        } else {
+          tc::sts128(prow + chunk16 * 16, pw);
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { nl[e] = nl_next[e]; nd[e] = nd_next[e]; }
+      }
+      if (C::kTS) tc::tmem_st_wait();
+      // the other stage was last read in tile i - 1, which every thread has left (S^T of tile i was issued only
+      // after all of them had signalled pds_full for tile i - 1)
+      if (prefetch) lsd_publish(i + 1, next_l, next_d);
       tc::fence_proxy_async();
       tc::tc_fence_before_sync();
       tc::mbar_arrive(pds_full);
+      if (i > 0 && !read_out_dq(i - 1)) { ok = false; break; }
     }
-    if (ok && tc::mbar_wait(dkv_full, 0, wc, 311) && key_tok + row < a.L) {
+    if (ok) ok = read_out_dq(num_qtiles - 1);
+    if (ok && tc::mbar_wait(dkv_full, 0, wc, 311) && cidx < 2 && key_tok + row < a.L) {
       tc::tc_fence_after_sync();
+      const int wg = cidx;
       const size_t base = (((size_t)brow * a.L + key_tok + row) * a.H + head) * D + wg * (D / 2);
 #pragma unroll
       for (int c = 0; c < D / 2; c += 8) {
@@ -318,32 +400,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         *reinterpret_cast<uint4 *>(a.dK + base + c) = kw;
         *reinterpret_cast<uint4 *>(a.dV + base + c) = vw;
       }
-    }
-  } else {
-    // dQ read-out warps: queries on the lanes, one warp per lane quadrant; each tile's product is added to the
-    // fp32 scratch with vector reductions while the compute warps are already on the next tile
-    const int q4 = warp & 3;
-    const int row = q4 * 32 + lane;                   // query row of the tile
-    const uint32_t lane_off = (uint32_t)(q4 * 32) << 16;
-    for (int i = 0; i < num_qtiles; ++i) {
-      const int q_tok = (int)my_scope[i / qtiles_per_bucket] * a.bucket + (i % qtiles_per_bucket) * BQ;
-      if (!tc::mbar_wait(dq_full, (uint32_t)i & 1u, wc, 310)) break;
-      tc::tc_fence_after_sync();
-      float *dst = a.dq_acc + (((size_t)brow * a.L + q_tok + row) * a.H + head) * D;
-      const bool live = row < BQ && q_tok + row < a.L;
-#pragma unroll
-      for (int c = 0; c < D; c += 16) {
-        uint32_t o[16];
-        tc::tmem_ld_32x32b_x16(tmem_base + lane_off + C::kDqCol + c, o);
-        tc::tmem_ld_wait();
-        if (live) {
-#pragma unroll
-          for (int e = 0; e < 16; e += 4)
-            atomicAdd(reinterpret_cast<float4 *>(dst + c + e), make_float4(__uint_as_float(o[e]), __uint_as_float(o[e + 1]), __uint_as_float(o[e + 2]), __uint_as_float(o[e + 3])));
-        }
-      }
-      tc::tc_fence_before_sync();
-      tc::mbar_arrive(dq_read);
     }
   }
 
