@@ -433,6 +433,43 @@ def run_attn_layer(args):
     print(json.dumps(line), flush=True)
 
 
+def run_gemm_mix(args):
+    """The projection GEMMs of one backbone forward (16 x 120k points: qkv, proj, fc1 with SwiGLU, fc2 at the five
+    levels), each timed alone.  `--level L` restricts to one level (for a small profiler capture)."""
+    from flash3dtransformer_b200.lib import pshattn
+    dev = torch.device("cuda:0")
+    peaks = measured_peaks()
+    g = torch.Generator(dev).manual_seed(0)
+    levels = [(1941504, 32, 4), (974848, 64, 4), (487424, 128, 4), (245760, 256, 12), (122880, 512, 4)]
+    if args.level >= 0:
+        levels = [levels[args.level]]
+    rows, total_ms, roof_ms = [], 0.0, 0.0
+    for m, c, blocks in levels:
+        m = m // args.shrink
+        for name, n, k, ns, epi, res in (("qkv", 3 * c, c, 3, 0, False), ("proj", c, c, 1, 0, True),
+                                         ("fc1_swiglu", 8 * c, c, 1, 2, False), ("fc2", c, 4 * c, 1, 0, True)):
+            a = torch.randn(m, k, device=dev, generator=g).bfloat16()
+            w = (torch.randn(n, k, device=dev, generator=g) / k ** 0.5).bfloat16()
+            b = torch.randn(n, device=dev, generator=g)
+            out_n = n // 2 if epi == 2 else n
+            out = torch.empty(m, out_n, device=dev, dtype=torch.bfloat16)
+            r = torch.randn(m, out_n, device=dev, generator=g).bfloat16() if res else None
+            t = _time_ms(lambda: pshattn.linear_bf16(a, w, b, out, residual=r, nsplit=ns, epilogue=epi), args.steps, args.warmup)
+            byt = 2.0 * (m * k + m * out_n + (m * out_n if res else 0))
+            flop = 2.0 * m * n * k
+            roof = max(byt / (peaks["hbm_gbs"] * 1e9), flop / (peaks["tflops"] * 1e12)) * 1e3
+            rows.append({"shape": f"{name} M={m} N={n} K={k}", "ms": t, "gbs": byt / t / 1e6, "tflops": flop / t / 1e9,
+                         "roofline_ms": roof, "frac": roof / t})
+            total_ms += t * blocks
+            roof_ms += roof * blocks
+    pshattn.device_status()
+    print(json.dumps({"metric": "ms of projection GEMMs per backbone forward", "value": total_ms, "unit": "ms", "n_gpus": 1,
+                      "steps": args.steps, "warmup": args.warmup, "higher_is_better": False, "dtype": "bf16", "data": "synthetic",
+                      "config": {"workload": "gemm_mix_backbone_16x120k", "level": args.level, "shrink": args.shrink},
+                      "roofline": {"bound": "hbm", "roofline_ms": roof_ms, "frac": roof_ms / total_ms, "peak_source": peaks["source"]},
+                      "shapes": rows}), flush=True)
+
+
 def run_psh_pool(args):
     """PSH build + scatter, three rounds of stride-2 sub-bucket pooling and the matching unpools on 8 scenes of
     1,000,000 points with heavy-tailed (Zipf 1.5) voxel occupancy, feature dim 128 fp32.  Reports points/s and the
@@ -506,8 +543,10 @@ def main():
     ap.add_argument("--points", type=int, default=POINTS_PER_SCENE)
     ap.add_argument("--ref-points", type=int, default=20000, help="points of the CPU arm's bounded sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="backbone", choices=["backbone", "attn_layer", "psh_pool"],
-                    help="backbone = the headline metric; the other two are single-GPU side measurements")
+    ap.add_argument("--workload", default="backbone", choices=["backbone", "attn_layer", "psh_pool", "gemm_mix"],
+                    help="backbone = the headline metric; the others are single-GPU side measurements")
+    ap.add_argument("--level", type=int, default=-1, help="gemm_mix: only this backbone level (0..4)")
+    ap.add_argument("--shrink", type=int, default=1, help="gemm_mix: divide the row counts (small profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -521,7 +560,7 @@ def main():
         if rank == 0:
             from flash3dtransformer_b200.lib import _cabi
             _cabi.load()
-            (run_attn_layer if args.workload == "attn_layer" else run_psh_pool)(args)
+            {"attn_layer": run_attn_layer, "psh_pool": run_psh_pool, "gemm_mix": run_gemm_mix}[args.workload](args)
         return
     if world > 1:
         import torch.distributed as dist
