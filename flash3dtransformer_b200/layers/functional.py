@@ -1,8 +1,9 @@
 """Autograd glue between torch modules and the native operators.
 
 Forward passes run the hand-written kernels (tcgen05 GEMM with fused bias / residual / SwiGLU epilogues, bucketed
-attention, pooling, unpooling).  Backward passes of the projections use torch matmuls (plain library GEMMs); the
-backward passes of attention, pooling and unpooling run the native kernels.
+attention, pooling, unpooling).  In the backward passes of the projections the input gradient g W runs on the same
+tcgen05 GEMM; the weight gradient g^T x (a reduction over all rows) is a plain library GEMM.  The backward passes of
+attention, pooling and unpooling run the native kernels.
 """
 from __future__ import annotations
 
@@ -33,6 +34,24 @@ def _fp32_bias(b: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
     if b is None:
         return None
     return b.detach() if b.dtype == torch.float32 else b.detach().float()
+
+
+class CoordEmbedFn(Function):
+    """y = x W^T + b for fp16 coordinates x [rows, 3]: the native embedding kernel (no gradient flows into x)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        out = torch.empty(x.shape[0], weight.shape[0], dtype=torch.bfloat16, device=x.device)
+        pshattn.coord_embed_bf16(x.contiguous(), weight.detach().float().contiguous(), bias.detach().float().contiguous(), out)
+        ctx.save_for_backward(x)
+        ctx.dtypes = (weight.dtype, bias.dtype)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        (x,) = ctx.saved_tensors
+        gf = g.float()
+        return None, (gf.t() @ x.float()).to(ctx.dtypes[0]), gf.sum(0).to(ctx.dtypes[1])
 
 
 class LinearFn(Function):
@@ -73,7 +92,9 @@ class LinearFn(Function):
             with torch.enable_grad():
                 z = torch.nn.functional.gelu(y, approximate="tanh")
             g = torch.autograd.grad(z, y, g.float())[0].to(wb.dtype)
-        gx = g @ wb
+        # gx = g W: the native GEMM computes A B^T, so W^T ([in, out], a small matrix) is materialised
+        gx = torch.empty(g.shape[0], wb.shape[1], dtype=torch.bfloat16, device=g.device)
+        pshattn.linear_bf16(g, wb.t().contiguous(), None, gx)
         gw = (g.t() @ xb).to(weight.dtype)
         gb = g.float().sum(0).to(bias.dtype) if bias is not None else None
         return gx, gw, gb, g_res, None, None

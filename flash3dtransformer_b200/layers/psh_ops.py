@@ -8,6 +8,7 @@ from torch import nn
 
 from ..psh import arithmatic as f3darith
 from ..psh import psh_main as pm
+from .functional import CoordEmbedFn
 
 
 class PSHScatterLayer(nn.Module):
@@ -35,6 +36,7 @@ class PSH3DCoordEmbedding(nn.Module):
         pad_to = f3darith.cdiv(coords.shape[0], self.alignment) * self.alignment
         scattered, _ = pm.batch_bucket_scatter(coords, seps, self.bucket_size, pad_to, hash_op, bbox=bbox, mean_n=mean_n,
                                                 scene_base=scene_base)
-        # K = 3 is below the tensor-core GEMM's 8-element granularity: three FMAs per output, left to torch
-        return torch.nn.functional.linear(scattered.to(self.feat_dtype), self.lin.weight.to(self.feat_dtype),
-                                          self.lin.bias.to(self.feat_dtype))
+        # K = 3 is not a tensor-core GEMM: the embedding kernel does the three FMAs per output
+        out = CoordEmbedFn.apply(scattered if scattered.dtype == torch.float16 else scattered.to(torch.float16),
+                                 self.lin.weight, self.lin.bias)
+        return out if self.feat_dtype == torch.bfloat16 else out.to(self.feat_dtype)

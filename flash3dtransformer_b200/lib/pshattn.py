@@ -354,6 +354,21 @@ def layernorm_bf16(x, weight, bias, out, eps=1e-5, gelu=False) -> None:
     _cabi.check(st, "layernorm_bf16")
 
 
+def coord_embed_bf16(coords, weight, bias, out) -> None:
+    """out = coords @ weight.T + bias for fp16 coords [rows, 3], fp32 weight [C, 3] / bias [C], bf16 out [rows, C].
+    Not part of the reference's operator module (it embeds with te.Linear, flash3dxfmr/layers/psh_ops.py:62)."""
+    dev = _check_tensors([coords, weight, bias, out], ["coords", "weight", "bias", "out"])
+    _check_dtype([coords], ["coords"], torch.float16)
+    _check_dtype([weight, bias], ["weight", "bias"], torch.float32)
+    _check_dtype([out], ["out"], torch.bfloat16)
+    _require(coords.dim() == 2 and coords.shape[1] == 3, "coords must be [rows, 3]")
+    _require(weight.dim() == 2 and weight.shape[1] == 3 and bias.numel() == weight.shape[0], "weight must be [C, 3], bias [C]")
+    _require(out.dim() == 2 and out.shape[0] == coords.shape[0] and out.shape[1] == weight.shape[0], "out must be [rows, C]")
+    st = _cabi.load().f3d_coord_embed_bf16(_ptr(coords), _ptr(weight), _ptr(bias), _ptr(out), coords.shape[0], weight.shape[0],
+                                           _dev_index(dev), _stream(dev))
+    _cabi.check(st, "coord_embed_bf16")
+
+
 def launch_count() -> int:
     """Kernels launched by the native library since it was loaded."""
     return int(_cabi.load().f3d_launch_count())

@@ -193,6 +193,12 @@ int f3d_buck_swin_fwd(const void *Q, const void *K, const void *V, void *O, void
 int f3d_layernorm_bf16(const void *x, const void *weight, const void *bias, void *y, uint32_t rows, uint32_t C, float eps,
                        int gelu, int device, void *stream);
 
+/* Coordinate embedding out = W x + b: fp16 coordinates [rows, 3], fp32 weight [C, 3] and bias [C], bf16 out [rows, C].
+ * Stands in for the te.Linear(3, emb_dim) of PSH3DCoordEmbedding (flash3dxfmr/layers/psh_ops.py:62,77).  C a multiple
+ * of 8, <= 2048. */
+int f3d_coord_embed_bf16(const void *coords, const void *weight, const void *bias, void *out, uint32_t rows, uint32_t C,
+                         int device, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

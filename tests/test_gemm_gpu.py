@@ -93,3 +93,36 @@ def test_gemm_errors(cuda_device):
         pshattn.linear_bf16(x, w, None, torch.zeros(16, 8, device=cuda_device, dtype=torch.bfloat16))
     with pytest.raises(RuntimeError, match="dtype"):
         pshattn.linear_bf16(x.float(), w, None, torch.zeros(16, 8, device=cuda_device, dtype=torch.bfloat16))
+
+
+@pytest.mark.parametrize("rows,c", [(1, 32), (1000, 32), (70001, 64), (4096, 512), (513, 2048)])
+def test_coord_embed(cuda_device, rows, c):
+    """The 3 -> C coordinate embedding (te.Linear(3, emb_dim) in the reference, flash3dxfmr/layers/psh_ops.py:62)
+    against an fp32 torch reference; the result differs from it only by the final rounding to bf16."""
+    from flash3dtransformer_b200.lib import pshattn
+    g = torch.Generator(cuda_device).manual_seed(rows + c)
+    x = (torch.randn(rows, 3, device=cuda_device, generator=g) * 20).half()
+    w = torch.randn(c, 3, device=cuda_device, generator=g) * 0.5
+    b = torch.randn(c, device=cuda_device, generator=g)
+    out = torch.full((rows, c), float("nan"), device=cuda_device, dtype=torch.bfloat16)
+    pshattn.coord_embed_bf16(x, w, b, out)
+    ref = x.float() @ w.t() + b
+    assert torch.isfinite(out.float()).all()
+    # one bf16 rounding of a value computed in fp32 (the FMA order may differ from torch's by an ulp of fp32)
+    assert ((out.float() - ref).abs() <= ref.abs() * 2.0 ** -8 + 1e-6).all()
+
+
+def test_linear_input_gradient_runs_native(cuda_device):
+    """The autograd backward of the projection computes g W on the native GEMM; compare with fp32 autograd."""
+    from flash3dtransformer_b200.layers.functional import LinearFn
+    g = torch.Generator(cuda_device).manual_seed(5)
+    x = torch.randn(1024, 64, device=cuda_device, generator=g).bfloat16().requires_grad_(True)
+    w = (torch.randn(96, 64, device=cuda_device, generator=g) / 8).requires_grad_(True)
+    b = torch.zeros(96, device=cuda_device, requires_grad=True)
+    y = LinearFn.apply(x, w, b, None, 1, 0)
+    gy = torch.randn(1024, 96, device=cuda_device, generator=g).bfloat16()
+    y.backward(gy)
+    ref_gx = gy.float() @ w.detach().bfloat16().float()
+    _check(x.grad, ref_gx)
+    ref_gw = gy.float().t() @ x.detach().float()
+    assert (w.grad - ref_gw).abs().max().item() <= 2e-2 * ref_gw.abs().max().item() + 1e-2
