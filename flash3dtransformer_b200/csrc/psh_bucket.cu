@@ -289,6 +289,20 @@ __global__ void __launch_bounds__(kPshThreads) psh_rankA_kernel(PshArgs a) {
   float lo[3], hi[3];
   load_bbox(a, lo, hi);
   const float ratio = probe_ratio(a.num_vox, a.divisor);
+  // LCG jump constants of this lane for the warp-wide phase of the walk: probe kSoloProbes + 32 j + lane uses the
+  // stream state n = 32 j + lane + 1 steps after the solo probes, s_n = A^n s_0 + C_n (mod 2^32), C_n = c (A^(n-1) + ... + 1)
+  constexpr uint32_t kSoloProbes = 8;
+  constexpr uint32_t kWarpBatches = (kNumProbes - kSoloProbes + 31) / 32;
+  uint32_t jump_a[kWarpBatches], jump_c[kWarpBatches];
+  {
+    uint32_t pa = 1u, pc = 0u, n = 0;
+#pragma unroll
+    for (uint32_t j = 0; j < kWarpBatches; ++j) {
+      const uint32_t want = j * 32 + lane + 1;
+      for (; n < want; ++n) { pa *= 1664525u; pc = pc * 1664525u + 1013904223u; }
+      jump_a[j] = pa; jump_c[j] = pc;
+    }
+  }
   const uint32_t wt = a.tile / kPshWarps;
   const uint32_t w0 = warp * wt, w1 = min(w0 + wt, t.cnt);
   uint16_t *st = s.stage + warp * kStageHalves;
@@ -352,28 +366,73 @@ __global__ void __launch_bounds__(kPshThreads) psh_rankA_kernel(PshArgs a) {
     }
     if (!need_coords) continue;
     uint32_t skew = warp_stage(a, t.start + t.t0 + g, gc, st, lane);
+    // Walk in two phases.  Phase 1: every overflowing point tries its first kSoloProbes probes on its own lane
+    // (scenes with free buckets nearby resolve almost everything here, 32 points at a time).  Phase 2: a point
+    // that is still unresolved gets the whole warp: lane l evaluates probe kSoloProbes + 32 j + l of batch j (its
+    // position in the point's LCG streams is reached by a jump, s_n = A^n s_0 + C_n), and the first admissible
+    // probe in table order is the lowest lane of the first batch that has one, so long walks (LiDAR scans at 90 %
+    // load) no longer hold the other 31 lanes up.
     for (uint32_t it = 0; it < gc; it += 32) {
       uint32_t k = it + lane;
       bool valid = k < gc;
       uint32_t mk = valid ? s.keys[g + k] : 0u;
-      if (valid && (mk & 0x8000u)) {
-        uint32_t init = mk & 0x7FFFu;
-        uint32_t vox[3], nvox[3], r[4];
+      const bool marked = valid && (mk & 0x8000u);
+      const uint32_t init = mk & 0x7FFFu;
+      uint32_t vox[3] = {0u, 0u, 0u};
+      ProbeStream ps{};
+      const uint32_t pt = t.t0 + g + k;
+      uint32_t found = a.nb;                           // a.nb = "no admissible probe" column
+      bool open = marked;
+      if (marked) {
         load_vox(a, st, skew, k, lo, hi, vox);
-        uint32_t pt = t.t0 + g + k;
-        uint32_t target = a.nb;                       // "no admissible probe" column
-        ProbeStream ps;
         probe_stream_init(a.key, t.scene + a.scene_base, pt, ps);
-        for (uint32_t p = 0; p < kNumProbes; ++p) {
+        uint32_t r[4], nvox[3];
+        for (uint32_t p = 0; p < kSoloProbes; ++p) {
           probe_stream_next(ps, r);
           perturb_vox(r, a.num_vox, ratio, a.probe + 3u * p, vox, nvox);
-          uint32_t c = first_hash(a.hash_type, nvox[0], nvox[1], nvox[2], a.divisor, a.nb);
-          if (c != init && c != kRecycleBucket && s.aux[c] < a.cap) { target = c; break; }
+          const uint32_t c = first_hash(a.hash_type, nvox[0], nvox[1], nvox[2], a.divisor, a.nb);
+          if (c != init && c != kRecycleBucket && s.aux[c] < a.cap) { found = c; open = false; break; }
         }
+      }
+      uint32_t todo = __ballot_sync(0xFFFFFFFFu, open);
+      while (todo) {
+        const int src = __ffs(todo) - 1;
+        todo &= todo - 1;
+        uint32_t bvox[3], bs[4];
+#pragma unroll
+        for (int d = 0; d < 3; ++d) bvox[d] = __shfl_sync(0xFFFFFFFFu, vox[d], src);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) bs[q] = __shfl_sync(0xFFFFFFFFu, ps.s[q], src);   // state after the solo probes
+        const uint32_t binit = __shfl_sync(0xFFFFFFFFu, init, src);
+#pragma unroll
+        for (uint32_t j = 0; j < kWarpBatches; ++j) {
+          const uint32_t p = kSoloProbes + j * 32 + lane;
+          uint32_t r[4], nvox[3];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const uint32_t sv = bs[q] * jump_a[j] + jump_c[j];
+            r[q] = sv ^ (sv >> 15);
+          }
+          bool ok = false;
+          uint32_t c = 0;
+          if (p < kNumProbes) {
+            perturb_vox(r, a.num_vox, ratio, a.probe + 3u * p, bvox, nvox);
+            c = first_hash(a.hash_type, nvox[0], nvox[1], nvox[2], a.divisor, a.nb);
+            ok = c != binit && c != kRecycleBucket && s.aux[c] < a.cap;
+          }
+          const uint32_t hit = __ballot_sync(0xFFFFFFFFu, ok);
+          if (hit) {
+            const uint32_t tc = __shfl_sync(0xFFFFFFFFu, c, __ffs(hit) - 1);
+            if (lane == src) found = tc;
+            break;
+          }
+        }
+      }
+      if (marked) {
         uint32_t gi = t.start + pt;
-        a.bucket_id[gi] = (uint16_t)target;
+        a.bucket_id[gi] = (uint16_t)found;
         a.bucket_offset[gi] = kPending;
-        atomicAdd(&rowB[target], 1u);
+        atomicAdd(&rowB[found], 1u);
         ++my_pending;
       }
     }
