@@ -470,6 +470,74 @@ def run_gemm_mix(args):
                       "shapes": rows}), flush=True)
 
 
+def run_train_step(args, rank: int, world: int, local_rank: int):
+    """Backbone forward + backward + gradient all-reduce + SGD step (the backward configuration): `--scenes` scans of
+    `--points` points per GPU, scene-sharded; NCCL carries only the PSH statistics and the gradient all-reduce."""
+    import torch.distributed as dist
+    from flash3dtransformer_b200 import parallel
+    from flash3dtransformer_b200.lib import _cabi, pshattn
+    from flash3dtransformer_b200.psh import batching
+    _cabi.load()
+    dev = torch.device(f"cuda:{local_rank}")
+    torch.cuda.set_device(dev)
+    model = build_model(dev).train()
+    opt = torch.optim.SGD(model.parameters(), lr=1e-3)
+    c16, seps = make_batch(rank, args.scenes, args.points)
+    coords = torch.from_numpy(c16).to(dev)
+    seps_dev = torch.from_numpy(seps).to(dev)
+    batching.host_seps(seps_dev)
+    n_params = sum(p.numel() for p in model.parameters())
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    t_ar = [0.0]
+
+    def step(timed: bool):
+        opt.zero_grad(set_to_none=True)
+        bbox, mean_n = parallel.global_psh_stats(coords, seps_dev)
+        out = model(coords, None, seps_dev, bbox=bbox, mean_n=mean_n, scene_base=rank * args.scenes)
+        loss = out.float().square().mean()
+        loss.backward()
+        if world > 1:
+            if timed:
+                ev[2].record()
+            parallel.allreduce_gradients(model.parameters())
+            if timed:
+                ev[3].record()
+        opt.step()
+        return loss
+
+    for _ in range(args.warmup):
+        loss = step(False)
+    torch.cuda.synchronize()
+    pshattn.device_status()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ar_ms = 0.0
+    ev[0].record()
+    for _ in range(args.steps):
+        loss = step(True)
+        if world > 1:
+            torch.cuda.synchronize()
+            ar_ms += ev[2].elapsed_time(ev[3])
+    ev[1].record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms = torch.tensor([ev[0].elapsed_time(ev[1]), ar_ms], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    pshattn.device_status()
+    if rank == 0:
+        ms_per_step = ms[0].item() / args.steps
+        pts = args.scenes * args.points * world
+        print(json.dumps({"metric": "points/sec (Flash3D backbone fwd+bwd+SGD)", "value": pts / (ms_per_step * 1e-3), "unit": "points/s",
+                          "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+                          "higher_is_better": True, "scaling": "weak", "dtype": "bf16", "data": "synthetic",
+                          "config": {"workload": f"flash3d_backbone_train_step_{args.scenes}x{args.points // 1000}k_per_gpu",
+                                     "parameters": n_params, "grad_allreduce_bytes": 4 * n_params},
+                          "grad_allreduce_ms_per_step": ms[1].item() / args.steps, "loss": float(loss.detach())}), flush=True)
+
+
 def run_psh_pool(args):
     """PSH build + scatter, three rounds of stride-2 sub-bucket pooling and the matching unpools on 8 scenes of
     1,000,000 points with heavy-tailed (Zipf 1.5) voxel occupancy, feature dim 128 fp32.  Reports points/s and the
@@ -543,7 +611,7 @@ def main():
     ap.add_argument("--points", type=int, default=POINTS_PER_SCENE)
     ap.add_argument("--ref-points", type=int, default=20000, help="points of the CPU arm's bounded sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="backbone", choices=["backbone", "attn_layer", "psh_pool", "gemm_mix"],
+    ap.add_argument("--workload", default="backbone", choices=["backbone", "attn_layer", "psh_pool", "gemm_mix", "train_step"],
                     help="backbone = the headline metric; the others are single-GPU side measurements")
     ap.add_argument("--layer-scenes", type=int, default=8, help="attn_layer: number of 120k-point scans (fewer for a profiler capture)")
     ap.add_argument("--level", type=int, default=-1, help="gemm_mix: only this backbone level (0..4)")
@@ -556,6 +624,19 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.workload == "train_step":
+        if world > 1:
+            import torch.distributed as dist
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            torch.cuda.set_device(local_rank)
+            dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
+        try:
+            run_train_step(args, rank, world, local_rank)
+        finally:
+            if world > 1:
+                import torch.distributed as dist
+                dist.destroy_process_group()
         return
     if args.workload != "backbone":
         if rank == 0:
