@@ -109,12 +109,23 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       tc::tma_prefetch_desc(&map_a); tc::tma_prefetch_desc(&map_b); tc::tma_prefetch_desc(&map_c);
       uint32_t it = 0;
       bool ok = true;
+      // With a single column tile and a k-block count that divides the ring, stage s always carries k-block
+      // s % kb_count, so its W tile never changes: it is loaded on the stage's first use and stays resident.
+      // (A TMA tile load costs about 7 cycles per box row whatever the row length; reloading a 128- or 256-row W
+      // tile for every 128 rows of A took a third of the time of the narrow-K shapes.)
+      const bool w_resident = n_tiles == 1 && kStages % kb_count == 0;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int m0 = (tile / n_tiles) * BM, n0 = (tile % n_tiles) * BN;
         for (int kb = 0; kb < kb_count; ++kb, ++it) {
           const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
           if (!tc::mbar_wait(&empty[s], ph ^ 1u, wc, 101)) { ok = false; break; }
           unsigned char *sa = stage_base + s * S::kStageBytes;
+          if (w_resident && it >= (uint32_t)kStages) {
+            // this stage already holds the W tile of k-block kb from its first use: only A moves
+            tc::mbar_expect_tx(&full[s], S::kABytes);
+            tc::tma_load_2d(sa, &map_a, &full[s], kb * BK, m0);
+            continue;
+          }
           tc::mbar_expect_tx(&full[s], S::kStageBytes);
           tc::tma_load_2d(sa, &map_a, &full[s], kb * BK, m0);
           if (g.epilogue == EPI_SWIGLU) {
