@@ -9,17 +9,22 @@
 //
 // Kernels:
 //   attn_bwd_delta_kernel   Delta = rowsum(dO o O), one thread per (token, head)
-//   attn_bwd_kernel<D>      one CTA per (scope, 128-key block, head, batch row); it loops over the query tiles of
-//                           the scope and keeps dK, dV for its keys in tensor memory
-//       warp 0      TMA producer: K_j, V_j once; Q_i, dO_i through a 2-stage ring
-//       warp 1      issues S^T = K Q^T and dP^T = V dO^T into tensor memory (keys on the lanes), then, once the
-//                   compute warps have published P^T and dS^T as bf16 in shared memory, dV += P^T dO, dK += dS^T Q
-//                   (shared-memory A, K-major) and dQ_i = dS K (the same dS^T tile read as an MN-major A operand)
-//       warps 2-9   compute: each thread owns one key row and half of the query columns; p = exp2(s*c - lse),
-//                   ds = p*(dp - delta) with lse/delta of the tile staged in shared memory; then they read dQ_i from
-//                   tensor memory (queries on the lanes) and add it to an fp32 scratch with vector atomics
+//   attn_bwd_kernel<D>      one CTA (576 threads) per (scope, 128-key block, head, batch row); it loops over the
+//                           query tiles of the scope and keeps dK, dV for its keys in tensor memory
+//       warp 0      TMA producer: K_j, V_j once; Q_i, dO_i through a 2- or 3-stage ring
+//       warp 1      issues S^T = K Q^T and dP^T = V dO^T into tensor memory (keys on the lanes); once the compute
+//                   warps have published P^T and dS^T it first issues the NEXT tile's S^T / dP^T, then dV += P^T dO
+//                   and dK += dS^T Q (A from tensor memory at D <= 32, else K-major shared-memory tiles) and
+//                   dQ_i = dS K (the dS^T shared-memory tile read as an MN-major A operand)
+//       warps 2-17  compute: a thread owns one key row and a quarter of the query columns; p = exp2(s*c - lse),
+//                   ds = p*(dp - delta) in packed fp32 pairs, with -lse / -delta of the tile staged in shared memory
+//                   one tile ahead; afterwards they read dQ of the previous tile from tensor memory (queries on the
+//                   lanes) and add it to an fp32 scratch with vector reductions
 //   attn_bwd_dq_convert     dQ = bf16(scratch / sqrt(D))
 // dQ needs the scratch because every key block of a scope contributes to every query; dK and dV are written once.
+//   attn_bwd_window_kernel<D>   windows of at most 512 tokens at D <= 32: one CTA per (scope, head) walks key blocks
+//                           and query tiles and keeps every dQ tile in tensor memory, so nothing goes through the
+//                           scratch (see the comment at the kernel)
 #include "f3d_common.cuh"
 #include "tc_sm100.cuh"
 #include "../../include/f3d_b200.h"
@@ -412,6 +417,297 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   if (warp == 1) { tc::tc_fence_after_sync(); tc::tmem_dealloc(tmem_base, 512); }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Small windows: when all query tiles of a scope fit in tensor memory as dQ accumulators (W / 128 * D <= 128
+// columns, i.e. W <= 512 at D = 32), one CTA takes a whole (scope, head): it walks the key blocks j and, inside,
+// the query tiles i, keeps dV_j / dK_j for the current block and dQ_i for every tile in tensor memory, and writes
+// all three once as bf16.  No fp32 scratch, no reductions, no conversion pass, and K / V of the next block are
+// prefetched into a second shared-memory buffer.
+template <int D> struct BwdWinCfg {
+  static constexpr int BQ = 128;
+  static constexpr int RB = D * 2;
+  static constexpr uint64_t SWZ = RB == 64 ? tc::kSwizzle64 : tc::kSwizzle32;
+  static constexpr int kKVBytes = kBK * D * 2;
+  static constexpr int kQBytes = BQ * D * 2;
+  static constexpr int kQStage = 2 * kQBytes;
+  static constexpr int QS = 3;
+  static constexpr int kPBytes = kBK * BQ * 2;                  // dS^T tile
+  static constexpr int kLsdBytes = 2 * 2 * BQ * 4;
+  static constexpr int kSmem = 2 * 2 * kKVBytes + QS * kQStage + 2 * kPBytes + kLsdBytes + 256 + 1024;
+  static constexpr int kMaxTiles = 4;                           // query tiles (and key blocks) per scope
+  static constexpr uint32_t kSCol = 0, kDpCol = 128, kPtCol = 256, kDvCol = 320, kDkCol = 352, kDqCol = 384;
+  static_assert(D <= 32 && kDqCol + kMaxTiles * D <= 512, "tensor-memory budget");
+};
+
+template <int D>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+attn_bwd_window_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, AttnBwdArgs a,
+                       __nv_bfloat16 *__restrict__ dQ) {
+  using C = BwdWinCfg<D>;
+  constexpr int BQ = C::BQ, QS = C::QS;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char *skv = smem;                                      // [2 buffers][K | V]
+  unsigned char *sqdo = skv + 2 * 2 * C::kKVBytes;                // [QS stages][Q | dO]
+  unsigned char *sdsb = sqdo + QS * C::kQStage;                   // [2 buffers] dS^T
+  float *slsd = reinterpret_cast<float *>(sdsb + 2 * C::kPBytes); // [stage][-lse2 | -delta][BQ]
+  uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<unsigned char *>(slsd) + C::kLsdBytes);
+  uint64_t *kv_full = bars /*[2]*/, *kv_empty = bars + 2 /*[2]*/, *qdo_full = bars + 4, *qdo_empty = qdo_full + QS;
+  uint64_t *s_full = qdo_empty + QS, *dp_full = s_full + 1, *pds_full = dp_full + 1, *pds_empty = pds_full + 1 /*[2]*/;
+  uint64_t *pt_free = pds_empty + 2, *dkv_full = pt_free + 1, *dkv_read = dkv_full + 1, *lsd_full = dkv_read + 1 /*[2]*/;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(lsd_full + 2);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int scope = blockIdx.x, head = blockIdx.y, brow = blockIdx.z;
+  const uint32_t *my_scope = a.scopes + (size_t)scope * a.k;
+  const int tiles_per_bucket = a.bucket / 128;
+  const int nt = a.k * tiles_per_bucket;                          // query tiles = key blocks of the scope (<= 4)
+  const int total = nt * nt;                                      // iterations t = j * nt + i
+  auto tile_tok = [&](int x) { return (int)my_scope[x / tiles_per_bucket] * a.bucket + (x % tiles_per_bucket) * 128; };
+
+  if (threadIdx.x == 0) {
+    for (int b = 0; b < 2; ++b) { tc::mbar_init(&kv_full[b], 1); tc::mbar_init(&kv_empty[b], 1); tc::mbar_init(&pds_empty[b], 1); }
+    for (int s = 0; s < QS; ++s) { tc::mbar_init(&qdo_full[s], 1); tc::mbar_init(&qdo_empty[s], 1); }
+    tc::mbar_init(s_full, 1); tc::mbar_init(dp_full, 1); tc::mbar_init(pds_full, 32 * kBwdComputeWarps);
+    tc::mbar_init(pt_free, 1); tc::mbar_init(dkv_full, 1); tc::mbar_init(dkv_read, 32 * kBwdComputeWarps);
+    tc::mbar_init(&lsd_full[0], BQ); tc::mbar_init(&lsd_full[1], BQ);
+    *abort_flag = 0;
+    tc::mbar_fence_init();
+  }
+  if (warp == 1) { tc::tmem_alloc(tmem_slot, 512); tc::tmem_relinquish(); }
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  tc::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  tc::WaitCtx wc{abort_flag, a.status};
+
+  if (warp == 0) {
+    if (tc::elect_one()) {
+      tc::tma_prefetch_desc(&map_q); tc::tma_prefetch_desc(&map_k); tc::tma_prefetch_desc(&map_v); tc::tma_prefetch_desc(&map_do);
+      auto load_kv = [&](int j) -> bool {
+        const int b = j & 1;
+        if (!tc::mbar_wait(&kv_empty[b], ((uint32_t)(j >> 1) & 1u) ^ 1u, wc, 321, 200)) return false;
+        unsigned char *sk = skv + b * 2 * C::kKVBytes, *sv = sk + C::kKVBytes;
+        tc::mbar_expect_tx(&kv_full[b], 2 * C::kKVBytes);
+        tc::tma_load_3d(sk, &map_k, &kv_full[b], 0, head, brow * a.L + tile_tok(j));
+        tc::tma_load_3d(sv, &map_v, &kv_full[b], 0, head, brow * a.L + tile_tok(j));
+        return true;
+      };
+      bool ok = load_kv(0);
+      for (int t = 0; t < total && ok; ++t) {
+        const int j = t / nt, i = t % nt, s = t % QS;
+        if (!tc::mbar_wait(&qdo_empty[s], ((uint32_t)(t / QS) & 1u) ^ 1u, wc, 322, 200)) break;
+        unsigned char *sq = sqdo + s * C::kQStage, *sdo = sq + C::kQBytes;
+        tc::mbar_expect_tx(&qdo_full[s], C::kQStage);
+        tc::tma_load_3d(sq, &map_q, &qdo_full[s], 0, head, brow * a.L + tile_tok(i));
+        tc::tma_load_3d(sdo, &map_do, &qdo_full[s], 0, head, brow * a.L + tile_tok(i));
+        // the next block's K / V go into the other buffer while this block is being worked on
+        if (i == 0 && j + 1 < nt) ok = load_kv(j + 1);
+      }
+    }
+
+  } else if (warp == 1) {
+    if (tc::elect_one()) {
+      constexpr uint32_t idesc_s = tc::make_idesc_f16(kBK, BQ, true, false, false);          // S^T, dP^T
+      constexpr uint32_t idesc_kv = tc::make_idesc_f16(kBK, D, true, false, true);           // dV (A in TMEM), dK: B MN-major
+      constexpr uint32_t idesc_dq = tc::make_idesc_f16(128, D, true, true, true);            // dQ: A and B MN-major
+      auto issue_s_dp = [&](int t) -> bool {
+        const int j = t / nt, i = t % nt, s = t % QS;
+        if (i == 0 && !tc::mbar_wait(&kv_full[j & 1], (uint32_t)(j >> 1) & 1u, wc, 323)) return false;
+        if (!tc::mbar_wait(&qdo_full[s], (uint32_t)(t / QS) & 1u, wc, 324)) return false;
+        tc::tc_fence_after_sync();
+        const uint32_t k_addr = tc::smem_u32(skv + (j & 1) * 2 * C::kKVBytes), v_addr = k_addr + C::kKVBytes;
+        const uint32_t q_addr = tc::smem_u32(sqdo + s * C::kQStage), do_addr = q_addr + C::kQBytes;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          tc::mma_f16_ss(tmem_base + C::kSCol, tc::make_smem_desc(k_addr + kk * 32, 16, 8 * C::RB, C::SWZ),
+                         tc::make_smem_desc(q_addr + kk * 32, 16, 8 * C::RB, C::SWZ), idesc_s, kk != 0);
+        tc::mma_commit(s_full);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          tc::mma_f16_ss(tmem_base + C::kDpCol, tc::make_smem_desc(v_addr + kk * 32, 16, 8 * C::RB, C::SWZ),
+                         tc::make_smem_desc(do_addr + kk * 32, 16, 8 * C::RB, C::SWZ), idesc_s, kk != 0);
+        tc::mma_commit(dp_full);
+        return true;
+      };
+      bool ok = issue_s_dp(0);
+      for (int t = 0; t < total && ok; ++t) {
+        const int j = t / nt, i = t % nt, s = t % QS, pb = t & 1;
+        // P^T (tensor memory) and dS^T (shared memory) of iteration t are published, S^T / dP^T have been read
+        if (!tc::mbar_wait(pds_full, (uint32_t)t & 1u, wc, 325)) { ok = false; break; }
+        if (t + 1 < total && !issue_s_dp(t + 1)) { ok = false; break; }
+        // a new key block overwrites dV / dK: the previous block's must have been read out
+        if (i == 0 && j > 0 && !tc::mbar_wait(dkv_read, (uint32_t)(j - 1) & 1u, wc, 326)) { ok = false; break; }
+        tc::tc_fence_after_sync();
+        const uint32_t k_addr = tc::smem_u32(skv + (j & 1) * 2 * C::kKVBytes);
+        const uint32_t q_addr = tc::smem_u32(sqdo + s * C::kQStage), do_addr = q_addr + C::kQBytes;
+        const uint32_t ds_addr = tc::smem_u32(sdsb + pb * C::kPBytes);
+#pragma unroll
+        for (int qk = 0; qk < BQ / 16; ++qk) {
+          const uint32_t a_off = (qk / 4) * (kBK * 128) + (qk % 4) * 32;
+          tc::mma_f16_ts(tmem_base + C::kDvCol, tmem_base + C::kPtCol + qk * 8,
+                         tc::make_smem_desc(do_addr + qk * 16 * C::RB, 16, 8 * C::RB, C::SWZ), idesc_kv, (i | qk) != 0);
+          tc::mma_f16_ss(tmem_base + C::kDkCol, tc::make_smem_desc(ds_addr + a_off, 16, 1024, tc::kSwizzle128),
+                         tc::make_smem_desc(q_addr + qk * 16 * C::RB, 16, 8 * C::RB, C::SWZ), idesc_kv, (i | qk) != 0);
+        }
+        tc::mma_commit(&qdo_empty[s]);
+        tc::mma_commit(pt_free);
+        // dQ_i (+)= dS K_j: accumulated over the key blocks in its own tensor-memory columns
+#pragma unroll
+        for (int ks = 0; ks < kBK / 16; ++ks)
+          tc::mma_f16_ss(tmem_base + C::kDqCol + i * D, tc::make_smem_desc(ds_addr + ks * 16 * 128, kBK * 128, 1024, tc::kSwizzle128),
+                         tc::make_smem_desc(k_addr + ks * 16 * C::RB, 16, 8 * C::RB, C::SWZ), idesc_dq, (j | ks) != 0);
+        tc::mma_commit(&pds_empty[pb]);
+        if (i == nt - 1) { tc::mma_commit(dkv_full); tc::mma_commit(&kv_empty[j & 1]); }
+      }
+    }
+  } else {
+    const int cw = warp - 2;                          // 0..15
+    const int q4 = warp & 3;                          // tensor-memory lane quadrant of this warp
+    const int cidx = cw >> 2;                         // which quarter of the query columns
+    const int ctid = cw * 32 + lane;                  // 0..511
+    const int row = q4 * 32 + lane;                   // key row (S^T, dP^T, dK, dV) or query row (dQ)
+    const uint32_t lane_off = (uint32_t)(q4 * 32) << 16;
+    const int col0 = cidx * 32;
+    const uint64_t c2 = bpack2(a.scale_log2, a.scale_log2);
+    bool ok = true;
+    auto lsd_index = [&](int t) { return ((size_t)brow * a.L + tile_tok(t % nt) + ctid) * a.H + head; };
+    auto lsd_publish = [&](int t, float l, float d) {
+      const uint32_t base = tc::smem_u32(slsd + (t & 1) * 2 * BQ);
+      tc::sts32(base + ctid * 4, l * -1.4426950408889634f);
+      tc::sts32(base + BQ * 4 + ctid * 4, -d);
+      tc::mbar_arrive(&lsd_full[t & 1]);
+    };
+    if (ctid < BQ) { const size_t idx = lsd_index(0); lsd_publish(0, a.lse[idx], a.delta[idx]); }
+    for (int t = 0; t < total && ok; ++t) {
+      const int j = t / nt, i = t % nt, pb = t & 1;
+      const uint32_t nlse2 = tc::smem_u32(slsd + (t & 1) * 2 * BQ), ndl = nlse2 + BQ * 4;
+      float next_l = 0.f, next_d = 0.f;
+      const bool prefetch = ctid < BQ && t + 1 < total;
+      if (prefetch) { const size_t idx = lsd_index(t + 1); next_l = a.lse[idx]; next_d = a.delta[idx]; }
+      if (!tc::mbar_wait(&lsd_full[t & 1], (uint32_t)(t >> 1) & 1u, wc, 327)) { ok = false; break; }
+      if (!tc::mbar_wait(s_full, (uint32_t)t & 1u, wc, 328) || !tc::mbar_wait(dp_full, (uint32_t)t & 1u, wc, 329)) { ok = false; break; }
+      // the dQ MMA that read this shared-memory buffer (iteration t - 2) must have finished
+      if (t >= 2 && !tc::mbar_wait(&pds_empty[pb], (uint32_t)(t / 2 - 1) & 1u, wc, 330)) { ok = false; break; }
+      tc::tc_fence_after_sync();
+      uint32_t sr[32], dr[32];
+      tc::tmem_ld_32x32b_x32(tmem_base + lane_off + C::kSCol + col0, sr);
+      tc::tmem_ld_32x32b_x32(tmem_base + lane_off + C::kDpCol + col0, dr);
+      uint64_t nl[4], nd[4];
+      tc::lds64x2(nlse2 + col0 * 4, nl[0], nl[1]);
+      tc::lds64x2(nlse2 + (col0 + 4) * 4, nl[2], nl[3]);
+      tc::lds64x2(ndl + col0 * 4, nd[0], nd[1]);
+      tc::lds64x2(ndl + (col0 + 4) * 4, nd[2], nd[3]);
+      tc::tmem_ld_wait();
+      if (t > 0) {
+        // the previous iteration's dV MMAs must have consumed the tensor-memory copy of P^T
+        if (!tc::mbar_wait(pt_free, (uint32_t)(t - 1) & 1u, wc, 331)) { ok = false; break; }
+        tc::tc_fence_after_sync();
+      }
+      const uint32_t drow = tc::smem_u32(sdsb + pb * C::kPBytes) + (col0 / 64) * (kBK * 128) + row * 128;
+#pragma unroll
+      for (int v8 = 0; v8 < 4; ++v8) {
+        uint64_t nl_next[4] = {0, 0, 0, 0}, nd_next[4] = {0, 0, 0, 0};
+        if (v8 + 1 < 4) {
+          tc::lds64x2(nlse2 + (col0 + v8 * 8 + 8) * 4, nl_next[0], nl_next[1]);
+          tc::lds64x2(nlse2 + (col0 + v8 * 8 + 12) * 4, nl_next[2], nl_next[3]);
+          tc::lds64x2(ndl + (col0 + v8 * 8 + 8) * 4, nd_next[0], nd_next[1]);
+          tc::lds64x2(ndl + (col0 + v8 * 8 + 12) * 4, nd_next[2], nd_next[3]);
+        }
+        uint4 pw, dw;
+        uint32_t *pw32 = reinterpret_cast<uint32_t *>(&pw), *dw32 = reinterpret_cast<uint32_t *>(&dw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float x0, x1;
+          bunpack2(bfma2(bpack2(__uint_as_float(sr[v8 * 8 + 2 * e]), __uint_as_float(sr[v8 * 8 + 2 * e + 1])), c2, nl[e]), x0, x1);
+          const float p0 = bwd_exp2(x0), p1 = bwd_exp2(x1);
+          const uint64_t tt = badd2(bpack2(__uint_as_float(dr[v8 * 8 + 2 * e]), __uint_as_float(dr[v8 * 8 + 2 * e + 1])), nd[e]);
+          float g0, g1;
+          bunpack2(bmul2(bpack2(p0, p1), tt), g0, g1);
+          const __nv_bfloat162 ph = __floats2bfloat162_rn(p0, p1), gh = __floats2bfloat162_rn(g0, g1);
+          pw32[e] = *reinterpret_cast<const uint32_t *>(&ph);
+          dw32[e] = *reinterpret_cast<const uint32_t *>(&gh);
+        }
+        const int chunk16 = ((col0 % 64) / 8 + v8) ^ (row & 7);
+        tc::sts128(drow + chunk16 * 16, dw);
+        tc::tmem_st_32x32b_x4(tmem_base + lane_off + C::kPtCol + col0 / 2 + v8 * 4, pw.x, pw.y, pw.z, pw.w);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { nl[e] = nl_next[e]; nd[e] = nd_next[e]; }
+      }
+      tc::tmem_st_wait();
+      if (prefetch) lsd_publish(t + 1, next_l, next_d);
+      tc::fence_proxy_async();
+      tc::tc_fence_before_sync();
+      tc::mbar_arrive(pds_full);
+      if (i == nt - 1) {
+        // end of key block j: dK_j and dV_j are complete
+        if (!tc::mbar_wait(dkv_full, (uint32_t)j & 1u, wc, 332)) { ok = false; break; }
+        tc::tc_fence_after_sync();
+        const int key_tok = tile_tok(j);
+        if (cidx < 2) {
+          const bool live = key_tok + row < a.L;
+          const size_t base = (((size_t)brow * a.L + key_tok + (live ? row : 0)) * a.H + head) * D + cidx * (D / 2);
+#pragma unroll
+          for (int c = 0; c < D / 2; c += 8) {
+            uint32_t kk[8], vv[8];
+            asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                         : "=r"(kk[0]), "=r"(kk[1]), "=r"(kk[2]), "=r"(kk[3]), "=r"(kk[4]), "=r"(kk[5]), "=r"(kk[6]), "=r"(kk[7])
+                         : "r"(tmem_base + lane_off + C::kDkCol + cidx * (D / 2) + c) : "memory");
+            asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                         : "=r"(vv[0]), "=r"(vv[1]), "=r"(vv[2]), "=r"(vv[3]), "=r"(vv[4]), "=r"(vv[5]), "=r"(vv[6]), "=r"(vv[7])
+                         : "r"(tmem_base + lane_off + C::kDvCol + cidx * (D / 2) + c) : "memory");
+            tc::tmem_ld_wait();
+            uint4 kw, vw;
+            __nv_bfloat162 *k2 = reinterpret_cast<__nv_bfloat162 *>(&kw), *v2 = reinterpret_cast<__nv_bfloat162 *>(&vw);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              k2[e] = __floats2bfloat162_rn(__uint_as_float(kk[2 * e]) * a.scale, __uint_as_float(kk[2 * e + 1]) * a.scale);
+              v2[e] = __floats2bfloat162_rn(__uint_as_float(vv[2 * e]), __uint_as_float(vv[2 * e + 1]));
+            }
+            if (live) {
+              *reinterpret_cast<uint4 *>(a.dK + base + c) = kw;
+              *reinterpret_cast<uint4 *>(a.dV + base + c) = vw;
+            }
+          }
+        }
+        tc::tc_fence_before_sync();
+        tc::mbar_arrive(dkv_read);
+      }
+    }
+    // dQ: the last block's dkv_full also covers the last dQ MMAs; warps of column quarter `cidx` take query tile `cidx`
+    if (ok && cidx < nt) {
+      tc::tc_fence_after_sync();
+      const int q_tok = tile_tok(cidx);
+      const bool live = q_tok + row < a.L;
+      __nv_bfloat16 *dst = dQ + (((size_t)brow * a.L + q_tok + (live ? row : 0)) * a.H + head) * D;
+#pragma unroll
+      for (int c = 0; c < D; c += 16) {
+        uint32_t o[16];
+        tc::tmem_ld_32x32b_x16(tmem_base + lane_off + C::kDqCol + cidx * D + c, o);
+        tc::tmem_ld_wait();
+        uint4 w[2];
+        __nv_bfloat162 *h2 = reinterpret_cast<__nv_bfloat162 *>(w);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) h2[e] = __floats2bfloat162_rn(__uint_as_float(o[2 * e]) * a.scale, __uint_as_float(o[2 * e + 1]) * a.scale);
+        if (live) {
+          *reinterpret_cast<uint4 *>(dst + c) = w[0];
+          *reinterpret_cast<uint4 *>(dst + c + 8) = w[1];
+        }
+      }
+    }
+  }
+
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) { tc::tc_fence_after_sync(); tc::tmem_dealloc(tmem_base, 512); }
+}
+
 // Delta[b,t,h] = sum_d dO * O  (tests/test_attn_bwd.py:24-27)
 __global__ void attn_bwd_delta_kernel(const __nv_bfloat16 *__restrict__ O, const __nv_bfloat16 *__restrict__ dO,
                                       float *__restrict__ delta, size_t rows, int D) {
@@ -460,6 +756,28 @@ static int launch_attn_bwd(const void *Q, const void *K, const void *V, const vo
   return check_launch("buck_swin_bwd");
 }
 
+template <int D>
+static int launch_attn_bwd_window(const void *Q, const void *K, const void *V, const void *dO, void *dQ, AttnBwdArgs a, int device,
+                                  cudaStream_t st) {
+  using C = BwdWinCfg<D>;
+  static bool attr[16] = {false};
+  auto kern = attn_bwd_window_kernel<D>;
+  if (device < 16 && !attr[device]) {
+    F3D_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem));
+    attr[device] = true;
+  }
+  CUtensorMap mq, mk, mv, mdo;
+  const uint64_t rows = (uint64_t)a.B * a.L;
+  const uint64_t s1 = (uint64_t)D * 2, s2 = (uint64_t)a.H * D * 2;
+  F3D_TRY(encode_tmap_3d(&mq, 0, Q, D, a.H, rows, s1, s2, D, 1, 128, C::RB));
+  F3D_TRY(encode_tmap_3d(&mdo, 0, dO, D, a.H, rows, s1, s2, D, 1, 128, C::RB));
+  F3D_TRY(encode_tmap_3d(&mk, 0, K, D, a.H, rows, s1, s2, D, 1, 128, C::RB));
+  F3D_TRY(encode_tmap_3d(&mv, 0, V, D, a.H, rows, s1, s2, D, 1, 128, C::RB));
+  dim3 grid(a.num_scopes, a.H, a.B);
+  kern<<<grid, kBwdThreads, C::kSmem, st>>>(mq, mk, mv, mdo, a, static_cast<__nv_bfloat16 *>(dQ));
+  return check_launch("buck_swin_bwd (window)");
+}
+
 }  // namespace f3d
 
 using namespace f3d;
@@ -481,6 +799,18 @@ extern "C" int f3d_buck_swin_bwd(const void *Q, const void *K, const void *V, co
                                                                        static_cast<float *>(Delta), rows, D);
   F3D_TRY(check_launch("buck_swin_bwd (delta)"));
   if (num_scopes == 0) return F3D_OK;
+  const long long window_tiles = (long long)scope_size * (bucket_size / 128);
+  if (D <= 32 && window_tiles <= BwdWinCfg<32>::kMaxTiles) {
+    // small windows: one CTA per (scope, head) keeps every dQ tile in tensor memory, no scratch and no reductions
+    const float scale = 1.f / sqrtf((float)D);
+    AttnBwdArgs a{static_cast<const float *>(LSE), static_cast<const float *>(Delta), nullptr,
+                  static_cast<__nv_bfloat16 *>(dK), static_cast<__nv_bfloat16 *>(dV), static_cast<const uint32_t *>(scope_buckets),
+                  B, L, H, num_scopes, scope_size, (int)bucket_size, (int)bucket_size / kBK, 1.4426950408889634f * scale, scale,
+                  status_word(device)};
+    if (!a.status) return F3D_ERR_CUDA;
+    F3D_TRY(D == 16 ? launch_attn_bwd_window<16>(Q, K, V, dO, dQ, a, device, st) : launch_attn_bwd_window<32>(Q, K, V, dO, dQ, a, device, st));
+    return maybe_sync(st, "buck_swin_bwd");
+  }
   void *acc = nullptr;
   F3D_TRY(workspace(device, 2, rows * D * sizeof(float), &acc));
   F3D_CUDA_TRY(cudaMemsetAsync(acc, 0, rows * D * sizeof(float), st));

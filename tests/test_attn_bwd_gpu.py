@@ -63,6 +63,16 @@ def test_multi_bucket_scopes(cuda_device, b, l, h, d, bucket, k):
     _check_all(_run(cuda_device, b, l, h, d, bucket, scopes, seed=1))
 
 
+@pytest.mark.parametrize("b,l,h,d,bucket,k", [(2, 2048, 2, 32, 128, 4), (1, 1536, 3, 32, 128, 3), (1, 2048, 2, 16, 256, 2),
+                                             (1, 1024, 2, 32, 128, 1), (2, 1024, 1, 16, 512, 1)])
+def test_small_windows(cuda_device, b, l, h, d, bucket, k):
+    """Windows of at most 512 tokens at D <= 32 take the kernel that keeps every dQ tile in tensor memory (one CTA per
+    scope and head, no scratch): 1 to 4 tiles per scope, buckets listed out of order."""
+    nb = l // bucket
+    scopes = [list(reversed(range(i, i + k))) for i in range(0, nb, k)]
+    _check_all(_run(cuda_device, b, l, h, d, bucket, scopes, seed=11))
+
+
 def test_unlisted_buckets_and_permutation(cuda_device):
     r = _run(cuda_device, 1, 2048, 2, 32, 256, [[0, 5], [2, 7]], seed=4)
     _check_all(r)
