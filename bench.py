@@ -381,13 +381,14 @@ def run_attn_layer(args):
     from flash3dtransformer_b200.lib import pshattn
     dev = torch.device("cuda:0")
     peaks = measured_peaks()
-    l, h, d, c, bucket = args.layer_scenes * 120000 // 512 * 512, 8, 32, 256, 512
+    ks = args.layer_scope
+    l, h, d, c, bucket = args.layer_scenes * 120000 // (512 * ks) * (512 * ks), 8, 32, 256, 512
     g = torch.Generator(dev).manual_seed(0)
     x = torch.randn(l, c, device=dev, generator=g).bfloat16()
     wqkv = (torch.randn(3 * c, c, device=dev, generator=g) / c ** 0.5).bfloat16()
     wp = (torch.randn(c, c, device=dev, generator=g) / c ** 0.5).bfloat16()
     bqkv, bp = torch.zeros(3 * c, device=dev), torch.zeros(c, device=dev)
-    scopes = torch.arange(l // bucket, dtype=torch.int64).reshape(-1, 1).to(torch.uint32).to(dev)
+    scopes = torch.arange(l // bucket, dtype=torch.int64).reshape(-1, ks).to(torch.uint32).to(dev)
     qkv = torch.empty(3, l, c, device=dev, dtype=torch.bfloat16)
     o = torch.empty(1, l, h, d, device=dev, dtype=torch.bfloat16)
     lse = torch.zeros(1, l, h, device=dev)
@@ -420,11 +421,11 @@ def run_attn_layer(args):
     t_b = _time_ms(bwd_attn, args.steps, args.warmup)
     t_l = _time_ms(layer, args.steps, args.warmup)
     pshattn.device_status()
-    flops_f = 4.0 * l * bucket * h * d
+    flops_f = 4.0 * l * bucket * ks * h * d
     line = {
         "metric": "tokens/sec (bucketed-attention layer fwd+bwd)", "value": l / (t_l * 1e-3), "unit": "tokens/s", "n_gpus": 1,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": t_l, "higher_is_better": True, "dtype": "bf16",
-        "data": "synthetic", "config": {"workload": f"attn_layer_fwd_bwd_{args.layer_scenes}x120k_dim256_h8_d32_bucket512"},
+        "data": "synthetic", "config": {"workload": f"attn_layer_fwd_bwd_{args.layer_scenes}x120k_dim256_h8_d32_bucket512_scope{ks}"},
         "attention_fwd": {"ms": t_f, "tflops": flops_f / (t_f * 1e-3) / 1e12, "frac_of_peak": flops_f / (t_f * 1e-3) / 1e12 / peaks["tflops"]},
         "attention_bwd": {"ms": t_b, "tflops": 2.5 * flops_f / (t_b * 1e-3) / 1e12,
                           "frac_of_peak": 2.5 * flops_f / (t_b * 1e-3) / 1e12 / peaks["tflops"]},
@@ -614,6 +615,7 @@ def main():
     ap.add_argument("--workload", default="backbone", choices=["backbone", "attn_layer", "psh_pool", "gemm_mix", "train_step"],
                     help="backbone = the headline metric; the others are single-GPU side measurements")
     ap.add_argument("--layer-scenes", type=int, default=8, help="attn_layer: number of 120k-point scans (fewer for a profiler capture)")
+    ap.add_argument("--layer-scope", type=int, default=1, help="attn_layer: buckets per attention scope (1 in the layer configuration, 8 in the backbone)")
     ap.add_argument("--level", type=int, default=-1, help="gemm_mix: only this backbone level (0..4)")
     ap.add_argument("--shrink", type=int, default=1, help="gemm_mix: divide the row counts (small profiler captures)")
     args = ap.parse_args()
