@@ -496,18 +496,29 @@ __global__ void __launch_bounds__(kPshThreads) psh_resolveB_kernel(PshArgs a) {
   const uint32_t w0 = warp * wt, w1 = min(w0 + wt, t.cnt);
   uint16_t *wh = s.whist + warp * a.nbp;
   const uint32_t gbase = t.start + t.t0;
-  for (uint32_t it = w0; it < w1; it += 32) {
-    uint32_t k = it + lane;
-    bool inb = k < w1;
-    bool valid = false;
-    uint32_t key = 0;
-    if (inb) {
-      uint32_t off = a.bucket_offset[gbase + k];
-      key = a.bucket_id[gbase + k];
-      valid = (off == kPending);
-      s.keys[k] = valid ? (uint16_t)key : (uint16_t)0xFFFFu;
+  // keys of pending points; 0xFFFE marks a settled recycle-bucket point beyond the capacity (a round C mover),
+  // 0xFFFF any other settled point, so the second sweep does not have to read ids and offsets again.  Four
+  // batches of loads are in flight per warp.
+  for (uint32_t it0 = w0; it0 < w1; it0 += 128) {
+    uint32_t offs[4], keys[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const uint32_t k = it0 + u * 32 + lane;
+      offs[u] = 0; keys[u] = 0;
+      if (k < w1) { offs[u] = a.bucket_offset[gbase + k]; keys[u] = a.bucket_id[gbase + k]; }
     }
-    warp_count(wh, key, valid, lane);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const uint32_t k = it0 + u * 32 + lane;
+      if (it0 + u * 32 >= w1) break;
+      const bool inb = k < w1;
+      const bool valid = inb && offs[u] == kPending;
+      if (inb) {
+        const bool over = keys[u] == kRecycleBucket && offs[u] >= a.cap && a.nb > 1;
+        s.keys[k] = valid ? (uint16_t)keys[u] : (over ? (uint16_t)0xFFFEu : (uint16_t)0xFFFFu);
+      }
+      warp_count(wh, keys[u], valid, lane);
+    }
   }
   __syncthreads();
   warp_prefix(s, a.nbp);
@@ -522,7 +533,7 @@ __global__ void __launch_bounds__(kPshThreads) psh_resolveB_kernel(PshArgs a) {
     uint32_t k = it + lane;
     bool inb = k < w1;
     uint32_t kk = inb ? s.keys[k] : 0xFFFFu;
-    bool valid = inb && kk != 0xFFFFu;
+    bool valid = inb && kk < 0xFFFEu;
     uint32_t q = warp_rank(wh, s.tbase, kk, valid, lane);
     if (!inb) continue;
     uint32_t gi = gbase + k;
@@ -543,8 +554,7 @@ __global__ void __launch_bounds__(kPshThreads) psh_resolveB_kernel(PshArgs a) {
         }
       }
     } else {
-      uint32_t off = a.bucket_offset[gi];
-      mover = (a.bucket_id[gi] == kRecycleBucket) && off >= a.cap && a.nb > 1;
+      mover = kk == 0xFFFEu;
     }
     if (mover) {
       uint32_t pt = t.t0 + k;
@@ -650,12 +660,24 @@ __global__ void __launch_bounds__(kPshThreads) psh_scatter_kernel(PshArgs a) {
   for (uint32_t g = w0; g < w1; g += kGroup) {
     uint32_t gc = min(kGroup, w1 - g);
     uint32_t skew = warp_stage(a, gbase + g, gc, st, lane);
-    for (uint32_t it = 0; it < gc; it += 32) {
+    // ids and offsets of the whole group are requested before the first is used: one batch of loads in flight per
+    // warp left this loop waiting on memory latency (issue slots 13 % busy on 8 x 1M points)
+    constexpr int kBatches = kGroup / 32;
+    uint32_t ids[kBatches], offs[kBatches];
+#pragma unroll
+    for (int u = 0; u < kBatches; ++u) {
+      const uint32_t k = u * 32 + lane;
+      ids[u] = 0; offs[u] = 0;
+      if (k < gc) { ids[u] = a.bucket_id[gbase + g + k]; offs[u] = a.bucket_offset[gbase + g + k]; }
+    }
+#pragma unroll
+    for (int u = 0; u < kBatches; ++u) {
+      const uint32_t it = u * 32;
+      if (it >= gc) break;
       uint32_t k = it + lane;
       bool inb = k < gc;
       uint32_t gi = gbase + g + k;
-      uint32_t id = 0, off = 0;
-      if (inb) { id = a.bucket_id[gi]; off = a.bucket_offset[gi]; }
+      uint32_t id = ids[u], off = offs[u];
       if (movers) {
         bool valid = inb && off == kPending;
         uint32_t r = warp_rank(wh, s.tbase, id, valid, lane);
