@@ -60,13 +60,38 @@ __device__ __forceinline__ float gelu_tanh(float x) {
   return 0.5f * x * (1.f + tanhf(u));
 }
 
-// x * sigmoid(x) with one special-function instruction: sigmoid(x) = 0.5 + 0.5 * tanh(x / 2); tanh.approx has a
-// relative error near 5e-4, an order of magnitude below the bf16 rounding of the result.
-__device__ __forceinline__ float silu_fast(float x) {
-  const float h = 0.5f * x;
-  float t;
-  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(h));
-  return fmaf(h, t, h);
+// packed fp32 pairs: one instruction works on two values (halves the issue slots of the epilogue arithmetic)
+__device__ __forceinline__ uint64_t gpack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void gunpack2(uint64_t v, float &lo, float &hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t gadd2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t gmul2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t gfma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+// silu(gate) * up for two columns with one special-function instruction each: sigmoid(x) = 0.5 + 0.5 * tanh(x / 2),
+// so with h = gate / 2, silu = h + h * tanh(h); tanh.approx has a relative error near 5e-4, an order of magnitude below
+// the bf16 rounding of the result
+__device__ __forceinline__ void swiglu_pair(uint64_t gate2, uint64_t up2, float &o0, float &o1) {
+  const uint64_t h2 = gmul2(gate2, gpack2(0.5f, 0.5f));
+  float h0, h1, t0, t1;
+  gunpack2(h2, h0, h1);
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t0) : "f"(h0));
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t1) : "f"(h1));
+  gunpack2(gmul2(gfma2(h2, gpack2(t0, t1), h2), up2), o0, o1);
 }
 
 template <int BN>
@@ -196,19 +221,16 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
               const float4 a4 = __ldg(pg + j), b4 = __ldg(pu + j);
-              const float bg[4] = {a4.x, a4.y, a4.z, a4.w}, bu[4] = {b4.x, b4.y, b4.z, b4.w};
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float gt = __uint_as_float(r[4 * j + e]) + bg[e], up = __uint_as_float(u[4 * j + e]) + bu[e];
-                v[4 * j + e] = silu_fast(gt) * up;
-              }
+              swiglu_pair(gadd2(gpack2(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1])), gpack2(a4.x, a4.y)),
+                          gadd2(gpack2(__uint_as_float(u[4 * j]), __uint_as_float(u[4 * j + 1])), gpack2(b4.x, b4.y)), v[4 * j], v[4 * j + 1]);
+              swiglu_pair(gadd2(gpack2(__uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])), gpack2(a4.z, a4.w)),
+                          gadd2(gpack2(__uint_as_float(u[4 * j + 2]), __uint_as_float(u[4 * j + 3])), gpack2(b4.z, b4.w)), v[4 * j + 2], v[4 * j + 3]);
             }
           } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const float gt = __uint_as_float(r[j]), up = __uint_as_float(u[j]);
-              v[j] = silu_fast(gt) * up;
-            }
+            for (int j = 0; j < 16; ++j)
+              swiglu_pair(gpack2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1])),
+                          gpack2(__uint_as_float(u[2 * j]), __uint_as_float(u[2 * j + 1])), v[2 * j], v[2 * j + 1]);
           }
         } else {
           uint32_t r[32];
@@ -222,7 +244,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
                 const float4 b4 = __ldg(bp + j);
-                v[4 * j] += b4.x; v[4 * j + 1] += b4.y; v[4 * j + 2] += b4.z; v[4 * j + 3] += b4.w;
+                gunpack2(gadd2(gpack2(v[4 * j], v[4 * j + 1]), gpack2(b4.x, b4.y)), v[4 * j], v[4 * j + 1]);
+                gunpack2(gadd2(gpack2(v[4 * j + 2], v[4 * j + 3]), gpack2(b4.z, b4.w)), v[4 * j + 2], v[4 * j + 3]);
               }
             } else {
 #pragma unroll
@@ -247,7 +270,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
               const uint4 w = __ldg(reinterpret_cast<const uint4 *>(rp + j));
               const __nv_bfloat162 *h2 = reinterpret_cast<const __nv_bfloat162 *>(&w);
 #pragma unroll
-              for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h2[e]); v[j + 2 * e] += f.x; v[j + 2 * e + 1] += f.y; }
+              for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h2[e]); gunpack2(gadd2(gpack2(v[j + 2 * e], v[j + 2 * e + 1]), gpack2(f.x, f.y)), v[j + 2 * e], v[j + 2 * e + 1]); }
             }
           } else {
 #pragma unroll
