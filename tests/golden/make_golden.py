@@ -1,7 +1,7 @@
 """Generates the golden fixtures in this folder from the reference's own pure-Python code.
 
-Run in a container that has the reference checkout (default /root/reference, or $F3D_REFERENCE):
-    python tests/golden/make_golden.py
+Run where the reference checkout is available, giving its path as the first argument or in $F3D_REFERENCE:
+    python tests/golden/make_golden.py <path to the reference checkout>
 The reference's compiled extension (flash3dxfmr.lib.pshattn), TransformerEngine and flash_attn are not needed:
 stub modules stand in for them, and only functions that never touch them are called.  The outputs are small
 .npz / .json files that the tests read; nothing at test time reads the reference checkout.
@@ -23,7 +23,9 @@ import types
 import numpy as np
 import torch
 
-REF = os.environ.get("F3D_REFERENCE", "/root/reference")
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("F3D_REFERENCE")
+if not REF or not os.path.isdir(os.path.join(REF, "flash3dxfmr")):
+    raise SystemExit("usage: make_golden.py <path to the reference checkout> (or set F3D_REFERENCE)")
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
