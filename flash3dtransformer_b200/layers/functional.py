@@ -105,7 +105,8 @@ def linear(x, weight, bias=None, residual=None, nsplit=1, epilogue=pshattn.EPI_N
 
 
 class LayerNormFn(Function):
-    """LayerNorm (+ optional GELU) on the native kernel; backward by autograd of the fp32 torch formula."""
+    """LayerNorm (+ optional GELU) on the native kernels, forward and backward; with the fused GELU the backward falls
+    back to autograd of the fp32 torch formula."""
 
     @staticmethod
     def forward(ctx, x, weight, bias, eps, gelu):
@@ -120,6 +121,13 @@ class LayerNormFn(Function):
     def backward(ctx, g):
         xb, weight, bias = ctx.saved_tensors
         eps, gelu = ctx.cfg
+        if not gelu and xb.shape[1] <= 1024:
+            gb16 = (g if g.dtype == torch.bfloat16 else g.to(torch.bfloat16)).contiguous()
+            gx = torch.empty_like(xb)
+            gw = torch.empty(xb.shape[1], dtype=torch.float32, device=xb.device)
+            gb = torch.empty_like(gw)
+            pshattn.layernorm_bwd_bf16(xb, gb16, weight.detach().float().contiguous(), gx, gw, gb, eps)
+            return gx, gw.to(weight.dtype), gb.to(bias.dtype), None, None
         with torch.enable_grad():
             xf = xb.float().requires_grad_(True)
             wf = weight.detach().float().requires_grad_(True)

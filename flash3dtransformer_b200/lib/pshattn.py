@@ -354,6 +354,19 @@ def layernorm_bf16(x, weight, bias, out, eps=1e-5, gelu=False) -> None:
     _cabi.check(st, "layernorm_bf16")
 
 
+def layernorm_bwd_bf16(x, grad_out, weight, grad_x, grad_weight, grad_bias, eps=1e-5) -> None:
+    """Backward of layernorm_bf16 (without GELU): x, grad_out, grad_x bf16 [rows, C]; weight, grad_weight, grad_bias
+    fp32 [C].  Not part of the reference's operator module (its LayerNorm backward comes from TransformerEngine)."""
+    dev = _check_tensors([x, grad_out, weight, grad_x, grad_weight, grad_bias], ["x", "grad_out", "weight", "grad_x", "grad_weight", "grad_bias"])
+    _check_dtype([x, grad_out, grad_x], ["x", "grad_out", "grad_x"], torch.bfloat16)
+    _check_dtype([weight, grad_weight, grad_bias], ["weight", "grad_weight", "grad_bias"], torch.float32)
+    _require(x.dim() == 2 and x.shape == grad_out.shape == grad_x.shape, "x, grad_out and grad_x must be [rows, C] of equal shape")
+    _require(weight.numel() == x.shape[1] == grad_weight.numel() == grad_bias.numel(), "weight, grad_weight, grad_bias must be [C]")
+    st = _cabi.load().f3d_layernorm_bwd_bf16(_ptr(x), _ptr(grad_out), _ptr(weight), _ptr(grad_x), _ptr(grad_weight), _ptr(grad_bias),
+                                             x.shape[0], x.shape[1], float(eps), _dev_index(dev), _stream(dev))
+    _cabi.check(st, "layernorm_bwd_bf16")
+
+
 def coord_embed_bf16(coords, weight, bias, out) -> None:
     """out = coords @ weight.T + bias for fp16 coords [rows, 3], fp32 weight [C, 3] / bias [C], bf16 out [rows, C].
     Not part of the reference's operator module (it embeds with te.Linear, flash3dxfmr/layers/psh_ops.py:62)."""

@@ -193,6 +193,13 @@ int f3d_buck_swin_fwd(const void *Q, const void *K, const void *V, void *O, void
 int f3d_layernorm_bf16(const void *x, const void *weight, const void *bias, void *y, uint32_t rows, uint32_t C, float eps,
                        int gelu, int device, void *stream);
 
+/* Backward of f3d_layernorm_bf16 without GELU: grad_x bf16 [rows, C], grad_weight / grad_bias fp32 [C] from x and grad_out
+ * (bf16 [rows, C]) and the fp32 weight.  The reference gets this from TransformerEngine's / torch's LayerNorm backward
+ * (flash3dxfmr/layers/stage.py:67,95).  Row sums are added in a fixed order (same bits every run).  C a multiple of 8,
+ * <= 1024. */
+int f3d_layernorm_bwd_bf16(const void *x, const void *grad_out, const void *weight, void *grad_x, void *grad_weight,
+                           void *grad_bias, uint32_t rows, uint32_t C, float eps, int device, void *stream);
+
 /* Coordinate embedding out = W x + b: fp16 coordinates [rows, 3], fp32 weight [C, 3] and bias [C], bf16 out [rows, C].
  * Stands in for the te.Linear(3, emb_dim) of PSH3DCoordEmbedding (flash3dxfmr/layers/psh_ops.py:62,77).  C a multiple
  * of 8, <= 2048. */
