@@ -81,12 +81,12 @@ class LinearFn(Function):
         g = g.contiguous()
         g_res = g if has_res else None
         if epilogue == pshattn.EPI_SWIGLU:
-            y = torch.addmm(bias.to(wb.dtype), xb, wb.t()) if bias is not None else xb @ wb.t()
-            f = y.shape[1] // 2
-            gate, up = y[:, :f].float(), y[:, f:].float()
-            sig = torch.sigmoid(gate)
-            gf = g.float()
-            g = torch.cat([gf * up * sig * (1 + gate * (1 - sig)), gf * gate * sig], dim=1).to(wb.dtype)
+            # the pre-activation [gate | up] is recomputed on the native GEMM, its gradient by one fused kernel
+            y = torch.empty(xb.shape[0], wb.shape[0], dtype=torch.bfloat16, device=xb.device)
+            pshattn.linear_bf16(xb, wb, _fp32_bias(bias), y)
+            gy = torch.empty_like(y)
+            pshattn.swiglu_bwd_bf16(y, g if g.dtype == torch.bfloat16 else g.to(torch.bfloat16), gy)
+            g = gy
         elif epilogue == pshattn.EPI_GELU:
             y = (torch.addmm(bias.to(wb.dtype), xb, wb.t()) if bias is not None else xb @ wb.t()).float().requires_grad_(True)
             with torch.enable_grad():
@@ -96,7 +96,14 @@ class LinearFn(Function):
         gx = torch.empty(g.shape[0], wb.shape[1], dtype=torch.bfloat16, device=g.device)
         pshattn.linear_bf16(g, wb.t().contiguous(), None, gx)
         gw = (g.t() @ xb).to(weight.dtype)
-        gb = g.float().sum(0).to(bias.dtype) if bias is not None else None
+        gb = None
+        if bias is not None:
+            if g.dtype == torch.bfloat16 and g.shape[1] % 8 == 0 and g.shape[1] <= 2048:
+                gb32 = torch.empty(g.shape[1], dtype=torch.float32, device=g.device)
+                pshattn.colsum_bf16(g, gb32)
+                gb = gb32.to(bias.dtype)
+            else:
+                gb = g.float().sum(0).to(bias.dtype)
         return gx, gw, gb, g_res, None, None
 
 

@@ -367,6 +367,28 @@ def layernorm_bwd_bf16(x, grad_out, weight, grad_x, grad_weight, grad_bias, eps=
     _cabi.check(st, "layernorm_bwd_bf16")
 
 
+def swiglu_bwd_bf16(pre_act, grad_out, grad_pre_act) -> None:
+    """Gradient of silu(gate) * up with respect to pre_act = [gate | up] (bf16 [rows, 2F]); grad_out bf16 [rows, F].
+    Not part of the reference's operator module (its MLP backward is TransformerEngine's)."""
+    dev = _check_tensors([pre_act, grad_out, grad_pre_act], ["pre_act", "grad_out", "grad_pre_act"])
+    _check_dtype([pre_act, grad_out, grad_pre_act], ["pre_act", "grad_out", "grad_pre_act"], torch.bfloat16)
+    _require(pre_act.dim() == 2 and grad_out.dim() == 2 and pre_act.shape == grad_pre_act.shape, "pre_act and grad_pre_act must be [rows, 2F]")
+    _require(pre_act.shape[0] == grad_out.shape[0] and pre_act.shape[1] == 2 * grad_out.shape[1], "grad_out must be [rows, F]")
+    st = _cabi.load().f3d_swiglu_bwd_bf16(_ptr(pre_act), _ptr(grad_out), _ptr(grad_pre_act), pre_act.shape[0], grad_out.shape[1],
+                                          _dev_index(dev), _stream(dev))
+    _cabi.check(st, "swiglu_bwd_bf16")
+
+
+def colsum_bf16(x, out) -> None:
+    """out fp32 [C] = sum over the rows of x bf16 [rows, C] (the bias gradient of a projection), in a fixed order."""
+    dev = _check_tensors([x, out], ["x", "out"])
+    _check_dtype([x], ["x"], torch.bfloat16)
+    _check_dtype([out], ["out"], torch.float32)
+    _require(x.dim() == 2 and out.numel() == x.shape[1], "x must be [rows, C] and out [C]")
+    st = _cabi.load().f3d_colsum_bf16(_ptr(x), _ptr(out), x.shape[0], x.shape[1], _dev_index(dev), _stream(dev))
+    _cabi.check(st, "colsum_bf16")
+
+
 def coord_embed_bf16(coords, weight, bias, out) -> None:
     """out = coords @ weight.T + bias for fp16 coords [rows, 3], fp32 weight [C, 3] / bias [C], bf16 out [rows, C].
     Not part of the reference's operator module (it embeds with te.Linear, flash3dxfmr/layers/psh_ops.py:62)."""

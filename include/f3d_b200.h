@@ -200,6 +200,15 @@ int f3d_layernorm_bf16(const void *x, const void *weight, const void *bias, void
 int f3d_layernorm_bwd_bf16(const void *x, const void *grad_out, const void *weight, void *grad_x, void *grad_weight,
                            void *grad_bias, uint32_t rows, uint32_t C, float eps, int device, void *stream);
 
+/* Backward of the SwiGLU epilogue out = silu(gate) * up: pre_act bf16 [rows, 2F] = [gate | up] (the fc1 GEMM's result
+ * before the activation), grad_out bf16 [rows, F] -> grad_pre_act bf16 [rows, 2F].  The reference's MLP is
+ * TransformerEngine's LayerNormMLP with activation "swiglu" (flash3dxfmr/layers/elem_wise.py); F a multiple of 8. */
+int f3d_swiglu_bwd_bf16(const void *pre_act, const void *grad_out, void *grad_pre_act, uint64_t rows, uint32_t F, int device,
+                        void *stream);
+
+/* Bias gradient: out fp32 [C] = column sums of x bf16 [rows, C], added in a fixed order.  C a multiple of 8, <= 2048. */
+int f3d_colsum_bf16(const void *x, void *out, uint64_t rows, uint32_t C, int device, void *stream);
+
 /* Coordinate embedding out = W x + b: fp16 coordinates [rows, 3], fp32 weight [C, 3] and bias [C], bf16 out [rows, C].
  * Stands in for the te.Linear(3, emb_dim) of PSH3DCoordEmbedding (flash3dxfmr/layers/psh_ops.py:62,77).  C a multiple
  * of 8, <= 2048. */

@@ -126,3 +126,58 @@ def test_linear_input_gradient_runs_native(cuda_device):
     _check(x.grad, ref_gx)
     ref_gw = gy.float().t() @ x.detach().float()
     assert (w.grad - ref_gw).abs().max().item() <= 2e-2 * ref_gw.abs().max().item() + 1e-2
+
+
+@pytest.mark.parametrize("rows,f", [(1, 8), (1000, 128), (4097, 256), (333, 2048)])
+def test_swiglu_backward(cuda_device, rows, f):
+    """Gradient of silu(gate) * up with respect to [gate | up] against fp32 autograd (bf16 outputs)."""
+    from flash3dtransformer_b200.lib import pshattn
+    g = torch.Generator(cuda_device).manual_seed(rows + f)
+    y = (torch.randn(rows, 2 * f, device=cuda_device, generator=g) * 2).bfloat16()
+    go = torch.randn(rows, f, device=cuda_device, generator=g).bfloat16()
+    out = torch.full_like(y, float("nan"))
+    pshattn.swiglu_bwd_bf16(y, go, out)
+    yf = y.float().requires_grad_(True)
+    z = torch.nn.functional.silu(yf[:, :f]) * yf[:, f:]
+    ref, = torch.autograd.grad(z, yf, go.float())
+    assert torch.isfinite(out.float()).all()
+    assert ((out.float() - ref).abs() <= ref.abs() * 2.0 ** -7 + 1e-3).all()
+
+
+@pytest.mark.parametrize("rows,c", [(1, 8), (1000, 96), (70001, 32), (5000, 2048), (63, 512)])
+def test_colsum(cuda_device, rows, c):
+    from flash3dtransformer_b200.lib import pshattn
+    g = torch.Generator(cuda_device).manual_seed(rows + c)
+    x = torch.randn(rows, c, device=cuda_device, generator=g).bfloat16()
+    out = torch.full((c,), float("nan"), device=cuda_device)
+    pshattn.colsum_bf16(x, out)
+    ref = x.double().sum(0)
+    assert (out.double() - ref).abs().max().item() <= 1e-5 * x.float().abs().sum(0).max().item() + 1e-6
+    out2 = torch.empty_like(out)
+    pshattn.colsum_bf16(x, out2)
+    assert torch.equal(out, out2)
+
+
+def test_swiglu_linear_gradients(cuda_device):
+    """LinearFn with the SwiGLU epilogue: input, weight and bias gradients against fp32 autograd."""
+    from flash3dtransformer_b200.layers.functional import LinearFn
+    from flash3dtransformer_b200.lib import pshattn
+    g = torch.Generator(cuda_device).manual_seed(21)
+    x = torch.randn(2048, 64, device=cuda_device, generator=g).bfloat16().requires_grad_(True)
+    w = (torch.randn(256, 64, device=cuda_device, generator=g) / 8).requires_grad_(True)
+    b = (torch.randn(256, device=cuda_device, generator=g) * 0.1).requires_grad_(True)
+    y = LinearFn.apply(x, w, b, None, 1, pshattn.EPI_SWIGLU)
+    gy = torch.randn(2048, 128, device=cuda_device, generator=g).bfloat16()
+    y.backward(gy)
+    xf = x.detach().float().requires_grad_(True)
+    wf = w.detach().bfloat16().float().requires_grad_(True)
+    bf = b.detach().clone().requires_grad_(True)
+    pre = xf @ wf.t() + bf
+    z = torch.nn.functional.silu(pre[:, :128]) * pre[:, 128:]
+    rx, rw, rb = torch.autograd.grad(z, (xf, wf, bf), gy.float())
+    # two bf16 roundings on the way (the pre-activation gradient, then the product with W)
+    err = (x.grad.float() - rx).abs()
+    assert err.max().item() <= 0.03 * rx.abs().max().item()
+    assert (err.mean() / rx.abs().mean()).item() <= 8e-3
+    assert (w.grad - rw).abs().max().item() <= 2e-2 * rw.abs().max().item() + 1e-2
+    assert (b.grad - rb).abs().max().item() <= 2e-2 * rb.abs().max().item() + 1e-2
