@@ -62,12 +62,24 @@ __global__ void __launch_bounds__(256) colsum_partial_kernel(const __nv_bfloat16
   }
 }
 
-__global__ void colsum_reduce_kernel(const float *__restrict__ partial, float *__restrict__ out, uint32_t blocks, uint32_t C) {
-  const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
+// out[c] = sum over the partial rows: 32 x 8 threads per 32 channels, rows ty, ty + 8, ... in order, then the eight
+// slices in order (fixed summation order)
+__global__ void __launch_bounds__(256) colsum_reduce_kernel(const float *__restrict__ partial, float *__restrict__ out, uint32_t blocks,
+                                                            uint32_t C) {
+  __shared__ float red[8][32];
+  const uint32_t tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const uint32_t c = blockIdx.x * 32 + tx;
   float s = 0.f;
-  for (uint32_t b = 0; b < blocks; ++b) s += partial[(size_t)b * C + c];
-  out[c] = s;
+  if (c < C)
+    for (uint32_t b = ty; b < blocks; b += 8) s += partial[(size_t)b * C + c];
+  red[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && c < C) {
+    float t = 0.f;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) t += red[q][tx];
+    out[c] = t;
+  }
 }
 
 }  // namespace f3d
@@ -106,6 +118,6 @@ extern "C" int f3d_colsum_bf16(const void *x, void *out, uint64_t rows, uint32_t
   const uint32_t threads = chunks >= 256 ? chunks : 256 / chunks * chunks;
   colsum_partial_kernel<<<blocks, threads, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), static_cast<float *>(partial), (size_t)rows, C, rows_per_block);
   F3D_TRY(check_launch("colsum_bf16"));
-  colsum_reduce_kernel<<<(C + 127) / 128, 128, 0, st>>>(static_cast<const float *>(partial), static_cast<float *>(out), blocks, C);
+  colsum_reduce_kernel<<<(C + 31) / 32, 256, 0, st>>>(static_cast<const float *>(partial), static_cast<float *>(out), blocks, C);
   return check_launch("colsum_bf16 (reduce)");
 }
