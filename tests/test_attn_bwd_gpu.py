@@ -56,7 +56,8 @@ def test_single_bucket_scopes(cuda_device, d):
 
 
 @pytest.mark.parametrize("b,l,h,d,bucket,k", [(1, 4096, 4, 32, 512, 8), (2, 2048, 8, 32, 512, 2), (1, 1536, 2, 64, 128, 3),
-                                             (1, 1280, 2, 128, 256, 5), (2, 2048, 4, 16, 512, 4)])
+                                             (1, 1280, 2, 128, 256, 5), (2, 2048, 4, 16, 512, 4), (1, 1280, 2, 32, 256, 5),
+                                             (1, 3072, 2, 32, 128, 12)])
 def test_multi_bucket_scopes(cuda_device, b, l, h, d, bucket, k):
     nb = l // bucket
     scopes = [list(range(i, i + k)) for i in range(0, nb, k)]
