@@ -140,7 +140,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       // tile for every 128 rows of A took a third of the time of the narrow-K shapes.)
       const bool w_resident = n_tiles == 1 && kStages % kb_count == 0;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile / n_tiles) * BM, n0 = (tile % n_tiles) * BN;
+        const int mt = n_tiles == 1 ? tile : tile / n_tiles;      // a single column tile is the common case: no division
+        const int m0 = mt * BM, n0 = (tile - mt * n_tiles) * BN;
         for (int kb = 0; kb < kb_count; ++kb, ++it) {
           const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
           if (!tc::mbar_wait(&empty[s], ph ^ 1u, wc, 101)) { ok = false; break; }
@@ -200,13 +201,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     const int out_cols = g.epilogue == EPI_SWIGLU ? BN / 2 : BN;     // output columns produced per tile
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t_local) {
       const uint32_t acc = t_local % kAcc, aph = (t_local / kAcc) & 1u;
-      const int m0 = (tile / n_tiles) * BM, n0 = (tile % n_tiles) * BN;
+      const int mt = n_tiles == 1 ? tile : tile / n_tiles;
+      const int m0 = mt * BM, n0 = (tile - mt * n_tiles) * BN;
       if (!tc::mbar_wait(&acc_full[acc], aph, wc, 104)) { ok = false; break; }
       tc::tc_fence_after_sync();
       const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
       const int row = m0 + q * 32 + lane;
-      for (int c0 = 0; c0 < out_cols; c0 += 32, ++task) {
-        if (task % kSub != sub) continue;
+      // this warp's tasks of the tile: numbers congruent to `sub` modulo kSub, `task` being the tile's first
+      for (int c0 = (int)((sub - task) & (kSub - 1)) * 32; c0 < out_cols; c0 += 32 * (int)kSub) {
         float v[32];
         const int oc0 = (g.epilogue == EPI_SWIGLU ? n0 / 2 : n0) + c0;      // first output column of the task
         // runtime switches (bias, activation) are tested once per task, never per element
@@ -308,11 +310,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         tc::fence_proxy_async();
         __syncwarp();
         if (lane == 0) {
-          tc::tma_store_3d(&map_c, ob, oc0 % g.split_n, m0 + q * 32, oc0 / g.split_n);
+          const int sp = g.nsplit == 1 ? 0 : oc0 / g.split_n;     // which output matrix (no division without splits)
+          tc::tma_store_3d(&map_c, ob, oc0 - sp * g.split_n, m0 + q * 32, sp);
           tc::tma_commit();
         }
         obuf ^= 1u;
       }
+      task += (uint32_t)(out_cols / 32);
       tc::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(&acc_empty[acc]);
