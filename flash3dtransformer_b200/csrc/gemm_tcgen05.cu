@@ -4,11 +4,11 @@
 // flash3dxfmr/layers/buck_swin.py:159,163,185-194) and the toy mma.sync kernel gemm_sm_bf16_ker
 // (src/psh/gemm.cuh:30-85, host src/psh/gemm_dispatcher.cu:26-80, which demands M == 128 and synchronises).
 //
-// Structure (one persistent CTA per SM, 576 threads):
+// Structure (one persistent CTA per SM, 448 threads):
 //   warp 0      TMA producer: A tile 128x64 and W tile BNx64 per stage, 128-byte swizzle, mbarrier completion
 //   warp 1      owns tensor memory; one elected lane issues tcgen05.mma (M=128, N=BN, K=16) four times per
 //               stage and commits the stage's "empty" barrier; after the last k-block it commits "accumulator full"
-//   warps 2-17  epilogue: four warps per 32-lane quadrant of the 128xBN fp32 accumulator; a warp takes 32 columns at
+//   warps 2-13  epilogue: three warps per 32-lane quadrant of the 128xBN fp32 accumulator; a warp takes 32 columns at
 //               a time (tcgen05.ld), adds bias / residual, applies GELU / SwiGLU, converts to bf16, stages the
 //               32x32 block in swizzled shared memory and writes it with a TMA store
 // Up to four accumulators (at most 512 tensor-memory columns) let the epilogues of earlier tiles overlap the MMAs of
@@ -22,7 +22,10 @@
 
 namespace f3d {
 
-constexpr int kEpiWarps = 16;         // four per tensor-memory lane quadrant
+// Three epilogue warps per tensor-memory lane quadrant: with 16 the register file caps a thread at 96 registers and the
+// epilogue spills; 12 warps get 128 registers, spill nothing and execute fewer control instructions per tile (the
+// epilogue is bound by instruction issue): 16.4 ms for the backbone's GEMM mix against 17.3 (16 warps) and 17.9 (8).
+constexpr int kEpiWarps = 12;
 constexpr int kGemmThreads = 64 + 32 * kEpiWarps;     // TMA warp, MMA warp, epilogue warps
 constexpr int BM = 128;
 constexpr int BK = 64;
@@ -189,8 +192,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       }
     }
   } else {
-    // 16 epilogue warps: four per tensor-memory lane quadrant.  A task is 32 output columns of the warp's 32
-    // rows; the tasks of a quadrant are numbered across tiles and dealt round-robin to its four warps, so narrow
+    // Epilogue warps: kEpiWarps / 4 per tensor-memory lane quadrant.  A task is 32 output columns of the warp's 32
+    // rows; the tasks of a quadrant are numbered across tiles and dealt round-robin to its warps, so narrow
     // tiles (one or two tasks) still keep all warps busy, each on a different accumulator buffer.
     const int q = warp & 3;                       // tensor-memory lane quadrant this warp may read
     const uint32_t sub = (uint32_t)(warp - 2) >> 2;     // which of the quadrant's warps
@@ -208,7 +211,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
       const int row = m0 + q * 32 + lane;
       // this warp's tasks of the tile: numbers congruent to `sub` modulo kSub, `task` being the tile's first
-      for (int c0 = (int)((sub - task) & (kSub - 1)) * 32; c0 < out_cols; c0 += 32 * (int)kSub) {
+      for (int c0 = (int)((sub + kSub - task % kSub) % kSub) * 32; c0 < out_cols; c0 += 32 * (int)kSub) {
         float v[32];
         const int oc0 = (g.epilogue == EPI_SWIGLU ? n0 / 2 : n0) + c0;      // first output column of the task
         // runtime switches (bias, activation) are tested once per task, never per element
