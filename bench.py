@@ -583,7 +583,24 @@ def run_psh_pool(args):
             pshattn.additive_unpool_fwd(ff_, down, up, sb_.unpool_ind, 2)
             down = up
 
+    # scatter index of the bucket order, features scattered through it and brought back to the input order
+    psh()
+    out2in = torch.empty(n, dtype=torch.uint32, device=dev)
+    in2out = torch.empty(n, dtype=torch.uint32, device=dev)
+    feat_sc, feat_back = torch.empty_like(feat), torch.empty_like(feat)
+
+    def index():
+        pshattn.scatter_index(buf.bucket_id, buf.bucket_offs, buf.bucket_cumsum, sp, out2in, in2out)
+
+    def gathers():
+        pshattn.gather_rows(feat, out2in, feat_sc)
+        pshattn.gather_rows(feat_sc, in2out, feat_back)
+
     t_psh = _time_ms(psh, args.steps, args.warmup)
+    t_index = _time_ms(index, args.steps, args.warmup)
+    t_gather = _time_ms(gathers, args.steps, args.warmup)
+    if not torch.equal(feat_back, feat):
+        raise RuntimeError("feature scatter followed by its inverse did not reproduce the input")
     t_pool = _time_ms(pools, args.steps, args.warmup)
     t_unpool = _time_ms(unpools, args.steps, args.warmup)
     rows = [lv[0].shape[0] for lv in levels]
@@ -591,6 +608,8 @@ def run_psh_pool(args):
     by_unpool = sum(r * (2.0 * c * 4 + c * 4 / 2 + 4) for r in rows)
     total_ms = t_psh + t_pool + t_unpool
     fam = {"psh_scatter": {"ms": t_psh, "gbs": 18.0 * n / (t_psh * 1e-3) / 1e9},
+           "scatter_index": {"ms": t_index, "gbs": 18.0 * n / (t_index * 1e-3) / 1e9},
+           "feat_scatter_and_restore": {"ms": t_gather, "gbs": 2.0 * n * (2 * c * 4 + 4) / (t_gather * 1e-3) / 1e9},
            "subbuck_pool_x3": {"ms": t_pool, "gbs": by_pool / (t_pool * 1e-3) / 1e9},
            "unpool_x3": {"ms": t_unpool, "gbs": by_unpool / (t_unpool * 1e-3) / 1e9}}
     for f in fam.values():

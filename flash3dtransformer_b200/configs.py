@@ -30,7 +30,9 @@ def hourglass_specs(channels: Sequence[int], depths: Sequence[int], bucket_size:
 
 
 def flash3d_backbone(channels=(32, 64, 128, 256, 512), depths=(2, 2, 2, 6, 2), bucket_size: int = 512,
-                     scope_size: int = 8, hash_op: int = 2):
+                     scope_size: int = 8, hash_op: int = 2, scatter_input_feat: bool = False,
+                     restore_input_order: bool = False):
     """The 5-stage hourglass backbone: channels 32/64/128/256/512, depths 2/2/2/6/2, stride-2 pooling between
     stages, mirrored decoder with additive unpooling."""
-    return layers.Flash3D(hourglass_specs(channels, depths, bucket_size, scope_size), bucket_size, scope_size, hash_op)
+    return layers.Flash3D(hourglass_specs(channels, depths, bucket_size, scope_size), bucket_size, scope_size, hash_op,
+                          scatter_input_feat=scatter_input_feat, restore_input_order=restore_input_order)

@@ -13,6 +13,7 @@ from . import hourglass as f3dhourglass
 from . import psh_ops
 from . import stage as f3dstage
 from ..psh import dev_context as f3ddev
+from .functional import GatherRowsFn
 
 
 class LeafModule(nn.Module):
@@ -41,8 +42,15 @@ class F3DLevelSpecs:
 class Flash3D(nn.Module):
     NVTX_SCOPE = "Flash3D"
 
-    def __init__(self, level_specs: List[F3DLevelSpecs], buck_size: int, scope_size: int, top_level_hash):
+    def __init__(self, level_specs: List[F3DLevelSpecs], buck_size: int, scope_size: int, top_level_hash,
+                 scatter_input_feat: bool = False, restore_input_order: bool = False):
+        """The last two switches (off by default, which is the reference's behaviour) finish what the reference's
+        feature scatter started (src/psh/batch_psh_bucket.cuh:617-753): `scatter_input_feat` brings input_feat [N, C]
+        into bucket order and adds it to the coordinate embedding, `restore_input_order` returns [N, C] features in the
+        order of the input points instead of [pad_to, C] in bucket order."""
         super().__init__()
+        self.scatter_input_feat = scatter_input_feat
+        self.restore_input_order = restore_input_order
         f3ddev.set_sync_stream(False)
         emb_chann = level_specs[0].encoder_specs[0].channels
         self.first_hashtype = top_level_hash
@@ -84,8 +92,16 @@ class Flash3D(nn.Module):
         shard's first scene."""
         if f3ddev.get_nvtx():
             nvtx.range_push(self.NVTX_SCOPE)
-        psh_feat = self.psh_scatter(coords, seps, self.first_hashtype, bbox=bbox, mean_n=mean_n, scene_base=scene_base)
+        if self.scatter_input_feat or self.restore_input_order:
+            psh_feat, (out2in, in2out) = self.psh_scatter(coords, seps, self.first_hashtype, bbox=bbox, mean_n=mean_n,
+                                                          scene_base=scene_base, want_index=True)
+            if self.scatter_input_feat:
+                psh_feat = psh_feat + GatherRowsFn.apply(input_feat.to(psh_feat.dtype), out2in, in2out)
+        else:
+            psh_feat = self.psh_scatter(coords, seps, self.first_hashtype, bbox=bbox, mean_n=mean_n, scene_base=scene_base)
         out = self.module_tree(coords, psh_feat, seps)
+        if self.restore_input_order:
+            out = GatherRowsFn.apply(out, in2out, out2in)
         if f3ddev.get_nvtx():
             nvtx.range_pop()
         return out

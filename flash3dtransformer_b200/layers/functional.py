@@ -54,6 +54,26 @@ class CoordEmbedFn(Function):
         return None, (gf.t() @ x.float()).to(ctx.dtypes[0]), gf.sum(0).to(ctx.dtypes[1])
 
 
+class GatherRowsFn(Function):
+    """out[i] = src[index[i]] (zero rows where index[i] is the padding mark).  `inverse` maps the rows of src to the
+    rows of out, so that the backward is the same gather run through it: with (out2in, in2out) it scatters features into
+    bucket order, with (in2out, out2in) it restores the input order."""
+
+    @staticmethod
+    def forward(ctx, src, index, inverse):
+        out = torch.empty(index.numel(), src.shape[1], dtype=src.dtype, device=src.device)
+        pshattn.gather_rows(src.contiguous(), index, out)
+        ctx.save_for_backward(inverse)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        (inverse,) = ctx.saved_tensors
+        gx = torch.empty(inverse.numel(), g.shape[1], dtype=g.dtype, device=g.device)
+        pshattn.gather_rows(g.contiguous(), inverse, gx)
+        return gx, None, None
+
+
 class LinearFn(Function):
     """y = x W^T + b (+ residual); forward on the tcgen05 GEMM."""
 

@@ -32,11 +32,15 @@ class PSH3DCoordEmbedding(nn.Module):
         self.feat_dtype = feat_dtype
         self.lin = nn.Linear(3, emb_dim)
 
-    def forward(self, coords, seps, hash_op, bbox=None, mean_n=None, scene_base=None):
+    def forward(self, coords, seps, hash_op, bbox=None, mean_n=None, scene_base=None, want_index=False):
+        """Embedded features [pad_to, C] in bucket order; with `want_index` also (out2in, in2out) of the scatter."""
         pad_to = f3darith.cdiv(coords.shape[0], self.alignment) * self.alignment
-        scattered, _ = pm.batch_bucket_scatter(coords, seps, self.bucket_size, pad_to, hash_op, bbox=bbox, mean_n=mean_n,
+        scattered, buffers = pm.batch_bucket_scatter(coords, seps, self.bucket_size, pad_to, hash_op, bbox=bbox, mean_n=mean_n,
                                                 scene_base=scene_base)
         # K = 3 is not a tensor-core GEMM: the embedding kernel does the three FMAs per output
         out = CoordEmbedFn.apply(scattered if scattered.dtype == torch.float16 else scattered.to(torch.float16),
                                  self.lin.weight, self.lin.bias)
-        return out if self.feat_dtype == torch.bfloat16 else out.to(self.feat_dtype)
+        out = out if self.feat_dtype == torch.bfloat16 else out.to(self.feat_dtype)
+        if want_index:
+            return out, pm.scatter_index(buffers, seps, pad_to)
+        return out

@@ -404,6 +404,38 @@ def coord_embed_bf16(coords, weight, bias, out) -> None:
     _cabi.check(st, "coord_embed_bf16")
 
 
+def scatter_index(bucket_id, bucket_offset, cumsum_counter, batch_sep, out2in, in2out=None) -> None:
+    """out2in[row in bucket order] = input row (rows past the input length get len + 3, the padding mark of
+    batch_psh_cumsum_scatter_feat_index_postpad_ker, src/psh/batch_psh_bucket.cuh:667) and, when given,
+    in2out[input row] = row in bucket order, from the outputs of batch_psh_scatter.  The reference declares the
+    operator that would fill scatter_idx_out2in but never binds it."""
+    ts = [bucket_id, bucket_offset, cumsum_counter, batch_sep, out2in] + ([in2out] if in2out is not None else [])
+    dev = _check_tensors(ts, ["bucket_id", "bucket_offset", "cumsum_counter", "batch_sep", "out2in", "in2out"][:len(ts)])
+    _check_dtype([bucket_id], ["bucket_id"], torch.uint16)
+    _check_dtype(ts[1:], ["bucket_offset", "cumsum_counter", "batch_sep", "out2in", "in2out"][:len(ts) - 1], torch.uint32)
+    n = bucket_id.numel()
+    _require(bucket_offset.numel() == n, "bucket_offset must have one entry per point")
+    _require(cumsum_counter.dim() == 2 and cumsum_counter.shape[0] == batch_sep.numel(), "cumsum_counter must be [B, num_bucket]")
+    _require(out2in.numel() >= n, "out2in must hold at least one entry per point")
+    _require(in2out is None or in2out.numel() == n, "in2out must have one entry per point")
+    st = _cabi.load().f3d_scatter_index(_ptr(bucket_id), _ptr(bucket_offset), _ptr(cumsum_counter), _ptr(batch_sep), _ptr(out2in),
+                                        _ptr(in2out) if in2out is not None else None, n, batch_sep.numel(),
+                                        cumsum_counter.shape[1], out2in.numel(), _dev_index(dev), _stream(dev))
+    _cabi.check(st, "scatter_index")
+
+
+def gather_rows(src, index, out) -> None:
+    """out[i] = src[index[i]] over rows of any element type; rows whose index is not a row of src are zero."""
+    dev = _check_tensors([src, index, out], ["src", "index", "out"])
+    _check_dtype([index], ["index"], torch.uint32)
+    _require(src.dim() == 2 and out.dim() == 2 and src.shape[1] == out.shape[1] and src.dtype == out.dtype,
+             "src and out must be [rows, C] of one dtype and width")
+    _require(index.numel() == out.shape[0], "index must have one entry per row of out")
+    st = _cabi.load().f3d_gather_rows(_ptr(src), _ptr(index), _ptr(out), out.shape[0], src.shape[0],
+                                      src.shape[1] * src.element_size(), _dev_index(dev), _stream(dev))
+    _cabi.check(st, "gather_rows")
+
+
 def launch_count() -> int:
     """Kernels launched by the native library since it was loaded."""
     return int(_cabi.load().f3d_launch_count())

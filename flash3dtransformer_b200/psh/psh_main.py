@@ -89,3 +89,16 @@ def batch_bucket_scatter(coords: torch.Tensor, seps: torch.Tensor, bucket_size: 
         bucket_size, NUM_VOX, bbox_min.contiguous(), bbox_max.contiguous(), buffers.probe_offs,
         buffers.bucket_cumsum, buffers.scattered_coord, 0.0, hash_op)
     return buffers.scattered_coord, buffers
+
+
+def scatter_index(buffers: BucketScatterBuffers, seps: torch.Tensor, pad_to: int, inverse: bool = True):
+    """(out2in uint32 [pad_to], in2out uint32 [N] or None) for a finished batch_bucket_scatter: out2in[row in bucket
+    order] = input row (padding rows hold N + 3, the mark of batch_psh_cumsum_scatter_feat_index_postpad_ker,
+    src/psh/batch_psh_bucket.cuh:667), in2out the inverse.  The reference allocates neither: its feature scatter stops
+    at the index (batch_psh_bucket.cuh:735)."""
+    n = buffers.bucket_id.numel()
+    dev = buffers.bucket_id.device
+    out2in = torch.empty(pad_to, dtype=torch.uint32, device=dev)
+    in2out = torch.empty(n, dtype=torch.uint32, device=dev) if inverse else None
+    pshattn.scatter_index(buffers.bucket_id, buffers.bucket_offs, buffers.bucket_cumsum, seps, out2in, in2out)
+    return out2in, in2out

@@ -215,6 +215,23 @@ int f3d_colsum_bf16(const void *x, void *out, uint64_t rows, uint32_t C, int dev
 int f3d_coord_embed_bf16(const void *coords, const void *weight, const void *bias, void *out, uint32_t rows, uint32_t C,
                          int device, void *stream);
 
+/* Scatter index of the bucket order (the part of batch_psh_cumsum_scatter_feat_index_postpad_ker the reference wrote,
+ * src/psh/batch_psh_bucket.cuh:617-753, plus its inverse): from the outputs of f3d_batch_psh_scatter - bucket_id u16 [N],
+ * bucket_offset u32 [N], cumsum_counter u32 [B, num_bucket] (inclusive) and batch_sep u32 [B] (inclusive scene ends) -
+ * out2in u32 [pad_to_N]: out2in[row in bucket order] = input row, rows [total_N, pad_to_N) = total_N + 3 (the
+ * reference's padding mark, batch_psh_bucket.cuh:667); in2out u32 [total_N] (may be NULL): in2out[input row] = row in
+ * bucket order. */
+int f3d_scatter_index(const void *bucket_id, const void *bucket_offset, const void *cumsum_counter, const void *batch_sep,
+                      void *out2in, void *in2out, uint32_t total_N, uint32_t batch_size, uint32_t num_bucket,
+                      uint32_t pad_to_N, int device, void *stream);
+
+/* Row gather out[i, :] = src[index[i], :] for i < rows_out; rows whose index is >= rows_src (the padding mark) are
+ * zero.  Rows are row_bytes bytes (a multiple of 4) of any element type.  With out2in it scatters input features into
+ * bucket order (what scattered_feat of batch_psh_bucket.cuh:627 was meant to receive), with in2out it brings results
+ * back to the input order; each is the other's backward. */
+int f3d_gather_rows(const void *src, const void *index, void *out, uint64_t rows_out, uint32_t rows_src, uint32_t row_bytes,
+                    int device, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

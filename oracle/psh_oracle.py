@@ -276,6 +276,35 @@ def psh_scatter(coord_f16: np.ndarray, seps, num_bucket: int, divisor: int, cap:
                 scattered_coord=scattered)
 
 
+def scatter_index(bucket_id, bucket_offs, bucket_cumsum, seps, pad_to: int):
+    """(out2in [pad_to], in2out [N]): out2in[row in bucket order] = input row with total_N + 3 on the padding rows, as
+    batch_psh_cumsum_scatter_feat_index_postpad_ker writes it (src/psh/batch_psh_bucket.cuh:667, 722-735: destination =
+    scene start + exclusive cumsum of the scene's bucket counters at the point's bucket + its offset in the bucket);
+    in2out is the inverse on the input rows."""
+    n = len(bucket_id)
+    out2in = np.full(pad_to, n + 3, dtype=np.uint32)
+    in2out = np.zeros(n, dtype=np.uint32)
+    start = 0
+    for s, end in enumerate(int(e) for e in seps):
+        if end > start:
+            bid = np.asarray(bucket_id[start:end]).astype(np.int64)
+            incl = np.asarray(bucket_cumsum[s]).astype(np.int64)
+            excl = np.concatenate([[0], incl[:-1]])
+            dst = start + excl[bid] + np.asarray(bucket_offs[start:end]).astype(np.int64)
+            in2out[start:end] = dst
+            out2in[dst] = np.arange(start, end)
+        start = max(start, end)
+    return out2in, in2out
+
+
+def gather_rows(src: np.ndarray, index: np.ndarray) -> np.ndarray:
+    """out[i] = src[index[i]], zero rows where the index is the padding mark (not a row of src)."""
+    out = np.zeros((len(index),) + src.shape[1:], dtype=src.dtype)
+    ok = index < len(src)
+    out[ok] = src[index[ok]]
+    return out
+
+
 def scoreboard_check(bucket_id, bucket_cntr, bucket_offs, seps, num_bucket: int) -> None:
     """src/psh/bucket_sanitizer_cpu.cpp:92-176: every (bucket, offset) slot below the bucket's counter is hit
     exactly once, no id or offset is out of range, and the residual counters return to zero."""

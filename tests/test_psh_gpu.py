@@ -167,3 +167,78 @@ def test_scene_sharded_run_reproduces_full_batch(cuda_device):
         assert torch.equal(mine.bucket_offs.view(torch.int32), full.bucket_offs[r0:r1].view(torch.int32))
         assert torch.equal(mine.scattered_coord.view(torch.int16), full.scattered_coord[r0:r1].view(torch.int16))
     psh_main.f3ddev.get_dev_manager().set_scene_base(0)
+
+
+def _gpu_index(dev, out, seps, pad_to, inverse=True):
+    from flash3dtransformer_b200.lib import pshattn
+    t = lambda k: torch.from_numpy(out[k]).to(dev)
+    sp = torch.from_numpy(np.asarray(seps, dtype=np.uint32)).to(dev)
+    o2i = torch.full((pad_to,), 0x7FFFFFFF, dtype=torch.uint32, device=dev)
+    i2o = torch.empty(len(out["bucket_id"]), dtype=torch.uint32, device=dev) if inverse else None
+    pshattn.scatter_index(t("bucket_id"), t("bucket_offs"), t("bucket_cumsum"), sp, o2i, i2o)
+    torch.cuda.synchronize()
+    return o2i, i2o
+
+
+@pytest.mark.parametrize("sizes,bucket,pad_align", [([20000], 256, 256), ([30000, 17001, 25013, 999], 512, 512 * 6),
+                                                     ([31, 1, 33, 2049, 4097, 5], 64, 7)])
+def test_scatter_index_bit_exact(cuda_device, sizes, bucket, pad_align):
+    coords32, seps = synthetic.batch(synthetic.lidar_scan, sizes, seed=21)
+    c16 = coords32.astype(np.float16)
+    n = c16.shape[0]
+    pad_to = -(-n // pad_align) * pad_align
+    nb, div, out = _gpu_scatter(cuda_device, c16, seps, bucket, 2, pad_to)
+    ref_o2i, ref_i2o = po.scatter_index(out["bucket_id"], out["bucket_offs"], out["bucket_cumsum"], seps, pad_to)
+    o2i, i2o = _gpu_index(cuda_device, out, seps, pad_to)
+    assert np.array_equal(o2i.cpu().numpy(), ref_o2i) and np.array_equal(i2o.cpu().numpy(), ref_i2o)
+    # the inverse index is optional
+    o2i_only, none = _gpu_index(cuda_device, out, seps, pad_to, inverse=False)
+    assert none is None and torch.equal(o2i_only, o2i)
+    # gathering the input coordinates through out2in is the coordinate scatter, bit for bit
+    from flash3dtransformer_b200.lib import pshattn
+    c4 = torch.zeros(n, 4, dtype=torch.float16, device=cuda_device)          # 8-byte rows
+    c4[:, :3] = torch.from_numpy(c16).to(cuda_device)
+    g = torch.empty(pad_to, 4, dtype=torch.float16, device=cuda_device)
+    pshattn.gather_rows(c4, o2i, g)
+    assert np.array_equal(g[:, :3].cpu().numpy().view(np.uint16), out["scattered_coord"].view(np.uint16))
+    back = torch.empty_like(c4)
+    pshattn.gather_rows(g, i2o, back)
+    assert torch.equal(back, c4)
+
+
+def test_scatter_index_empty_scenes(cuda_device):
+    pts = np.concatenate([np.random.default_rng(0).uniform(-5, 5, (700, 3)), np.zeros((1, 3)),
+                          np.full((900, 3), 1.25)]).astype(np.float32)
+    seps = np.array([700, 700, 701, 1601])
+    c16 = pts.astype(np.float16)
+    nb, div, out = _gpu_scatter(cuda_device, c16, seps, 128, 1, 1700)
+    ref_o2i, ref_i2o = po.scatter_index(out["bucket_id"], out["bucket_offs"], out["bucket_cumsum"], seps, 1700)
+    o2i, i2o = _gpu_index(cuda_device, out, seps, 1700)
+    assert np.array_equal(o2i.cpu().numpy(), ref_o2i) and np.array_equal(i2o.cpu().numpy(), ref_i2o)
+
+
+@pytest.mark.parametrize("dtype,width", [(torch.bfloat16, 32), (torch.bfloat16, 36), (torch.float32, 3), (torch.float16, 6),
+                                          (torch.uint8, 20), (torch.bfloat16, 512)])
+def test_gather_rows_bit_exact(cuda_device, dtype, width):
+    from flash3dtransformer_b200.lib import pshattn
+    g = torch.Generator(device="cpu").manual_seed(width)
+    rows_src, rows_out = 5003, 7001
+    src = torch.randint(0, 255, (rows_src, width * torch.empty(0, dtype=dtype).element_size()), dtype=torch.uint8,
+                        generator=g).view(dtype).to(cuda_device)
+    index = torch.randint(0, rows_src + 40, (rows_out,), generator=g).to(torch.uint32)     # some past the end: zero rows
+    out = torch.empty(rows_out, width, dtype=dtype, device=cuda_device)
+    pshattn.gather_rows(src, index.to(cuda_device), out)
+    ref = po.gather_rows(src.cpu().view(torch.uint8).numpy(), index.numpy())
+    assert np.array_equal(out.cpu().view(torch.uint8).numpy(), ref)
+
+
+def test_gather_rows_argument_errors(cuda_device):
+    from flash3dtransformer_b200.lib import pshattn
+    src = torch.zeros(10, 3, dtype=torch.bfloat16, device=cuda_device)                      # 6-byte rows
+    idx = torch.zeros(4, dtype=torch.uint32, device=cuda_device)
+    with pytest.raises(RuntimeError):
+        pshattn.gather_rows(src, idx, torch.empty(4, 3, dtype=torch.bfloat16, device=cuda_device))
+    ok = torch.zeros(10, 4, dtype=torch.bfloat16, device=cuda_device)
+    with pytest.raises(RuntimeError):
+        pshattn.gather_rows(ok, idx, torch.empty(5, 4, dtype=torch.bfloat16, device=cuda_device))
+    pshattn.gather_rows(ok, idx[:0], torch.empty(0, 4, dtype=torch.bfloat16, device=cuda_device))   # empty: no launch

@@ -104,3 +104,23 @@ def test_edge_cases():
     with pytest.raises(ValueError):
         po.psh_scatter(coords, seps, nb, 65535, 128, 0xFFFF, coords.min(0), coords.max(0), po.probe_table(),
                        10, 0.0, 1)
+
+
+def test_scatter_index_is_the_permutation_of_the_coordinate_scatter():
+    # empty scene, single-point scene, odd sizes; padded past the input length
+    coords32, seps = synthetic.batch(synthetic.lidar_scan, [3000, 1, 4500], seed=11)
+    seps = np.array([seps[0], seps[0], seps[1], seps[2]])
+    coords, nb, out = _run(coords32, seps, 128, 2, pad_align=128 * 6)
+    n, pad_to = coords.shape[0], out["scattered_coord"].shape[0]
+    out2in, in2out = po.scatter_index(out["bucket_id"], out["bucket_offs"], out["bucket_cumsum"], seps, pad_to)
+    assert np.array_equal(out2in[in2out], np.arange(n))
+    assert np.all(out2in[n:] == n + 3) and np.all(out2in[:n] < n)
+    # gathering the input coordinates through out2in reproduces the scatter (padding rows are zero)
+    assert np.array_equal(po.gather_rows(coords, out2in).view(np.uint16), out["scattered_coord"].view(np.uint16))
+    # and in2out brings them back
+    assert np.array_equal(po.gather_rows(out["scattered_coord"], in2out).view(np.uint16), coords.view(np.uint16))
+    # a scene keeps its row range
+    start = 0
+    for end in seps:
+        assert np.all((in2out[start:end] >= start) & (in2out[start:end] < end))
+        start = end
