@@ -44,6 +44,7 @@ struct GemmArgs {
   __nv_bfloat16 *c_ptr;
   long long split_stride;
   int *status;
+  int ksplit;            // > 1: A is [ksplit, M, K], W is [ksplit, N, K] and the products of the slices are summed
 };
 
 template <int BN> struct GemmSmem {
@@ -117,7 +118,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = (g.M + BM - 1) / BM, n_tiles = (g.N + BN - 1) / BN;
   const int num_tiles = m_tiles * n_tiles;
-  const int kb_count = (g.K + BK - 1) / BK;
+  const int kb_per_split = (g.K + BK - 1) / BK;
+  const int kb_count = kb_per_split * g.ksplit;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { tc::mbar_init(&full[s], 1); tc::mbar_init(&empty[s], 1); }
@@ -149,20 +151,29 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
           if (!tc::mbar_wait(&empty[s], ph ^ 1u, wc, 101)) { ok = false; break; }
           unsigned char *sa = stage_base + s * S::kStageBytes;
+          // k-block kb of slice sp starts at column kx of rows [sp * M + m0, ...) of A and [sp * N + n0, ...) of W;
+          // columns past K are zero-filled by the copy, rows past a slice's end land in rows or columns never stored
+          int kx = kb * BK, ya = m0, yb = n0;
+          if (g.ksplit > 1) {
+            const int sp = kb / kb_per_split;
+            kx = (kb - sp * kb_per_split) * BK;
+            ya += sp * g.M;
+            yb += sp * g.N;
+          }
           if (w_resident && it >= (uint32_t)kStages) {
             // this stage already holds the W tile of k-block kb from its first use: only A moves
             tc::mbar_expect_tx(&full[s], S::kABytes);
-            tc::tma_load_2d(sa, &map_a, &full[s], kb * BK, m0);
+            tc::tma_load_2d(sa, &map_a, &full[s], kx, ya);
             continue;
           }
           tc::mbar_expect_tx(&full[s], S::kStageBytes);
-          tc::tma_load_2d(sa, &map_a, &full[s], kb * BK, m0);
+          tc::tma_load_2d(sa, &map_a, &full[s], kx, ya);
           if (g.epilogue == EPI_SWIGLU) {
             // gate rows [n0/2, n0/2 + BN/2) and up rows [N/2 + n0/2, ...) of W share one tile
             tc::tma_load_2d(sa + S::kABytes, &map_b, &full[s], kb * BK, n0 / 2);
             tc::tma_load_2d(sa + S::kABytes + S::kBBytes / 2, &map_b, &full[s], kb * BK, g.N / 2 + n0 / 2);
           } else {
-            tc::tma_load_2d(sa + S::kABytes, &map_b, &full[s], kb * BK, n0);
+            tc::tma_load_2d(sa + S::kABytes, &map_b, &full[s], kx, yb);
           }
         }
       }
@@ -365,7 +376,7 @@ static int launch_gemm(const CUtensorMap &ma, const CUtensorMap &mb, const CUten
 
 // C (bf16, nsplit matrices of [M, split_n] with leading dimension split_n, `split_stride` elements apart)
 int linear_bf16(const void *A, int lda, const void *W, int ldw, const void *bias, const void *residual, int ldr, void *C,
-                long long split_stride, int M, int N, int K, int nsplit, int epilogue, int device, cudaStream_t st) {
+                long long split_stride, int M, int N, int K, int nsplit, int epilogue, int device, cudaStream_t st, int ksplit = 1) {
   if (M <= 0 || N <= 0 || K <= 0) return set_error(F3D_ERR_ARG, "gemm: M, N, K must be positive (got %d, %d, %d)", M, N, K);
   if (K % 8 || lda % 8 || ldw % 8) return set_error(F3D_ERR_ARG, "gemm: K and the leading dimensions must be multiples of 8 (TMA 16-byte rule)");
   if (nsplit < 1 || N % nsplit) return set_error(F3D_ERR_ARG, "gemm: N=%d is not divisible into %d splits", N, nsplit);
@@ -375,6 +386,9 @@ int linear_bf16(const void *A, int lda, const void *W, int ldw, const void *bias
   int split_n = out_n / nsplit;
   if (split_n % 8) return set_error(F3D_ERR_ARG, "gemm: output row length %d is not a multiple of 8", split_n);
   if (residual && nsplit != 1) return set_error(F3D_ERR_ARG, "gemm: residual needs nsplit == 1");
+  if (ksplit < 1 || (ksplit > 1 && (epilogue == EPI_SWIGLU || lda != K || ldw != K)))
+    return set_error(F3D_ERR_ARG, "gemm: %d slices along K need dense operands and no SwiGLU epilogue", ksplit);
+  if ((long long)ksplit * M > 0x7FFFFFFFll) return set_error(F3D_ERR_UNSUPPORTED, "gemm: %d slices of %d rows exceed the copy coordinates", ksplit, M);
   int BN = 256;
   if (epilogue == EPI_SWIGLU) BN = (N % 256 == 0) ? 256 : 128;
   else if (N <= 32) BN = 32;
@@ -383,13 +397,13 @@ int linear_bf16(const void *A, int lda, const void *W, int ldw, const void *bias
   const int direct = (nsplit > 1 && split_n % 32) ? 1 : 0;      // a 32-column task must not straddle two outputs
   if (reinterpret_cast<uintptr_t>(C) % 16) return set_error(F3D_ERR_ARG, "gemm: output pointer is not 16-byte aligned");
   CUtensorMap ma, mb, mc;
-  F3D_TRY(encode_tmap_2d(&ma, 0, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, BM, 128));
+  F3D_TRY(encode_tmap_2d(&ma, 0, A, (uint64_t)K, (uint64_t)M * ksplit, (uint64_t)lda * 2, BK, BM, 128));
   int b_box_rows = epilogue == EPI_SWIGLU ? BN / 2 : BN;
-  F3D_TRY(encode_tmap_2d(&mb, 0, W, (uint64_t)K, (uint64_t)N, (uint64_t)ldw * 2, BK, b_box_rows, 128));
+  F3D_TRY(encode_tmap_2d(&mb, 0, W, (uint64_t)K, (uint64_t)N * ksplit, (uint64_t)ldw * 2, BK, b_box_rows, 128));
   F3D_TRY(encode_tmap_3d(&mc, 0, C, (uint64_t)split_n, (uint64_t)M, (uint64_t)nsplit, (uint64_t)split_n * 2,
                          (uint64_t)split_stride * 2, 32, 32, 1, 64));
   GemmArgs g{M, N, K, nsplit, split_n, static_cast<const float *>(bias), static_cast<const __nv_bfloat16 *>(residual), ldr,
-             epilogue, direct, static_cast<__nv_bfloat16 *>(C), split_stride, status_word(device)};
+             epilogue, direct, static_cast<__nv_bfloat16 *>(C), split_stride, status_word(device), ksplit};
   if (!g.status) return F3D_ERR_CUDA;
   switch (BN) {
     case 32: return launch_gemm<32>(ma, mb, mc, g, device, st);
@@ -412,6 +426,15 @@ extern "C" int f3d_linear_bf16(const void *A, const void *W, const void *bias, c
   F3D_TRY(linear_bf16(A, K, W, K, bias, residual, out_n, C, (long long)M * (out_n / (nsplit > 0 ? nsplit : 1)), M, N, K, nsplit,
                       epilogue, device, st));
   return maybe_sync(st, "linear_bf16");
+}
+
+extern "C" int f3d_linear_ksplit_bf16(const void *A, const void *W, const void *bias, const void *residual, void *C, int M, int N,
+                                      int K, int ksplit, int device, void *stream) {
+  DeviceGuard guard(device);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  F3D_TRY(maybe_sync(st, "linear_ksplit_bf16"));
+  F3D_TRY(linear_bf16(A, K, W, K, bias, residual, N, C, (long long)M * N, M, N, K, 1, EPI_NONE, device, st, ksplit));
+  return maybe_sync(st, "linear_ksplit_bf16");
 }
 
 // O[M,N] = A[M,K] . B[K,N]: the reference's gemm_sm_bf16 export (src/psh/gemm_dispatcher.cu:26-80).  B is

@@ -124,14 +124,14 @@ extern "C" int f3d_layernorm_bf16(const void *x, const void *weight, const void 
   auto yp = static_cast<__nv_bfloat16 *>(y);
   auto wp = static_cast<const float *>(weight), bp = static_cast<const float *>(bias);
   if (nchunk >= 2 && nchunk <= 32 && (nchunk & (nchunk - 1)) == 0) {
-    // rows of 16..256 channels: two 16-byte chunks per lane (32 bytes in flight per thread and one shuffle level
-    // fewer measured 6-13 % faster than one chunk per lane)
+    // rows of 16..256 channels: two 16-byte chunks per lane (one shuffle level fewer: 6-13 % faster than one chunk)
+    // and two rows per lane group, so a thread has four loads in flight (another 10-14 %; four rows: 30 % slower)
     switch (nchunk / 2) {
-      case 1: launch_ln<1, 2, 1>(xp, wp, bp, yp, rows, C, eps, gelu, st); break;
-      case 2: launch_ln<2, 2, 1>(xp, wp, bp, yp, rows, C, eps, gelu, st); break;
-      case 4: launch_ln<4, 2, 1>(xp, wp, bp, yp, rows, C, eps, gelu, st); break;
-      case 8: launch_ln<8, 2, 1>(xp, wp, bp, yp, rows, C, eps, gelu, st); break;
-      default: launch_ln<16, 2, 1>(xp, wp, bp, yp, rows, C, eps, gelu, st); break;
+      case 1: launch_ln<1, 2, 2>(xp, wp, bp, yp, rows, C, eps, gelu, st); break;
+      case 2: launch_ln<2, 2, 2>(xp, wp, bp, yp, rows, C, eps, gelu, st); break;
+      case 4: launch_ln<4, 2, 2>(xp, wp, bp, yp, rows, C, eps, gelu, st); break;
+      case 8: launch_ln<8, 2, 2>(xp, wp, bp, yp, rows, C, eps, gelu, st); break;
+      default: launch_ln<16, 2, 2>(xp, wp, bp, yp, rows, C, eps, gelu, st); break;
     }
     return check_launch("layernorm_bf16");
   }

@@ -41,6 +41,38 @@ class BuckSwinFwdFunction(Function):
         return bwd.dQ, bwd.dK, bwd.dV, None, None
 
 
+class BuckSwinPackedFunction(Function):
+    """The same attention with Q, K and V given as the three [B*L, C] matrices of one packed tensor, the layout the QKV
+    projection writes.  The backward hands the three slices of ONE packed gradient to buck_swin_bwd, so autograd neither
+    zero-fills a packed gradient per slice nor adds the three up (which cost more HBM traffic than the projection
+    itself)."""
+
+    @staticmethod
+    def forward(ctx, qkv, shape, scope_buckets, buck_size: int):
+        b, l, h, d = shape
+        Q, K, V = (qkv[i].view(b, l, h, d) for i in range(3))
+        buff = sa.BuckSwinFwdBuffers.create_buckswin_fwd_buff(Q)
+        pshattn.buck_swin_fwd(Q, K, V, buff.O, buff.LSE, scope_buckets, buck_size)
+        ctx.save_for_backward(qkv, buff.O, buff.LSE)
+        ctx.cfg = (shape, scope_buckets, buck_size)
+        return buff.O
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        qkv, O, lse = ctx.saved_tensors
+        shape, scope_buckets, buck_size = ctx.cfg
+        b, l, h, d = shape
+        # scope tables made by SwinPlan are marked when they put every bucket in exactly one scope; then every row of
+        # the gradient is written by the kernel and the buffer needs no zero fill
+        covered = getattr(scope_buckets, "_f3d_partition_of", -1) == l
+        grad = torch.empty_like(qkv) if covered else torch.zeros_like(qkv)
+        Q, K, V = (qkv[i].view(b, l, h, d) for i in range(3))
+        dQ, dK, dV = (grad[i].view(b, l, h, d) for i in range(3))
+        delta = torch.empty(b, l, h, dtype=torch.float32, device=O.device)      # every row is written by the delta kernel
+        pshattn.buck_swin_bwd(Q, K, V, O, grad_output.contiguous(), lse, delta, dQ, dK, dV, scope_buckets, buck_size)
+        return grad, None, None, None
+
+
 class BucketSwinAttention(nn.Module):
     def __init__(self, buck_size: int) -> None:
         super().__init__()
@@ -72,8 +104,7 @@ class BucketSwinAttentionModule(nn.Module):
         if f3ddev.get_nvtx():
             nvtx.range_push(self.NVTX_SCOPE)
         qkv = F3.linear(x.reshape(b * l, c), self.qkv.weight, self.qkv.bias, nsplit=3)       # [3, B*L, C]
-        q, k, v = (qkv[i].view(b, l, self.num_heads, self.head_dim) for i in range(3))
-        attn_out = self.attn(q, k, v, scope_buckets)
+        attn_out = BuckSwinPackedFunction.apply(qkv, (b, l, self.num_heads, self.head_dim), scope_buckets, self.attn.buck_size)
         out = F3.linear(attn_out.view(b * l, c), self.proj.weight, self.proj.bias, residual=residual).view(b, l, c)
         if f3ddev.get_nvtx():
             nvtx.range_pop()

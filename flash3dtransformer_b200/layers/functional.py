@@ -97,7 +97,7 @@ class LinearFn(Function):
         nsplit, epilogue, has_res = ctx.cfg
         wb = bf16_weight(weight)
         if nsplit > 1:
-            g = g.permute(1, 0, 2).reshape(g.shape[1], -1)
+            return LinearFn._backward_split(xb, weight, bias, wb, g.contiguous())
         g = g.contiguous()
         g_res = g if has_res else None
         if epilogue == pshattn.EPI_SWIGLU:
@@ -127,13 +127,39 @@ class LinearFn(Function):
         return gx, gw, gb, g_res, None, None
 
 
+def _split_backward(xb, weight, bias, wb, g):
+    """Backward of a projection whose output is nsplit separate matrices: g is the packed gradient [S, M, C]."""
+    s, m, c = g.shape
+    # grad_x = sum_s g[s] W_s as one GEMM over the slices; W_s^T ([in, C] per slice) is a small matrix
+    wt = wb.view(s, c, wb.shape[1]).transpose(1, 2).contiguous()
+    gx = torch.empty(m, wb.shape[1], dtype=torch.bfloat16, device=g.device)
+    pshattn.linear_ksplit_bf16(g, wt, gx)
+    gw = torch.empty(s * c, xb.shape[1], dtype=torch.bfloat16, device=g.device)
+    for i in range(s):
+        torch.mm(g[i].t(), xb, out=gw[i * c:(i + 1) * c])
+    gw = gw.to(weight.dtype)
+    gb = None
+    if bias is not None:
+        if c % 8 == 0 and c <= 2048:
+            gb32 = torch.empty(s, c, dtype=torch.float32, device=g.device)
+            for i in range(s):
+                pshattn.colsum_bf16(g[i], gb32[i])
+            gb = gb32.reshape(-1).to(bias.dtype)
+        else:
+            gb = g.float().sum(1).reshape(-1).to(bias.dtype)
+    return gx, gw, gb, None, None, None
+
+
+LinearFn._backward_split = staticmethod(_split_backward)
+
+
 def linear(x, weight, bias=None, residual=None, nsplit=1, epilogue=pshattn.EPI_NONE):
     return LinearFn.apply(x, weight, bias, residual, nsplit, epilogue)
 
 
 class LayerNormFn(Function):
-    """LayerNorm (+ optional GELU) on the native kernels, forward and backward; with the fused GELU the backward falls
-    back to autograd of the fp32 torch formula."""
+    """LayerNorm (+ optional GELU) on the native kernels, forward and backward; with the fused GELU the backward
+    recomputes the normalised rows, takes the gradient through the activation and runs the same native backward."""
 
     @staticmethod
     def forward(ctx, x, weight, bias, eps, gelu):
@@ -148,8 +174,12 @@ class LayerNormFn(Function):
     def backward(ctx, g):
         xb, weight, bias = ctx.saved_tensors
         eps, gelu = ctx.cfg
-        if not gelu and xb.shape[1] <= 1024:
+        if xb.shape[1] <= 1024:
             gb16 = (g if g.dtype == torch.bfloat16 else g.to(torch.bfloat16)).contiguous()
+            if gelu:
+                y = torch.empty_like(xb)
+                pshattn.layernorm_bf16(xb, weight.detach().float().contiguous(), bias.detach().float().contiguous(), y, eps, False)
+                gb16 = torch.ops.aten.gelu_backward(gb16, y, approximate="none")
             gx = torch.empty_like(xb)
             gw = torch.empty(xb.shape[1], dtype=torch.float32, device=xb.device)
             gb = torch.empty_like(gw)

@@ -315,6 +315,31 @@ def linear_bf16(x, weight, bias, out, residual=None, nsplit=1, epilogue=EPI_NONE
     _cabi.check(st, "linear_bf16")
 
 
+def linear_ksplit_bf16(x, weight, out, bias=None, residual=None) -> None:
+    """out [M, N] = sum_s x[s] @ weight[s]^T for x bf16 [S, M, K] and weight bf16 [S, N, K]: the input gradient of a
+    projection whose output is S separate matrices (Q, K, V), computed from the packed gradient in one GEMM."""
+    tensors, names = [x, weight, out], ["x", "weight", "out"]
+    if residual is not None:
+        tensors.append(residual); names.append("residual")
+    dev = _check_tensors(tensors, names)
+    _check_dtype(tensors, names, torch.bfloat16)
+    _require(x.dim() == 3 and weight.dim() == 3 and x.shape[0] == weight.shape[0] and x.shape[2] == weight.shape[2],
+             f"x must be [S, M, K] and weight [S, N, K], got {tuple(x.shape)} and {tuple(weight.shape)}")
+    s, m, k = x.shape
+    n = weight.shape[1]
+    _require(tuple(out.shape) == (m, n), f"out must be [{m},{n}]")
+    _require(residual is None or tuple(residual.shape) == (m, n), f"residual must be [{m},{n}]")
+    bptr = ctypes.c_void_p(0)
+    if bias is not None:
+        _check_tensors([bias], ["bias"])
+        _check_dtype([bias], ["bias"], torch.float32)
+        _require(bias.numel() == n, f"bias must have {n} elements")
+        bptr = _ptr(bias)
+    st = _cabi.load().f3d_linear_ksplit_bf16(_ptr(x), _ptr(weight), bptr, _ptr(residual) if residual is not None else None,
+                                             _ptr(out), m, n, k, s, _dev_index(dev), _stream(dev))
+    _cabi.check(st, "linear_ksplit_bf16")
+
+
 # --------------------------------------------------------------------------------------- bucketed attention
 def _check_qkv(tensors, names):
     dev = _check_tensors(tensors, names)

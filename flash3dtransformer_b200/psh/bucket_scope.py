@@ -79,7 +79,12 @@ class SwinPlan:
     def gen_scopes_from_plan(self, total_N: int, device) -> torch.Tensor:
         key = (total_N, self.plan_name, self.buck_size, self.scope_size_in_buck, str(device))
         if key not in _SCOPE_CACHE:
-            _SCOPE_CACHE[key] = torch.tensor(self.scope_list(total_N), dtype=torch.uint32).to(device)
+            scopes = self.scope_list(total_N)
+            t = torch.tensor(scopes, dtype=torch.uint32).to(device)
+            # every bucket in exactly one scope: the attention backward then writes every gradient row itself
+            flat = sorted(b for sc in scopes for b in sc)
+            t._f3d_partition_of = total_N if flat == list(range(total_N // self.buck_size)) else -1
+            _SCOPE_CACHE[key] = t
         return _SCOPE_CACHE[key]
 
 

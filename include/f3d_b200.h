@@ -215,6 +215,13 @@ int f3d_colsum_bf16(const void *x, void *out, uint64_t rows, uint32_t C, int dev
 int f3d_coord_embed_bf16(const void *coords, const void *weight, const void *bias, void *out, uint32_t rows, uint32_t C,
                          int device, void *stream);
 
+/* Sum of slice products C[M, N] = sum_s A[s] W[s]^T (+ bias) (+ residual): A bf16 [ksplit, M, K], W bf16 [ksplit, N, K],
+ * both dense.  One GEMM whose k-blocks walk the slices; it is the input gradient of a projection that wrote its output as
+ * separate matrices (the Q, K, V layout of f3d_linear_bf16 with nsplit = 3: grad_x = sum_s grad[s] W_s), without first
+ * interleaving the three gradients.  K a multiple of 8. */
+int f3d_linear_ksplit_bf16(const void *A, const void *W, const void *bias, const void *residual, void *C, int M, int N, int K,
+                           int ksplit, int device, void *stream);
+
 /* Scatter index of the bucket order (the part of batch_psh_cumsum_scatter_feat_index_postpad_ker the reference wrote,
  * src/psh/batch_psh_bucket.cuh:617-753, plus its inverse): from the outputs of f3d_batch_psh_scatter - bucket_id u16 [N],
  * bucket_offset u32 [N], cumsum_counter u32 [B, num_bucket] (inclusive) and batch_sep u32 [B] (inclusive scene ends) -

@@ -181,3 +181,44 @@ def test_swiglu_linear_gradients(cuda_device):
     assert (err.mean() / rx.abs().mean()).item() <= 8e-3
     assert (w.grad - rw).abs().max().item() <= 2e-2 * rw.abs().max().item() + 1e-2
     assert (b.grad - rb).abs().max().item() <= 2e-2 * rb.abs().max().item() + 1e-2
+
+
+@pytest.mark.parametrize("s,m,n,k", [(3, 1024, 32, 32), (3, 3000, 64, 64), (3, 777, 128, 128), (3, 1536, 256, 256),
+                                     (3, 640, 512, 512), (2, 333, 96, 40), (4, 129, 64, 200)])
+def test_linear_ksplit(cuda_device, s, m, n, k):
+    """Sum of slice products (one GEMM over the K slices): also a last row tile that runs into the next slice's rows
+    and K that is not a multiple of the 64-column k-block."""
+    from flash3dtransformer_b200.lib import pshattn
+    g = torch.Generator(cuda_device).manual_seed(s * 1000 + m)
+    x = torch.randn(s, m, k, device=cuda_device, generator=g).bfloat16()
+    w = (torch.randn(s, n, k, device=cuda_device, generator=g) / (s * k) ** 0.5).bfloat16()
+    out = torch.full((m, n), float("nan"), device=cuda_device, dtype=torch.bfloat16)
+    pshattn.linear_ksplit_bf16(x, w, out)
+    pshattn.device_status()
+    ref = torch.einsum("smk,snk->mn", x.float(), w.float())
+    _check(out, ref)
+    b = torch.randn(n, device=cuda_device, generator=g) * 0.1
+    res = torch.randn(m, n, device=cuda_device, generator=g).bfloat16()
+    pshattn.linear_ksplit_bf16(x, w, out, bias=b, residual=res)
+    _check(out, ref + b + res.float(), max_abs=4e-2)
+    with pytest.raises(RuntimeError):
+        pshattn.linear_ksplit_bf16(x, w[:, :, : k - 8].contiguous(), out)
+
+
+def test_split_projection_gradients(cuda_device):
+    """Backward of the Q/K/V projection (packed gradient [3, M, C]) against fp32 autograd."""
+    from flash3dtransformer_b200.layers.functional import LinearFn
+    g = torch.Generator(cuda_device).manual_seed(9)
+    m, c = 2000, 64
+    x = torch.randn(m, c, device=cuda_device, generator=g).bfloat16().requires_grad_(True)
+    w = (torch.randn(3 * c, c, device=cuda_device, generator=g) / 8).requires_grad_(True)
+    b = torch.zeros(3 * c, device=cuda_device, requires_grad=True)
+    y = LinearFn.apply(x, w, b, None, 3, 0)                       # [3, m, c]
+    gy = torch.randn(3, m, c, device=cuda_device, generator=g).bfloat16()
+    y.backward(gy)
+    flat = gy.permute(1, 0, 2).reshape(m, 3 * c).float()
+    _check(x.grad, flat @ w.detach().bfloat16().float())
+    ref_gw = flat.t() @ x.detach().float()
+    assert (w.grad - ref_gw).abs().max().item() <= 2e-2 * ref_gw.abs().max().item() + 1e-2
+    ref_gb = flat.sum(0)
+    assert (b.grad - ref_gb).abs().max().item() <= 1e-3 * ref_gb.abs().max().item() + 1e-3

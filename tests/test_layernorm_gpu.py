@@ -67,3 +67,24 @@ def test_layernorm_autograd_path(cuda_device):
     rx, = torch.autograd.grad(ref, xf, go.float())
     assert ((xr.grad.float() - rx).abs() <= rx.abs() * 2.0 ** -7 + 3e-3).all()
     assert wr.grad is not None and br.grad is not None
+
+
+def test_layernorm_gelu_autograd_path(cuda_device):
+    """LayerNorm with the fused GELU: the backward recomputes the normalised rows (bf16), takes the gradient through
+    the activation and runs the native LayerNorm backward; compared with fp32 autograd of the same formula.  The extra
+    bf16 rounding of the recomputed rows allows 2^-6 relative."""
+    from flash3dtransformer_b200.layers.functional import layer_norm
+    x, w, b, go = _inputs(cuda_device, 5000, 64, 4)
+    xr = x.clone().requires_grad_(True)
+    wr, br = w.clone().requires_grad_(True), b.clone().requires_grad_(True)
+    y = layer_norm(xr, wr, br, gelu=True)
+    y.backward(go)
+    xf = x.float().requires_grad_(True)
+    wf, bf = w.clone().requires_grad_(True), b.clone().requires_grad_(True)
+    ref = torch.nn.functional.gelu(torch.nn.functional.layer_norm(xf, (64,), wf, bf, 1e-5))
+    rx, rw, rb = torch.autograd.grad(ref, (xf, wf, bf), go.float())
+    err = (xr.grad.float() - rx).abs()
+    assert (err <= rx.abs() * 2.0 ** -6 + 2e-2).all(), err.max().item()
+    assert err.mean().item() <= 2e-3 * rx.abs().mean().item() + 1e-4
+    assert (wr.grad - rw).abs().max().item() <= 5e-3 * rw.abs().max().item() + 5e-2
+    assert (br.grad - rb).abs().max().item() <= 5e-3 * rb.abs().max().item() + 5e-2
