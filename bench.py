@@ -596,6 +596,17 @@ def run_psh_pool(args):
         pshattn.gather_rows(feat, out2in, feat_sc)
         pshattn.gather_rows(feat_sc, in2out, feat_back)
 
+    # scan records (x, y, z, intensity as fp32) to fp16 coordinates + intensity: the front end of a real data loader
+    records = torch.cat([coords.float(), torch.rand(n, 1, device=dev)], dim=1).contiguous()
+    rec_coords = torch.empty(n, 3, dtype=torch.float16, device=dev)
+    rec_extra = torch.empty(n, 1, dtype=torch.float32, device=dev)
+
+    def collate():
+        pshattn.collate_points_f32(records, rec_coords, rec_extra)
+
+    t_collate = _time_ms(collate, args.steps, args.warmup)
+    if not torch.equal(rec_coords, coords):
+        raise RuntimeError("collated coordinates differ from the input coordinates")
     t_psh = _time_ms(psh, args.steps, args.warmup)
     t_index = _time_ms(index, args.steps, args.warmup)
     t_gather = _time_ms(gathers, args.steps, args.warmup)
@@ -608,6 +619,7 @@ def run_psh_pool(args):
     by_unpool = sum(r * (2.0 * c * 4 + c * 4 / 2 + 4) for r in rows)
     total_ms = t_psh + t_pool + t_unpool
     fam = {"psh_scatter": {"ms": t_psh, "gbs": 18.0 * n / (t_psh * 1e-3) / 1e9},
+           "collate_points": {"ms": t_collate, "gbs": 26.0 * n / (t_collate * 1e-3) / 1e9},
            "scatter_index": {"ms": t_index, "gbs": 18.0 * n / (t_index * 1e-3) / 1e9},
            "feat_scatter_and_restore": {"ms": t_gather, "gbs": 2.0 * n * (2 * c * 4 + 4) / (t_gather * 1e-3) / 1e9},
            "subbuck_pool_x3": {"ms": t_pool, "gbs": by_pool / (t_pool * 1e-3) / 1e9},

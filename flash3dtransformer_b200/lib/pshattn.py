@@ -429,6 +429,23 @@ def coord_embed_bf16(coords, weight, bias, out) -> None:
     _cabi.check(st, "coord_embed_bf16")
 
 
+def collate_points_f32(records, coords, extra=None) -> None:
+    """records fp32 [rows, dim] (x, y, z, further channels) -> coords fp16 [rows, 3] and extra fp32 [rows, dim - 3]:
+    the cast and slice of collate_coords_flat_sep (flash3dxfmr/psh/batching.py:13-28) in one pass on the device."""
+    ts = [records, coords] + ([extra] if extra is not None else [])
+    dev = _check_tensors(ts, ["records", "coords", "extra"][:len(ts)])
+    _check_dtype([records], ["records"], torch.float32)
+    _check_dtype([coords], ["coords"], torch.float16)
+    _require(records.dim() == 2 and tuple(coords.shape) == (records.shape[0], 3), "records must be [rows, dim], coords [rows, 3]")
+    if extra is not None:
+        _check_dtype([extra], ["extra"], torch.float32)
+        _require(records.shape[1] > 3 and tuple(extra.shape) == (records.shape[0], records.shape[1] - 3),
+                 "extra must be [rows, dim - 3]")
+    st = _cabi.load().f3d_collate_points_f32(_ptr(records), _ptr(coords), _ptr(extra) if extra is not None else None,
+                                             records.shape[0], records.shape[1], _dev_index(dev), _stream(dev))
+    _cabi.check(st, "collate_points_f32")
+
+
 def scatter_index(bucket_id, bucket_offset, cumsum_counter, batch_sep, out2in, in2out=None) -> None:
     """out2in[row in bucket order] = input row (rows past the input length get len + 3, the padding mark of
     batch_psh_cumsum_scatter_feat_index_postpad_ker, src/psh/batch_psh_bucket.cuh:667) and, when given,

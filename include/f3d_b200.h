@@ -222,6 +222,13 @@ int f3d_coord_embed_bf16(const void *coords, const void *weight, const void *bia
 int f3d_linear_ksplit_bf16(const void *A, const void *W, const void *bias, const void *residual, void *C, int M, int N, int K,
                            int ksplit, int device, void *stream);
 
+/* Raw scan records to operator inputs: records fp32 [rows, point_dim] (x, y, z, then intensity / ring / time; the
+ * layout of KITTI and nuScenes .bin files, point_dim 3..6) -> coords fp16 [rows, 3] (round to nearest even) and, when
+ * extra is not NULL, extra fp32 [rows, point_dim - 3].  One pass on the device in place of the cast, slice and copy of
+ * collate_coords_flat_sep (flash3dxfmr/psh/batching.py:13-28). */
+int f3d_collate_points_f32(const void *records, void *coords, void *extra, uint64_t rows, uint32_t point_dim, int device,
+                           void *stream);
+
 /* Scatter index of the bucket order (the part of batch_psh_cumsum_scatter_feat_index_postpad_ker the reference wrote,
  * src/psh/batch_psh_bucket.cuh:617-753, plus its inverse): from the outputs of f3d_batch_psh_scatter - bucket_id u16 [N],
  * bucket_offset u32 [N], cumsum_counter u32 [B, num_bucket] (inclusive) and batch_sep u32 [B] (inclusive scene ends) -

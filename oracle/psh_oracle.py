@@ -305,6 +305,16 @@ def gather_rows(src: np.ndarray, index: np.ndarray) -> np.ndarray:
     return out
 
 
+def collate_points(records: np.ndarray, sizes):
+    """(coords fp16 [N, 3], extra fp32 [N, dim - 3], seps uint32 [B]) from fp32 point records: the cast, slice and
+    cumulative sizes of collate_coords_flat_sep (flash3dxfmr/psh/batching.py:13-28; numpy's float16 cast rounds to
+    nearest even like torch's)."""
+    records = np.asarray(records, dtype=np.float32)
+    with np.errstate(over="ignore"):
+        coords = records[:, :3].astype(np.float16)
+    return coords, np.ascontiguousarray(records[:, 3:]), np.cumsum(np.asarray(sizes, dtype=np.int64)).astype(np.uint32)
+
+
 def scoreboard_check(bucket_id, bucket_cntr, bucket_offs, seps, num_bucket: int) -> None:
     """src/psh/bucket_sanitizer_cpu.cpp:92-176: every (bucket, offset) slot below the bucket's counter is hit
     exactly once, no id or offset is out of range, and the residual counters return to zero."""
