@@ -487,6 +487,17 @@ def run_train_step(args, rank: int, world: int, local_rank: int):
     coords = torch.from_numpy(c16).to(dev)
     seps_dev = torch.from_numpy(seps).to(dev)
     batching.host_seps(seps_dev)
+    # micro-batches of whole scenes: gradients accumulate over them, so a rank's share of a large batch (64 scenes of
+    # 200k points on one GPU) runs in the memory of one micro-batch; every micro-batch uses the global PSH statistics
+    micro = args.micro_scenes if args.micro_scenes > 0 else args.scenes
+    chunks = []
+    for s0 in range(0, args.scenes, micro):
+        s1 = min(args.scenes, s0 + micro)
+        lo = int(seps[s0 - 1]) if s0 else 0
+        sp = torch.from_numpy((seps[s0:s1].astype(np.int64) - lo).astype(np.uint32)).to(dev)
+        batching.host_seps(sp)
+        chunks.append((coords[lo:int(seps[s1 - 1])], sp, rank * args.scenes + s0))
+    total_rows = float(coords.shape[0])
     n_params = sum(p.numel() for p in model.parameters())
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
     t_ar = [0.0]
@@ -494,9 +505,12 @@ def run_train_step(args, rank: int, world: int, local_rank: int):
     def step(timed: bool):
         opt.zero_grad(set_to_none=True)
         bbox, mean_n = parallel.global_psh_stats(coords, seps_dev)
-        out = model(coords, None, seps_dev, bbox=bbox, mean_n=mean_n, scene_base=rank * args.scenes)
-        loss = out.float().square().mean()
-        loss.backward()
+        loss = None
+        for c, sp, base in chunks:
+            out = model(c, None, sp, bbox=bbox, mean_n=mean_n, scene_base=base)
+            part = out.float().square().mean() * (c.shape[0] / total_rows)
+            part.backward()
+            loss = part.detach() if loss is None else loss + part.detach()
         if world > 1:
             if timed:
                 ev[2].record()
@@ -535,7 +549,8 @@ def run_train_step(args, rank: int, world: int, local_rank: int):
                           "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
                           "higher_is_better": True, "scaling": "weak", "dtype": "bf16", "data": "synthetic",
                           "config": {"workload": f"flash3d_backbone_train_step_{args.scenes}x{args.points // 1000}k_per_gpu",
-                                     "parameters": n_params, "grad_allreduce_bytes": 4 * n_params},
+                                     "micro_batch_scenes": micro, "parameters": n_params, "grad_allreduce_bytes": 4 * n_params},
+                          "peak_memory_gb": torch.cuda.max_memory_allocated(dev) / 1e9,
                           "grad_allreduce_ms_per_step": ms[1].item() / args.steps, "loss": float(loss.detach())}), flush=True)
 
 
@@ -641,6 +656,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--scenes", type=int, default=SCENES_PER_GPU)
     ap.add_argument("--points", type=int, default=POINTS_PER_SCENE)
+    ap.add_argument("--micro-scenes", type=int, default=0, help="train_step: scenes per micro-batch (gradient accumulation); 0 = all")
     ap.add_argument("--ref-points", type=int, default=20000, help="points of the CPU arm's bounded sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="backbone", choices=["backbone", "attn_layer", "psh_pool", "gemm_mix", "train_step"],
