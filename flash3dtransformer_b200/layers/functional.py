@@ -54,6 +54,34 @@ class CoordEmbedFn(Function):
         return None, (gf.t() @ x.float()).to(ctx.dtypes[0]), gf.sum(0).to(ctx.dtypes[1])
 
 
+# Largest weight (elements) whose gradient goes to the native kernel: above it the output tiles outnumber the SMs, the
+# operands are re-read once per tile column, and the library's split-K GEMM measured faster (N x K = 4096 x 512: 198
+# against 98 us; 2048 x 256 and below: 40-100 us against 48-127 us).
+_WGRAD_MAX_ELEMS = 512 * 1024
+
+
+def _param_grads(g, xb, weight, bias):
+    """(grad_weight, grad_bias) of y = x W^T + b for the bf16 gradient g [M, N] and input xb [M, K]: one native pass
+    over both (fp32 results, fixed summation order) for the shapes it takes, else a library GEMM plus the native
+    column sums."""
+    n, k = g.shape[1], xb.shape[1]
+    if g.dtype == torch.bfloat16 and pshattn.wgrad_supported(n, k) and n * k <= _WGRAD_MAX_ELEMS:
+        gw = torch.empty(n, k, dtype=torch.float32, device=g.device)
+        gb = torch.empty(n, dtype=torch.float32, device=g.device) if bias is not None else None
+        pshattn.linear_wgrad_bf16(g, xb, gw, gb)
+        return gw.to(weight.dtype), (gb.to(bias.dtype) if bias is not None else None)
+    gw = (g.t() @ xb).to(weight.dtype)
+    gb = None
+    if bias is not None:
+        if g.dtype == torch.bfloat16 and n % 8 == 0 and n <= 2048:
+            gb32 = torch.empty(n, dtype=torch.float32, device=g.device)
+            pshattn.colsum_bf16(g, gb32)
+            gb = gb32.to(bias.dtype)
+        else:
+            gb = g.float().sum(0).to(bias.dtype)
+    return gw, gb
+
+
 class GatherRowsFn(Function):
     """out[i] = src[index[i]] (zero rows where index[i] is the padding mark).  `inverse` maps the rows of src to the
     rows of out, so that the backward is the same gather run through it: with (out2in, in2out) it scatters features into
@@ -115,15 +143,7 @@ class LinearFn(Function):
         # gx = g W: the native GEMM computes A B^T, so W^T ([in, out], a small matrix) is materialised
         gx = torch.empty(g.shape[0], wb.shape[1], dtype=torch.bfloat16, device=g.device)
         pshattn.linear_bf16(g, wb.t().contiguous(), None, gx)
-        gw = (g.t() @ xb).to(weight.dtype)
-        gb = None
-        if bias is not None:
-            if g.dtype == torch.bfloat16 and g.shape[1] % 8 == 0 and g.shape[1] <= 2048:
-                gb32 = torch.empty(g.shape[1], dtype=torch.float32, device=g.device)
-                pshattn.colsum_bf16(g, gb32)
-                gb = gb32.to(bias.dtype)
-            else:
-                gb = g.float().sum(0).to(bias.dtype)
+        gw, gb = _param_grads(g, xb, weight, bias)
         return gx, gw, gb, g_res, None, None
 
 
@@ -134,19 +154,9 @@ def _split_backward(xb, weight, bias, wb, g):
     wt = wb.view(s, c, wb.shape[1]).transpose(1, 2).contiguous()
     gx = torch.empty(m, wb.shape[1], dtype=torch.bfloat16, device=g.device)
     pshattn.linear_ksplit_bf16(g, wt, gx)
-    gw = torch.empty(s * c, xb.shape[1], dtype=torch.bfloat16, device=g.device)
-    for i in range(s):
-        torch.mm(g[i].t(), xb, out=gw[i * c:(i + 1) * c])
-    gw = gw.to(weight.dtype)
-    gb = None
-    if bias is not None:
-        if c % 8 == 0 and c <= 2048:
-            gb32 = torch.empty(s, c, dtype=torch.float32, device=g.device)
-            for i in range(s):
-                pshattn.colsum_bf16(g[i], gb32[i])
-            gb = gb32.reshape(-1).to(bias.dtype)
-        else:
-            gb = g.float().sum(1).reshape(-1).to(bias.dtype)
+    parts = [_param_grads(g[i], xb, weight, bias[i * c:(i + 1) * c] if bias is not None else None) for i in range(s)]
+    gw = torch.cat([p[0] for p in parts], dim=0)
+    gb = torch.cat([p[1] for p in parts], dim=0) if bias is not None else None
     return gx, gw, gb, None, None, None
 
 

@@ -315,6 +315,30 @@ def linear_bf16(x, weight, bias, out, residual=None, nsplit=1, epilogue=EPI_NONE
     _cabi.check(st, "linear_bf16")
 
 
+def wgrad_supported(n: int, k: int) -> bool:
+    """Shapes linear_wgrad_bf16 takes: N a multiple of 8, K = 32 or a multiple of 64."""
+    return n % 8 == 0 and (k == 32 or k % 64 == 0)
+
+
+def linear_wgrad_bf16(grad_out, x, grad_weight, grad_bias=None) -> None:
+    """grad_weight fp32 [N, K] = grad_out^T @ x and grad_bias fp32 [N] = grad_out.sum(0) for bf16 grad_out [M, N] and
+    x [M, K]: the parameter gradients of a projection in one pass over both operands, added in a fixed order."""
+    ts, names = [grad_out, x, grad_weight], ["grad_out", "x", "grad_weight"]
+    if grad_bias is not None:
+        ts.append(grad_bias); names.append("grad_bias")
+    dev = _check_tensors(ts, names)
+    _check_dtype([grad_out, x], ["grad_out", "x"], torch.bfloat16)
+    _check_dtype(ts[2:], names[2:], torch.float32)
+    _require(grad_out.dim() == 2 and x.dim() == 2 and grad_out.shape[0] == x.shape[0], "grad_out must be [M, N] and x [M, K]")
+    m, n = grad_out.shape
+    k = x.shape[1]
+    _require(tuple(grad_weight.shape) == (n, k), f"grad_weight must be [{n},{k}]")
+    _require(grad_bias is None or grad_bias.numel() == n, f"grad_bias must have {n} elements")
+    st = _cabi.load().f3d_linear_wgrad_bf16(_ptr(grad_out), _ptr(x), _ptr(grad_weight), _ptr(grad_bias) if grad_bias is not None else None,
+                                            m, n, k, _dev_index(dev), _stream(dev))
+    _cabi.check(st, "linear_wgrad_bf16")
+
+
 def linear_ksplit_bf16(x, weight, out, bias=None, residual=None) -> None:
     """out [M, N] = sum_s x[s] @ weight[s]^T for x bf16 [S, M, K] and weight bf16 [S, N, K]: the input gradient of a
     projection whose output is S separate matrices (Q, K, V), computed from the packed gradient in one GEMM."""

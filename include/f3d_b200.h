@@ -215,6 +215,13 @@ int f3d_colsum_bf16(const void *x, void *out, uint64_t rows, uint32_t C, int dev
 int f3d_coord_embed_bf16(const void *coords, const void *weight, const void *bias, void *out, uint32_t rows, uint32_t C,
                          int device, void *stream);
 
+/* Weight and bias gradient of a projection y = x W^T + b: grad_weight fp32 [N, K] = grad_out^T x and, when grad_bias is
+ * not NULL, grad_bias fp32 [N] = column sums of grad_out, for grad_out bf16 [M, N] and x bf16 [M, K] (both dense).  One
+ * pass over grad_out and x on the tensor cores (neither is transposed in memory), sums over row slabs added in a fixed
+ * order.  N a multiple of 8; K = 32 or a multiple of 64. */
+int f3d_linear_wgrad_bf16(const void *grad_out, const void *x, void *grad_weight, void *grad_bias, int M, int N, int K,
+                          int device, void *stream);
+
 /* Sum of slice products C[M, N] = sum_s A[s] W[s]^T (+ bias) (+ residual): A bf16 [ksplit, M, K], W bf16 [ksplit, N, K],
  * both dense.  One GEMM whose k-blocks walk the slices; it is the input gradient of a projection that wrote its output as
  * separate matrices (the Q, K, V layout of f3d_linear_bf16 with nsplit = 3: grad_x = sum_s grad[s] W_s), without first

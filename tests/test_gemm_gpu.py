@@ -222,3 +222,38 @@ def test_split_projection_gradients(cuda_device):
     assert (w.grad - ref_gw).abs().max().item() <= 2e-2 * ref_gw.abs().max().item() + 1e-2
     ref_gb = flat.sum(0)
     assert (b.grad - ref_gb).abs().max().item() <= 1e-3 * ref_gb.abs().max().item() + 1e-3
+
+
+@pytest.mark.parametrize("m,n,k", [(1000, 32, 32), (4097, 96, 32), (3000, 256, 32), (5000, 64, 64), (2048, 192, 64),
+                                   (1500, 128, 128), (777, 384, 128), (3001, 256, 256), (900, 512, 512), (640, 2048, 512),
+                                   (1200, 64, 1024), (63, 40, 192), (1, 8, 64)])
+def test_linear_wgrad(cuda_device, m, n, k):
+    """grad_W = g^T x and grad_b = colsum(g) against fp32 torch; fp32 accumulation of exact bf16 products, so only the
+    summation order differs: 1e-4 of the largest entry plus 1e-5 * sqrt(M)."""
+    from flash3dtransformer_b200.lib import pshattn
+    gen = torch.Generator(cuda_device).manual_seed(m + n + k)
+    g = torch.randn(m, n, device=cuda_device, generator=gen).bfloat16()
+    x = torch.randn(m, k, device=cuda_device, generator=gen).bfloat16()
+    gw = torch.full((n, k), float("nan"), device=cuda_device)
+    gb = torch.full((n,), float("nan"), device=cuda_device)
+    pshattn.linear_wgrad_bf16(g, x, gw, gb)
+    pshattn.device_status()
+    ref_w = g.float().t() @ x.float()
+    ref_b = g.float().sum(0)
+    tol_w = 1e-4 * ref_w.abs().max().item() + 1e-5 * m ** 0.5
+    assert torch.isfinite(gw).all() and (gw - ref_w).abs().max().item() <= tol_w, (gw - ref_w).abs().max().item()
+    assert (gb - ref_b).abs().max().item() <= 1e-4 * ref_b.abs().max().item() + 1e-5 * m ** 0.5
+    # without the bias gradient, and the same bits on a second run
+    gw2 = torch.empty_like(gw)
+    pshattn.linear_wgrad_bf16(g, x, gw2)
+    assert torch.equal(gw, gw2)
+
+
+def test_linear_wgrad_errors(cuda_device):
+    from flash3dtransformer_b200.lib import pshattn
+    g = torch.zeros(16, 32, device=cuda_device, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError):
+        pshattn.linear_wgrad_bf16(g, torch.zeros(16, 48, device=cuda_device, dtype=torch.bfloat16), torch.zeros(32, 48, device=cuda_device))
+    with pytest.raises(RuntimeError):
+        pshattn.linear_wgrad_bf16(g, torch.zeros(15, 64, device=cuda_device, dtype=torch.bfloat16), torch.zeros(32, 64, device=cuda_device))
+    assert pshattn.wgrad_supported(96, 32) and not pshattn.wgrad_supported(96, 48) and not pshattn.wgrad_supported(20, 64)
