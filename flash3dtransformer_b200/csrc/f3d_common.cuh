@@ -62,8 +62,16 @@ struct DeviceGuard {
   int prev = -1;
   bool changed = false;
   explicit DeviceGuard(int dev) {
+    // A host thread that has made no runtime call yet (an autograd worker whose first operator is one of ours) has no
+    // context bound, and driver entry points such as cuTensorMapEncodeTiled then fail with "invalid context":
+    // cudaSetDevice binds the device's primary context, so it runs once per thread even when the device is unchanged.
+    static thread_local int bound = -1;
     cudaGetDevice(&prev);
-    if (prev != dev) { cudaSetDevice(dev); changed = true; }
+    if (prev != dev || bound != dev) {
+      cudaSetDevice(dev);
+      bound = dev;
+      changed = prev != dev;
+    }
   }
   ~DeviceGuard() { if (changed) cudaSetDevice(prev); }
 };

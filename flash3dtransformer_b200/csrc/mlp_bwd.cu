@@ -37,7 +37,7 @@ __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const __nv_bfloat16 *__
 
 // partial[b][c] = sum over the rows of block b; blocks stride over the rows
 __global__ void __launch_bounds__(256) colsum_partial_kernel(const __nv_bfloat16 *__restrict__ x, float *__restrict__ partial, size_t rows,
-                                                             uint32_t C, uint32_t rows_per_block) {
+                                                             uint32_t C, uint32_t ld, uint32_t rows_per_block) {
   const uint32_t chunks = C / 8;                      // threads of a block: [row slots][chunks]
   const uint32_t ch = threadIdx.x % chunks, slot = threadIdx.x / chunks, slots = blockDim.x / chunks;
   __shared__ float red[256 * 8];
@@ -50,7 +50,7 @@ __global__ void __launch_bounds__(256) colsum_partial_kernel(const __nv_bfloat16
     for (; r + 3 * (size_t)slots < r1; r += 4 * (size_t)slots) {
       uint4 q[4];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) q[k] = __ldg(reinterpret_cast<const uint4 *>(x + (r + (size_t)k * slots) * C) + ch);
+      for (int k = 0; k < 4; ++k) q[k] = __ldg(reinterpret_cast<const uint4 *>(x + (r + (size_t)k * slots) * ld) + ch);
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&q[k]);
@@ -59,7 +59,7 @@ __global__ void __launch_bounds__(256) colsum_partial_kernel(const __nv_bfloat16
       }
     }
     for (; r < r1; r += slots) {
-      const uint4 q = __ldg(reinterpret_cast<const uint4 *>(x + r * C) + ch);
+      const uint4 q = __ldg(reinterpret_cast<const uint4 *>(x + r * ld) + ch);
       const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&q);
 #pragma unroll
       for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h[e]); acc[2 * e] += f.x; acc[2 * e + 1] += f.y; }
@@ -115,7 +115,7 @@ extern "C" int f3d_swiglu_bwd_bf16(const void *pre_act, const void *grad_out, vo
 }
 
 extern "C" int f3d_colsum_bf16(const void *x, void *out, uint64_t rows, uint32_t C, int device, void *stream) {
-  if (C == 0 || C % 8 || C > 2048) return set_error(F3D_ERR_ARG, "colsum: column count %u must be a multiple of 8, at most 2048", C);
+  if (C == 0 || C % 8) return set_error(F3D_ERR_ARG, "colsum: column count %u must be a positive multiple of 8", C);
   if (reinterpret_cast<uintptr_t>(x) % 16) return set_error(F3D_ERR_ARG, "colsum: input pointer must be 16-byte aligned");
   DeviceGuard guard(device);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
@@ -124,13 +124,20 @@ extern "C" int f3d_colsum_bf16(const void *x, void *out, uint64_t rows, uint32_t
   uint32_t rows_per_block = (uint32_t)((rows + blocks - 1) / blocks);
   if (rows_per_block < 64) rows_per_block = 64;
   blocks = (uint32_t)((rows + rows_per_block - 1) / rows_per_block);
-  void *partial = nullptr;
-  F3D_TRY(workspace(device, 4, (size_t)blocks * C * sizeof(float), &partial));
-  // a block is [row slots][chunks of 8 channels]; wide rows use several passes of 256 threads' worth of chunks
-  const uint32_t chunks = C / 8;
-  const uint32_t threads = chunks >= 256 ? chunks : 256 / chunks * chunks;
-  colsum_partial_kernel<<<blocks, threads, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), static_cast<float *>(partial), (size_t)rows, C, rows_per_block);
-  F3D_TRY(check_launch("colsum_bf16"));
-  colsum_reduce_kernel<<<(C + 31) / 32, 256, 0, st>>>(static_cast<const float *>(partial), static_cast<float *>(out), blocks, C);
-  return check_launch("colsum_bf16 (reduce)");
+  // column blocks of at most 2048 (256 threads x 8 channels), one after the other through the same scratch
+  for (uint32_t c0 = 0; c0 < C; c0 += 2048) {
+    const uint32_t cb = C - c0 < 2048 ? C - c0 : 2048;
+    void *partial = nullptr;
+    F3D_TRY(workspace(device, 4, (size_t)blocks * 2048 * sizeof(float), &partial));
+    // a block is [row slots][chunks of 8 channels]
+    const uint32_t chunks = cb / 8;
+    const uint32_t threads = 256 / chunks * chunks;
+    colsum_partial_kernel<<<blocks, threads, 0, st>>>(static_cast<const __nv_bfloat16 *>(x) + c0, static_cast<float *>(partial), (size_t)rows, cb, C,
+                                                      rows_per_block);
+    F3D_TRY(check_launch("colsum_bf16"));
+    colsum_reduce_kernel<<<(cb + 31) / 32, 256, 0, st>>>(static_cast<const float *>(partial), static_cast<float *>(out) + c0, blocks, cb);
+    F3D_TRY(check_launch("colsum_bf16 (reduce)"));
+  }
+  return F3D_OK;
 }
+

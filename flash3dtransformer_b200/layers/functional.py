@@ -73,7 +73,7 @@ def _param_grads(g, xb, weight, bias):
     gw = (g.t() @ xb).to(weight.dtype)
     gb = None
     if bias is not None:
-        if g.dtype == torch.bfloat16 and n % 8 == 0 and n <= 2048:
+        if g.dtype == torch.bfloat16 and n % 8 == 0:
             gb32 = torch.empty(n, dtype=torch.float32, device=g.device)
             pshattn.colsum_bf16(g, gb32)
             gb = gb32.to(bias.dtype)

@@ -206,7 +206,7 @@ int f3d_layernorm_bwd_bf16(const void *x, const void *grad_out, const void *weig
 int f3d_swiglu_bwd_bf16(const void *pre_act, const void *grad_out, void *grad_pre_act, uint64_t rows, uint32_t F, int device,
                         void *stream);
 
-/* Bias gradient: out fp32 [C] = column sums of x bf16 [rows, C], added in a fixed order.  C a multiple of 8, <= 2048. */
+/* Bias gradient: out fp32 [C] = column sums of x bf16 [rows, C], added in a fixed order.  C a multiple of 8. */
 int f3d_colsum_bf16(const void *x, void *out, uint64_t rows, uint32_t C, int device, void *stream);
 
 /* Coordinate embedding out = W x + b: fp16 coordinates [rows, 3], fp32 weight [C, 3] and bias [C], bf16 out [rows, C].

@@ -144,7 +144,7 @@ def test_swiglu_backward(cuda_device, rows, f):
     assert ((out.float() - ref).abs() <= ref.abs() * 2.0 ** -7 + 1e-3).all()
 
 
-@pytest.mark.parametrize("rows,c", [(1, 8), (1000, 96), (70001, 32), (5000, 2048), (63, 512)])
+@pytest.mark.parametrize("rows,c", [(1, 8), (1000, 96), (70001, 32), (5000, 2048), (63, 512), (3000, 4096), (777, 2056)])
 def test_colsum(cuda_device, rows, c):
     from flash3dtransformer_b200.lib import pshattn
     g = torch.Generator(cuda_device).manual_seed(rows + c)
