@@ -166,3 +166,25 @@ def test_input_features_and_input_order(cuda_device):
     with torch.no_grad():
         out2 = full(coords, feat, seps)
     assert not torch.equal(out2, out)
+
+
+def test_batchnorm_pool_wrappers_forward_backward(cuda_device):
+    """The reference's whole-model test wraps pooling and unpooling in BatchNorm1d + GELU
+    (tests/test_psh_hourglass.py:103-106): user-supplied normalisation modules run as given next to the native
+    kernels, forward and backward."""
+    import dataclasses
+    from torch import nn
+    from flash3dtransformer_b200 import configs, layers
+    from flash3dtransformer_b200.lib import pshattn
+    torch.manual_seed(0)
+    specs = configs.hourglass_specs((32, 64), (2, 2))
+    specs = [dataclasses.replace(s, pool_norm=nn.BatchNorm1d, unpool_norm=nn.BatchNorm1d) for s in specs]
+    model = layers.Flash3D(specs, 512, 8, 2).to(cuda_device).train()
+    coords, seps = _batch(cuda_device, [20000, 26000], seed=4)
+    out = model(coords, coords, seps)
+    assert out.dtype == torch.bfloat16 and torch.isfinite(out.float()).all()
+    out.float().square().mean().backward()
+    pshattn.device_status()
+    for n, p in model.named_parameters():
+        assert p.grad is not None and torch.isfinite(p.grad).all(), n
+    assert any(isinstance(m, nn.BatchNorm1d) for m in model.modules())
