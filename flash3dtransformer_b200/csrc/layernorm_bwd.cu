@@ -130,22 +130,24 @@ __global__ void __launch_bounds__(kLnbThreads) layernorm_bwd_kernel(const __nv_b
   }
 }
 
-// dweight[c] / dbias[c] = sum over the per-CTA partial rows.  A block of 32 x 8 threads takes 32 channels: thread
-// (tx, ty) adds rows ty, ty + 8, ... in order, then the eight slices are added in order (fixed summation order).
-__global__ void __launch_bounds__(256) layernorm_bwd_reduce_kernel(const float *__restrict__ partial, float *__restrict__ dweight,
-                                                                   float *__restrict__ dbias, uint32_t blocks, uint32_t C) {
-  __shared__ float red[2][8][32];
+// dweight[c] / dbias[c] = sum over the per-CTA partial rows.  A block of 32 x 32 threads takes 32 channels: thread
+// (tx, ty) adds rows ty, ty + 32, ... in order, then the 32 strands are added in order (fixed summation order; with
+// up to 1184 partial rows, eight strands left every thread a chain of 148 dependent loads and additions).
+constexpr int kLnbStrands = 32;
+__global__ void __launch_bounds__(32 * kLnbStrands) layernorm_bwd_reduce_kernel(const float *__restrict__ partial, float *__restrict__ dweight,
+                                                                                float *__restrict__ dbias, uint32_t blocks, uint32_t C) {
+  __shared__ float red[2][kLnbStrands][32];
   const uint32_t tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const uint32_t c = blockIdx.x * 32 + tx;
   float a = 0.f, b = 0.f;
   if (c < C)
-    for (uint32_t p = ty; p < blocks; p += 8) { a += partial[((size_t)p * 2) * C + c]; b += partial[((size_t)p * 2 + 1) * C + c]; }
+    for (uint32_t p = ty; p < blocks; p += kLnbStrands) { a += partial[((size_t)p * 2) * C + c]; b += partial[((size_t)p * 2 + 1) * C + c]; }
   red[0][ty][tx] = a; red[1][ty][tx] = b;
   __syncthreads();
   if (ty == 0 && c < C) {
     float sa = 0.f, sb = 0.f;
 #pragma unroll
-    for (int q = 0; q < 8; ++q) { sa += red[0][q][tx]; sb += red[1][q][tx]; }
+    for (int q = 0; q < kLnbStrands; ++q) { sa += red[0][q][tx]; sb += red[1][q][tx]; }
     dweight[c] = sa;
     dbias[c] = sb;
   }
@@ -202,6 +204,6 @@ extern "C" int f3d_layernorm_bwd_bf16(const void *x, const void *grad_out, const
     }
   }
   F3D_TRY(check_launch("layernorm_bwd_bf16"));
-  layernorm_bwd_reduce_kernel<<<(C + 31) / 32, 256, 0, st>>>(pp, static_cast<float *>(grad_weight), static_cast<float *>(grad_bias), grid, C);
+  layernorm_bwd_reduce_kernel<<<(C + 31) / 32, 32 * kLnbStrands, 0, st>>>(pp, static_cast<float *>(grad_weight), static_cast<float *>(grad_bias), grid, C);
   return check_launch("layernorm_bwd_bf16 (reduce)");
 }
