@@ -37,11 +37,19 @@ template <> struct Chunk<float> {
   __device__ static void store(float *p, const float (&v)[4]) {
     *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
   }
+  __device__ static void cvt(const uint4 &q, float (&v)[4]) {
+    v[0] = __uint_as_float(q.x); v[1] = __uint_as_float(q.y); v[2] = __uint_as_float(q.z); v[3] = __uint_as_float(q.w);
+  }
 };
 template <> struct Chunk<__nv_bfloat16> {
   static constexpr int N = 8;
   __device__ static void load(const __nv_bfloat16 *p, float (&v)[8]) {
     uint4 q = *reinterpret_cast<const uint4 *>(p);
+    const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&q);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+  }
+  __device__ static void cvt(const uint4 &q, float (&v)[8]) {
     const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&q);
 #pragma unroll
     for (int i = 0; i < 4; ++i) { float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
@@ -57,6 +65,11 @@ template <> struct Chunk<__half> {
   static constexpr int N = 8;
   __device__ static void load(const __half *p, float (&v)[8]) {
     uint4 q = *reinterpret_cast<const uint4 *>(p);
+    const __half2 *h = reinterpret_cast<const __half2 *>(&q);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { float2 f = __half22float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+  }
+  __device__ static void cvt(const uint4 &q, float (&v)[8]) {
     const __half2 *h = reinterpret_cast<const __half2 *>(&q);
 #pragma unroll
     for (int i = 0; i < 4; ++i) { float2 f = __half22float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
@@ -81,36 +94,71 @@ struct GatherArgs {
 template <typename T>
 __global__ void __launch_bounds__(kPoolThreads) pool_reduce_kernel(const T *__restrict__ in, T *__restrict__ out, GatherArgs a) {
   constexpr int N = Chunk<T>::N;
-  uint64_t gid = (uint64_t)blockIdx.x * kPoolThreads + threadIdx.x;
-  uint32_t row = (uint32_t)(gid / a.chunks_per_row), ch = (uint32_t)(gid % a.chunks_per_row);
-  if (row >= a.out_rows) return;
-  float acc[N];
+  // A thread reduces two 16-byte chunks of the output (slots 2 * gid and 2 * gid + 1).  Members are taken two at a
+  // time: the indices and then the 16-byte loads of both chunks are issued before the first value is used, so a thread
+  // has four loads in flight; every chunk still adds its members in slot order.
+  const uint64_t total = (uint64_t)a.out_rows * a.chunks_per_row;
+  const uint64_t g0 = ((uint64_t)blockIdx.x * kPoolThreads + threadIdx.x) * 2;
+  if (g0 >= total) return;
+  uint32_t row[2], ch[2], cnt[2] = {0u, 0u};
+  bool live[2];
+  float acc[2][N];
   const float init = a.op == O_MIN ? INFINITY : (a.op == O_MAX ? -INFINITY : 0.f);
 #pragma unroll
-  for (int i = 0; i < N; ++i) acc[i] = init;
-  uint32_t cnt = 0;
-  if (row < a.ind_rows) {
-    for (uint32_t s = 0; s < a.S; ++s) {
-      uint32_t r = __ldg(a.unpool_ind + (size_t)row * a.S + s);
-      if (r < a.valid_N) {
-        ++cnt;
-        float v[N];
-        Chunk<T>::load(in + (size_t)r * a.C + ch * N, v);
+  for (int k = 0; k < 2; ++k) {
+    const uint64_t g = g0 + k;
+    live[k] = g < total;
+    row[k] = (uint32_t)((live[k] ? g : g0) / a.chunks_per_row);
+    ch[k] = (uint32_t)((live[k] ? g : g0) % a.chunks_per_row);
 #pragma unroll
-        for (int i = 0; i < N; ++i) {
-          if (a.op == O_MIN) acc[i] = fminf(acc[i], v[i]);
-          else if (a.op == O_MAX) acc[i] = fmaxf(acc[i], v[i]);
-          else acc[i] = __fadd_rn(acc[i], v[i]);
+    for (int i = 0; i < N; ++i) acc[k][i] = init;
+  }
+  for (uint32_t s0 = 0; s0 < a.S; s0 += 2) {
+    uint32_t r[2][2];
+    bool ok[2][2];
+    uint4 q[2][2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k)
+#pragma unroll
+      for (int m = 0; m < 2; ++m) {
+        const bool has = live[k] && row[k] < a.ind_rows && s0 + m < a.S;
+        r[k][m] = has ? __ldg(a.unpool_ind + (size_t)row[k] * a.S + s0 + m) : 0xFFFFFFFFu;
+      }
+#pragma unroll
+    for (int k = 0; k < 2; ++k)
+#pragma unroll
+      for (int m = 0; m < 2; ++m) {
+        ok[k][m] = r[k][m] < a.valid_N;
+        q[k][m] = make_uint4(0, 0, 0, 0);
+        if (ok[k][m]) q[k][m] = __ldg(reinterpret_cast<const uint4 *>(in + (size_t)r[k][m] * a.C + ch[k] * N));
+      }
+#pragma unroll
+    for (int k = 0; k < 2; ++k)
+#pragma unroll
+      for (int m = 0; m < 2; ++m) {
+        if (ok[k][m]) {
+          ++cnt[k];
+          float v[N];
+          Chunk<T>::cvt(q[k][m], v);
+#pragma unroll
+          for (int i = 0; i < N; ++i) {
+            if (a.op == O_MIN) acc[k][i] = fminf(acc[k][i], v[i]);
+            else if (a.op == O_MAX) acc[k][i] = fmaxf(acc[k][i], v[i]);
+            else acc[k][i] = __fadd_rn(acc[k][i], v[i]);
+          }
         }
       }
-    }
   }
 #pragma unroll
-  for (int i = 0; i < N; ++i) {
-    if (a.op == O_MEAN && cnt) acc[i] = __fdiv_rn(acc[i], (float)cnt);
-    if (cnt == 0) acc[i] = 0.f;
+  for (int k = 0; k < 2; ++k) {
+    if (!live[k]) continue;
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      if (a.op == O_MEAN && cnt[k]) acc[k][i] = __fdiv_rn(acc[k][i], (float)cnt[k]);
+      if (cnt[k] == 0) acc[k][i] = 0.f;
+    }
+    Chunk<T>::store(out + (size_t)row[k] * a.C + ch[k] * N, acc[k]);
   }
-  Chunk<T>::store(out + (size_t)row * a.C + ch * N, acc);
 }
 
 // ------------------------------------------------------------------------------------------ pooling backward
@@ -272,7 +320,7 @@ extern "C" int f3d_batch_subbuck_reduce(
   GatherArgs a{static_cast<const uint32_t *>(unpool_ind), unpool_rows, reduced_rows, total_N, feat_dim, subbuck_size, red_op,
                feat_dim * (uint32_t)esize(feat_dtype) / 16};
   if (reduced_rows > 0) {
-    F3D_DISPATCH_DT(feat_dtype, pool_reduce_kernel<T><<<blocks_for(reduced_rows, a.chunks_per_row), kPoolThreads, 0, st>>>(
+    F3D_DISPATCH_DT(feat_dtype, pool_reduce_kernel<T><<<(blocks_for(reduced_rows, a.chunks_per_row) + 1) / 2, kPoolThreads, 0, st>>>(
         static_cast<const T *>(scattered_feat), static_cast<T *>(reduced_feat), a));
   }
   F3D_TRY(check_launch("batch_subbuck_reduce"));
