@@ -25,11 +25,11 @@ constexpr uint32_t kPending = 0xFFFFFFFFu; // bucket_offset marker for a point w
 // IEEE fp32 with explicit rounding: no fast-math, no FMA contraction, so numpy float32 reproduces it.
 __device__ __forceinline__ uint32_t vox_axis(float c, float lo, float hi, uint32_t num_vox) {
   float t = __fdiv_rn(__fmul_rn(__fsub_rn(c, lo), (float)num_vox), __fsub_rn(hi, lo));
-  float v = floorf(t);
-  if (!(v >= 0.f)) return 0u;              // negative or NaN (degenerate bbox)
+  // clamp(x, 0, top) = max(0, min(x, top)) (src/common/arithmetic.cuh:26-29) with the device rule of min / max: a NaN
+  // operand is dropped.  On an axis where every point has the same coordinate the quotient is 0/0 = NaN, min(NaN, top)
+  // is top, and the voxel index is num_vox - 1, as in the reference.
   float top = (float)(num_vox - 1u);
-  if (v > top) v = top;
-  return (uint32_t)v;
+  return (uint32_t)fmaxf(0.f, fminf(floorf(t), top));
 }
 
 // x < 1024: bit i moves to bit 3i

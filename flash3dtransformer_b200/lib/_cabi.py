@@ -30,6 +30,7 @@ PROTOTYPES = {
                                               _vp, _vp, _vp, _vp, _vp, _u32, _f32, _u32, _int, _vp]),
     "f3d_batch_psh_scatter_pad_hash_noalloc": (_int, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _u32, _u32,
                                                       _vp, _vp, _vp, _vp, _vp, _u32, _f32, _u32, _int, _vp]),
+    "f3d_batch_bucket_sanitizer_cpu": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32]),
     "f3d_batch_subbuck_reduce": (_int, [_vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                         _vp, _u32, _u32, _u32, _int, _u32, _u32, _int, _vp]),
     "f3d_batch_subbuck_reduce_backward": (_int, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _int, _u32, _u32, _int, _vp]),

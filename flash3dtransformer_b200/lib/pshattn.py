@@ -158,6 +158,44 @@ def batch_psh_scatter(coord, bucket_id, bucket_counter, bucket_offset, batch_sep
                                cumsum_counter, scatter_coord, 0.0, HASH_ZORDER_MOD)
 
 
+# --------------------------------------------------------------------------------------- scoreboard check
+def batch_bucket_sanitizer_cpu(bucket_id, bucket_counter, bucket_offset, offset_check_table, bucket_residual,
+                               batch_sep, offset_maxcnt, batch_size, num_bucket) -> None:
+    """f3d::batch_bucket_sanitizer_cpu (src/psh/bucket_sanitizer_cpu.cpp:92-176; call site tests/test_psh.py:127-129).
+    The scoreboard check of a finished bucketing, on the host: tensors of any device are copied to the CPU (as the
+    reference does, :104-110), every point takes one unit off `bucket_residual[scene, bucket]` and marks
+    `offset_check_table[scene, bucket, offset]`; every slot below a bucket's count must end up marked exactly once.
+    `bucket_residual` and `offset_check_table` are updated in place on their own device (:172-173).  A violation
+    raises RuntimeError naming the first offending point or slot."""
+    tensors = [bucket_id, bucket_counter, bucket_offset, offset_check_table, bucket_residual, batch_sep, offset_maxcnt]
+    names = ["bucket_id", "bucket_counter", "bucket_offset", "offset_check_table", "bucket_residual", "batch_sep",
+             "offset_maxcnt"]
+    for t, n in zip(tensors, names):
+        _require(isinstance(t, torch.Tensor), f"{n} must be a torch.Tensor")
+    _check_dtype([bucket_id], ["bucket_id"], torch.uint16)
+    _check_dtype([bucket_counter, bucket_offset, bucket_residual, batch_sep, offset_maxcnt],
+                 ["bucket_counter", "bucket_offset", "bucket_residual", "batch_sep", "offset_maxcnt"], torch.uint32)
+    _check_dtype([offset_check_table], ["offset_check_table"], torch.int8)
+    batch_size, num_bucket = int(batch_size), int(num_bucket)
+    _require(offset_check_table.dim() == 3 and offset_check_table.shape[0] == batch_size
+             and offset_check_table.shape[1] == num_bucket,
+             f"offset_check_table must be [{batch_size},{num_bucket},max_count], got {tuple(offset_check_table.shape)}")
+    _require(bucket_counter.numel() == batch_size * num_bucket and bucket_residual.numel() == batch_size * num_bucket,
+             f"bucket_counter / bucket_residual must be [{batch_size},{num_bucket}]")
+    _require(batch_sep.numel() >= batch_size and offset_maxcnt.numel() >= batch_size,
+             "batch_sep / offset_maxcnt are shorter than batch_size")
+    _require(bucket_offset.numel() >= bucket_id.numel(), "bucket_offset is shorter than bucket_id")
+    host = [t.detach().cpu().contiguous() for t in tensors]
+    # the two in/out buffers are private host copies even for CPU inputs, so a failed check changes nothing
+    table, residual = host[3].clone(), host[4].clone()
+    st = _cabi.load().f3d_batch_bucket_sanitizer_cpu(
+        _ptr(host[0]), _ptr(host[1]), _ptr(host[2]), _ptr(table), _ptr(residual), _ptr(host[5]), _ptr(host[6]),
+        bucket_id.numel(), batch_size, num_bucket, offset_check_table.shape[2])
+    _cabi.check(st, "batch_bucket_sanitizer_cpu")
+    bucket_residual.copy_(residual.view(bucket_residual.shape))
+    offset_check_table.copy_(table)
+
+
 # ------------------------------------------------------------------------------------- pooling / unpooling
 def _feat_code(t: torch.Tensor, name: str) -> int:
     _require(t.dtype in _FEAT_DTYPES, f"Tensor {name} has dtype {t.dtype}; bfloat16, float16 and float32 are supported")

@@ -61,7 +61,12 @@ int f3d_release_workspaces(void);
  *   bucket_id      u16  [total_N]          out
  *   bucket_counter u32  [batch,num_bucket] out (final per-scene bucket sizes)
  *   bucket_offset  u32  [total_N]          out
- *   batch_sep      u32  [batch]            in  (inclusive end row of each scene)
+ *   batch_sep      u32  [batch]            in  (exclusive end row of each scene = cumulative point count, i.e. the
+ *                                               inclusive scan of the scene sizes; scene s covers rows
+ *                                               [batch_sep[s-1], batch_sep[s]))
+ *   instance_max_N                         must be >= the largest scene: it sizes the grid, and points of a scene
+ *                                          beyond it would keep stale bucket ids and offsets (the reference sizes
+ *                                          its grid the same way, src/psh/batch_psh_bucket_dispatcher.cu:258-262)
  *   bbox_min/max   fp16 [3]                in
  *   probe_offsets  i16  [128,3]            in
  *   cumsum_counter u32  [batch,num_bucket] out (inclusive cumsum of bucket_counter)
@@ -91,6 +96,26 @@ int f3d_batch_psh_scatter_pad_hash_noalloc(
     uint32_t bucket_size, uint32_t num_vox, const void *bbox_min, const void *bbox_max, const void *probe_offsets,
     void *cumsum_counter, void *scatter_coord, uint32_t pad_to_N, float pad_num, uint32_t hash_type,
     int device, void *stream);
+
+/* ---- scoreboard check of a finished bucketing (host code, no kernel) ----
+ * replaces f3d::batch_bucket_sanitizer_cpu (src/psh/bucket_sanitizer_cpu.cpp:92-176; binding src/f3d_frontend.cu:133;
+ * call site tests/test_psh.py:127-129).  Every pointer is a HOST pointer (the reference moves each tensor to the CPU
+ * before it reads it, :104-110):
+ *   bucket_id          u16 [total_N]                          in
+ *   bucket_counter     u32 [batch,num_bucket]                 in
+ *   bucket_offset      u32 [total_N]                          in
+ *   offset_check_table i8  [batch,num_bucket,table_slots]     in/out: += 1 at every point's (scene, bucket, offset)
+ *   bucket_residual    u32 [batch,num_bucket]                 in/out: -= 1 per point of the bucket (a copy of
+ *                                                             bucket_counter ends at zero)
+ *   batch_sep          u32 [batch]                            in
+ *   offset_maxcnt      u32 [batch]                            in  (largest bucket count of each scene)
+ * Returns F3D_STATUS_BAD_ARGUMENT, with the position in f3d_last_error(), for a bucket id >= num_bucket, an offset >=
+ * offset_maxcnt of its scene, or a slot below a bucket's count that was not marked exactly once (the reference throws
+ * std::runtime_error with the same text). */
+int f3d_batch_bucket_sanitizer_cpu(
+    const void *bucket_id, const void *bucket_counter, const void *bucket_offset, void *offset_check_table,
+    void *bucket_residual, const void *batch_sep, const void *offset_maxcnt, uint32_t total_N, uint32_t batch_size,
+    uint32_t num_bucket, uint32_t table_slots);
 
 /* ---- sub-bucket construction + feature pooling ----
  * replaces f3d::batch_subbuck_reduce (src/psh/batch_subbuck_pooling_dispatcher.cu:35-144; binding
@@ -238,7 +263,7 @@ int f3d_collate_points_f32(const void *records, void *coords, void *extra, uint6
 
 /* Scatter index of the bucket order (the part of batch_psh_cumsum_scatter_feat_index_postpad_ker the reference wrote,
  * src/psh/batch_psh_bucket.cuh:617-753, plus its inverse): from the outputs of f3d_batch_psh_scatter - bucket_id u16 [N],
- * bucket_offset u32 [N], cumsum_counter u32 [B, num_bucket] (inclusive) and batch_sep u32 [B] (inclusive scene ends) -
+ * bucket_offset u32 [N], cumsum_counter u32 [B, num_bucket] (inclusive) and batch_sep u32 [B] (cumulative point counts: exclusive scene ends) -
  * out2in u32 [pad_to_N]: out2in[row in bucket order] = input row, rows [total_N, pad_to_N) = total_N + 3 (the
  * reference's padding mark, batch_psh_bucket.cuh:667); in2out u32 [total_N] (may be NULL): in2out[input row] = row in
  * bucket order. */

@@ -71,15 +71,15 @@ def psh_params(sizes, bucket_size: int, num_vox: int = 0xFFFF):
 # ------------------------------------------------------------------------------------------------- arithmetic
 def vox_coords(coord_f16: np.ndarray, bbox_min_f16, bbox_max_f16, num_vox: int) -> np.ndarray:
     """src/psh/hash_fns.cuh:23-33 in IEEE fp32: floor((c - min) * num_vox / (max - min)) clamped to
-    [0, num_vox-1]; a NaN (degenerate bbox) maps to 0."""
+    [0, num_vox-1] by max(0, min(x, num_vox-1)) (src/common/arithmetic.cuh:26-29).  Device min / max drop a NaN
+    operand, so the 0/0 of an axis on which every point has the same coordinate becomes num_vox-1 (np.fmin / np.fmax
+    have the same rule; oracle/_ref holds the reference's own lines compiled for the host, which agree)."""
     c = coord_f16.astype(F32)
     lo = np.asarray(bbox_min_f16, dtype=np.float16).astype(F32)
     hi = np.asarray(bbox_max_f16, dtype=np.float16).astype(F32)
     with np.errstate(divide="ignore", invalid="ignore"):
         t = ((c - lo[None, :]) * F32(num_vox)) / (hi - lo)[None, :]
-        v = np.floor(t)
-    ok = v >= 0
-    v = np.where(ok, np.minimum(v, F32(num_vox - 1)), F32(0))
+        v = np.fmax(F32(0), np.fmin(np.floor(t), F32(num_vox - 1)))
     return v.astype(np.uint32)
 
 

@@ -13,7 +13,12 @@ What is captured
   host_plan.json    round_next_two_power, cdiv, round_next_multiply (psh/arithmatic.py), calc_red_sep_sizes
                     (psh/subbuck.py:40-53), sep2sizes / collate (psh/batching.py), the probe-offset set
                     (psh/bucket.py:19-40, order-free because the reference shuffles it)
+  call_sites.json   every call `pshattn.<operator>(...)` in the reference's Python package and tests (file, line, number
+                    of positional arguments, keyword names), read from the syntax tree: the argument lists the drop-in
+                    operator module has to accept
 """
+import ast
+import glob
 import importlib
 import json
 import os
@@ -130,6 +135,34 @@ def main():
     flat, seps = batching.collate_coords_flat_sep(coords, coord_dtype=torch.float16, sep_dtype=torch.int32)
     plan["collate"] = {"flat": flat.float().tolist(), "seps": seps.tolist()}
     json.dump(plan, open(os.path.join(HERE, "host_plan.json"), "w"))
+
+    # ---- operator call sites of the reference's host code and tests
+    sites = []
+    for path in sorted(glob.glob(os.path.join(REF, "flash3dxfmr", "**", "*.py"), recursive=True)
+                       + glob.glob(os.path.join(REF, "tests", "*.py"))):
+        tree = ast.parse(open(path).read())
+        for node in ast.walk(tree):
+            if not (isinstance(node, ast.Call) and isinstance(node.func, ast.Attribute)):
+                continue
+            chain, cur = [node.func.attr], node.func.value
+            while isinstance(cur, ast.Attribute):
+                chain.append(cur.attr)
+                cur = cur.value
+            if isinstance(cur, ast.Call):          # pshattn.DeviceManagerSingleton.instance().method(...)
+                inner = cur.func
+                if isinstance(inner, ast.Attribute) and inner.attr == "instance":
+                    chain.append("instance()")
+                    cur = inner.value
+                    while isinstance(cur, ast.Attribute):
+                        chain.append(cur.attr)
+                        cur = cur.value
+            if not (isinstance(cur, ast.Name) and cur.id == "pshattn"):
+                continue
+            if any(isinstance(a, ast.Starred) for a in node.args):
+                continue
+            sites.append({"file": os.path.relpath(path, REF), "line": node.lineno, "name": ".".join(reversed(chain)),
+                          "nargs": len(node.args), "keywords": [k.arg for k in node.keywords]})
+    json.dump(sites, open(os.path.join(HERE, "call_sites.json"), "w"), indent=0)
     print("golden fixtures written to", HERE)
 
 

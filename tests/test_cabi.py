@@ -36,7 +36,7 @@ def test_operator_module_has_the_reference_surface():
     from flash3dtransformer_b200.lib import pshattn
     for name in ["DeviceManagerSingleton", "batch_psh_scatter", "batch_psh_scatter_pad", "batch_psh_scatter_pad_hash",
                  "additive_unpool_fwd", "additive_unpool_bwd", "batch_subbuck_reduce", "batch_subbuck_reduce_backward",
-                 "gemm_sm_bf16", "buck_swin_fwd"]:
+                 "gemm_sm_bf16", "buck_swin_fwd", "buck_swin_bwd", "batch_bucket_sanitizer_cpu"]:
         assert hasattr(pshattn, name), name
     mgr = pshattn.DeviceManagerSingleton.instance()
     assert mgr is pshattn.DeviceManagerSingleton.instance()

@@ -242,3 +242,48 @@ def test_gather_rows_argument_errors(cuda_device):
     with pytest.raises(RuntimeError):
         pshattn.gather_rows(ok, idx, torch.empty(5, 4, dtype=torch.bfloat16, device=cuda_device))
     pshattn.gather_rows(ok, idx[:0], torch.empty(0, 4, dtype=torch.bfloat16, device=cuda_device))   # empty: no launch
+
+
+@pytest.mark.parametrize("hash_type", [1, 2, 3, 4])
+def test_kernel_output_against_the_reference_compiled_for_the_host(cuda_device, hash_type):
+    """The kernels' bucketing goes through the reference's own scoreboard check (src/psh/bucket_sanitizer_cpu.cpp,
+    compiled into oracle/_ref by oracle/ref_build.py), and every point that was not rebalanced carries the bucket id the
+    reference's own hash lines (src/psh/hash_fns.cuh, same build) give it."""
+    from oracle import ref_build
+    import os
+    san = ref_build.load_sanitizer()
+    if san is None or not os.path.exists(ref_build.HASH_LIB):
+        pytest.skip("oracle/_ref has not been built")
+    sizes = [30000, 17001, 25013]
+    coords32, seps = synthetic.batch(synthetic.lidar_scan, sizes, seed=6)
+    c16 = coords32.astype(np.float16)
+    nb, div, out = _gpu_scatter(cuda_device, c16, seps, 256, hash_type, c16.shape[0])
+    t = lambda a, dt: torch.from_numpy(np.ascontiguousarray(a)).view(dt)
+    cnt = t(out["bucket_cntr"], torch.uint32)
+    maxcnt = torch.max(cnt.to(torch.int32), dim=-1)[0].to(torch.uint32)
+    table = torch.zeros((len(sizes), nb, int(torch.max(cnt.to(torch.int32)))), dtype=torch.int8)
+    res = cnt.clone()
+    san.batch_bucket_sanitizer_cpu(t(out["bucket_id"], torch.uint16), cnt, t(out["bucket_offs"], torch.uint32), table, res,
+                                   t(seps.astype(np.uint32), torch.uint32), maxcnt, len(sizes), nb)
+    assert int(res.to(torch.int64).sum()) == 0
+    _, h = ref_build.RefHash().vox_hash(c16, c16.min(0), c16.max(0), 0xFFFF, div, nb)
+    first = h[hash_type - 1]
+    kept = out["bucket_id"] == first
+    # points leave their first bucket only when it overflowed (src/psh/batch_psh_bucket.cuh:157-246)
+    assert kept.mean() > 0.5
+    start = 0
+    for s, end in enumerate(seps):
+        ids, f = out["bucket_id"][start:end], first[start:end]
+        full = np.bincount(f, minlength=nb) > 256
+        assert np.all(full[f[ids != f]] | (f[ids != f] == 0))
+        start = end
+
+
+def test_flat_axis_bit_exact(cuda_device):
+    # every point at the same height: the voxel quotient of that axis is 0/0 (the reference's clamp keeps the top voxel)
+    coords32, seps = synthetic.batch(synthetic.lidar_scan, [9000, 7000], seed=2)
+    coords32[:, 2] = -1.5
+    c16 = coords32.astype(np.float16)
+    for hash_type in (1, 2):
+        nb, div, out = _gpu_scatter(cuda_device, c16, seps, 256, hash_type, c16.shape[0])
+        _compare(out, _oracle(c16, seps, nb, div, 256, hash_type, c16.shape[0]))

@@ -39,7 +39,9 @@ def test_vox_clamp_and_degenerate_bbox():
     assert v.min() == 0 and v.max() == 0xFFFE and np.all(v[1] == 32767)
     flat = np.array([[1, 2, 3], [1, 5, 3]], dtype=np.float16)
     v = po.vox_coords(flat, flat.min(0), flat.max(0), 0xFFFF)
-    assert np.all(v[:, 0] == 0) and np.all(v[:, 2] == 0) and v[1, 1] == 0xFFFE
+    # a flat axis divides 0 by 0; the device's min / max drop the NaN, which leaves the top voxel (the reference's
+    # own clamp compiled for the host gives the same: tests/test_ref_pins.py)
+    assert np.all(v[:, 0] == 0xFFFE) and np.all(v[:, 2] == 0xFFFE) and v[0, 1] == 0 and v[1, 1] == 0xFFFE
 
 
 def _run(coords32, seps, bucket_size, hash_type, pad_align=None):
