@@ -12,8 +12,12 @@ scenes (weak scaling, scenes sharded along batch_sep); the only collective in th
 all-reduce that keeps bucket ids independent of the sharding.
 
 Rank 0 prints one JSON line: whole-job points/s with inputs resident in HBM (`value`), the same metric through the
-public API from pinned host buffers (`e2e`), the roofline position of the dominant kernel family (`roofline`), and
-the CPU restatement timed on the host cores (`cpu_baseline`).
+public API from pinned host buffers to a pinned host copy of the output features (`e2e`), the roofline position of the
+dominant kernel family (`roofline`), the CPU restatement timed on the host cores (`cpu_baseline`) and, under `extras`,
+short runs of the other configurations after the headline measurement: `strong` (the 16-scan batch sharded over the N
+ranks, output rows gathered), `train_step` (forward + backward + overlapped gradient all-reduce + SGD on this rank's
+share of 64 scans of 200,000 points) and, on one GPU, `attn_layer` (one attention layer forward + backward on 8 scans)
+and `psh_pool` (PSH + 3 poolings + 3 unpoolings on 8 scenes of 1,000,000 points).  `--no-extras` skips them.
 """
 from __future__ import annotations
 
@@ -38,6 +42,7 @@ POINTS_PER_SCENE = 120_000
 CHANNELS = (32, 64, 128, 256, 512)
 DEPTHS = (2, 2, 2, 6, 2)
 BUCKET, SCOPE, HASH_OP = 512, 8, 2
+ATTN_FWD_TRAFFIC_PER_OPERAND_BYTE = 0.9245     # dram bytes / operand bytes of the attention forward in its profiler capture
 
 
 # ----------------------------------------------------------------------------------------------------- helpers
@@ -212,17 +217,29 @@ def cpu_backbone_points_per_s(points: int, steps: int, warmup: int = 0):
     return points / dt, dt, torch.get_num_threads()
 
 
+def headline_config(args, world: int):
+    return {"workload": f"flash3d_backbone_fwd_5stage_{args.scenes}x{args.points // 1000}k_per_gpu",
+            "scenes_per_gpu": args.scenes, "points_per_scene": args.points, "channels": list(CHANNELS),
+            "depths": list(DEPTHS), "bucket_size": BUCKET, "scope_size": SCOPE, "hash_op": HASH_OP,
+            "parallelism": f"scene-sharded x{world}",
+            "l2": "activations per layer (>= 124 MB) exceed the 126 MB L2 across a step; no explicit flush"}
+
+
 def run_reference(args, rank: int):
+    """The CPU arm: the same model and metric on the host cores, each step one scan of `--ref-points` points (a bounded
+    sample of the workload: points/s of this path does not depend on how many scans a step holds, scenes are
+    independent).  Loads no part of the CUDA library."""
     if rank != 0:
         return
     pts = args.ref_points
-    value, dt, cores = cpu_backbone_points_per_s(pts, args.steps, min(args.warmup, 1))
-    sample = f"1 scan of {pts} points per step, full backbone forward, fp32 torch/numpy CPU restatement"
+    value, dt, cores = cpu_backbone_points_per_s(pts, args.steps, args.warmup)
+    sample = (f"each step = 1 scan of {pts} points of the workload's distribution through the full 5-stage backbone forward, "
+              f"fp32 torch/numpy CPU restatement (oracle/backbone_oracle.py), {cores} threads")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "points/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "flash3d_backbone_fwd_5stage_16x120k (CPU arm: bounded sample)", "sample": sample},
+        "config": headline_config(args, args.gpus),
         "cpu_baseline": {"value": value, "unit": "points/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "points/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "the reference has no CPU implementation of this path and cannot be built here (empty ThunderKittens "
@@ -252,8 +269,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     from flash3dtransformer_b200 import parallel
 
     def step(c, s):
-        # bounding box + mean scene size over all ranks' scenes (three tiny all-reduces when world > 1)
-        bbox, mean_n = parallel.global_psh_stats(c, s)
+        # bounding box over all ranks' scenes (one 6-value all-reduce when world > 1); the global scene and point counts
+        # are known to every rank, so the step has no host synchronisation
+        bbox, mean_n = parallel.global_psh_stats(c, s, total_scenes=args.scenes * world, total_points=n_points * world)
         with torch.no_grad():
             return model(c, None, s, bbox=bbox, mean_n=mean_n, scene_base=rank * args.scenes)
 
@@ -291,21 +309,46 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     ms_per_step = ms.item() / args.steps
     pshattn.device_status()
 
-    # ---- end to end: pinned host buffers in, scalar result out, every step
+    # ---- end to end: pinned host buffers in, the step's output features back in pinned host memory, every step.
+    # The copy-back runs on its own stream into one of two host buffers, so step i+1 computes while step i's features
+    # leave the device; the timed region ends when the last copy has landed.
+    host_out = [torch.empty(out.shape, dtype=out.dtype).pin_memory() for _ in range(2)]
+    copy_stream = torch.cuda.Stream(dev)
+    done = [None, None]
+    main_stream = torch.cuda.current_stream(dev)
     barrier()
     torch.cuda.synchronize()
     t0 = time.perf_counter()
-    checksum = 0.0
-    for _ in range(args.steps):
+    for i in range(args.steps):
         c = host_coords.to(dev, non_blocking=True)
-        s = host_seps.to(dev, non_blocking=True)
+        # the loader's host copy of the separators travels with the device copy (psh.scan_io does the same), so the
+        # layers plan their buffers without reading anything back
+        s = batching.attach_host_seps(host_seps.to(dev, non_blocking=True), host_seps)
         o = step(c, s)
-        checksum = float(o.float().mean().item())        # device -> host read of the step's result
+        if done[i % 2] is not None:
+            done[i % 2].synchronize()                    # the host buffer of two steps ago has been filled
+        copy_stream.wait_stream(main_stream)
+        with torch.cuda.stream(copy_stream):
+            host_out[i % 2].copy_(o, non_blocking=True)
+            o.record_stream(copy_stream)
+            done[i % 2] = torch.cuda.Event()
+            done[i % 2].record(copy_stream)
     torch.cuda.synchronize()
     e2e_s = torch.tensor([time.perf_counter() - t0], device=dev)
     if world > 1:
         dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
     e2e_per_step = e2e_s.item() / args.steps
+    d2h_bytes = int(out.numel() * out.element_size())
+    out_cpu = out.cpu()
+    last = host_out[(args.steps - 1) % 2]
+    checksum = float(last[:n_points].float().mean())      # read on the host, outside the timed region
+    if not torch.equal(last, out_cpu):
+        raise RuntimeError("the features copied back in the end-to-end loop differ from the device-resident run")
+    extras = None
+    if not args.no_extras:
+        del out, o, host_out, last, out_cpu, model, coords
+        torch.cuda.empty_cache()
+        extras = run_extras(args, rank, world, local_rank)
 
     if rank != 0:
         return
@@ -320,14 +363,16 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         traffic = None
         if dominant == "attention_fwd":
             achieved, peak, unit, bound = f["flops"] / sec / 1e12, peaks["tflops"], "TFLOP/s", "tensor"
-            # ncu capture of this kernel (profiles/attn_fwd_d32_w4096_8x120k.md): dram read + write equal the
-            # algorithmic operand bytes (236.2 MB measured against 255.5 MB algorithmic on the captured launch), so
-            # the per-launch traffic of a full-size launch is its algorithmic bytes scaled by that ratio
-            traffic = 0.9245 * f["bytes"] / f["launches"]
+            # DRAM read + write bytes of this kernel from a profiler capture of a smaller launch of the same kernel
+            # (2 scans instead of 16: 236.2 MB measured against 255.5 MB of operands), scaled to this launch by its
+            # operand bytes; traffic grows in proportion to the tokens because every CTA reads its own Q / K / V once
+            traffic = ATTN_FWD_TRAFFIC_PER_OPERAND_BYTE * f["bytes"] / f["launches"]
         else:
             achieved, peak, unit, bound = f["bytes"] / sec / 1e9, peaks["hbm_gbs"], "GB/s", "hbm"
         roofline = {"kernel": dominant, "bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
-                    "frac": achieved / peak, "traffic": traffic, "peak_source": peaks["source"],
+                    "frac": achieved / peak, "traffic": traffic,
+                    "traffic_source": "profiler capture of a smaller launch, scaled by operand bytes" if traffic else None,
+                    "peak_source": peaks["source"],
                     "launches": f["launches"], "avg_launch_ms": f["ms"] / f["launches"],
                     "share_of_kernel_time": f["ms"] / total_fam_ms}
     kernels = {k: {"ms_per_step": v["ms"] / args.steps, "share": v["ms"] / total_fam_ms,
@@ -345,20 +390,107 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "metric": METRIC, "value": total_points / (ms_per_step * 1e-3), "unit": "points/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"flash3d_backbone_fwd_5stage_{args.scenes}x{args.points // 1000}k_per_gpu",
-                   "scenes_per_gpu": args.scenes, "points_per_scene": args.points, "channels": list(CHANNELS),
-                   "depths": list(DEPTHS), "bucket_size": BUCKET, "scope_size": SCOPE, "hash_op": HASH_OP,
-                   "parallelism": f"scene-sharded x{world}",
-                   "l2": "activations per layer (>= 124 MB) exceed the 126 MB L2 across a step; no explicit flush"},
+        "config": headline_config(args, world),
         "e2e": {"value": total_points / e2e_per_step, "unit": "points/s", "h2d_bytes_per_step": int(c16.nbytes + seps.nbytes),
-                "d2h_bytes_per_step": 4, "ms_per_step": e2e_per_step * 1e3, "checksum": checksum},
+                "d2h_bytes_per_step": d2h_bytes, "ms_per_step": e2e_per_step * 1e3, "checksum": checksum,
+                "result": "output features [rows, 32] bf16 copied to pinned host memory every step (copy overlapped with the next step)"},
         "gpu_launches": int(launches),
         "clocks": clocks,
         "roofline": roofline,
         "kernels": kernels,
         "cpu_baseline": cpu,
+        "extras": extras,
     }
     print(json.dumps(line), flush=True)
+
+
+def run_extras(args, rank: int, world: int, local_rank: int):
+    """Short runs of the other configurations, after the headline's timed regions; every rank takes part in the
+    multi-GPU ones, rank 0 returns the results."""
+    import copy
+    import torch.distributed as dist
+    res = {}
+    ex = copy.copy(args)
+    ex.steps, ex.warmup = 3, 3
+    t0 = time.perf_counter()
+    res["strong"] = strong_scaling_measure(ex, rank, world, local_rank)
+    torch.cuda.empty_cache()
+    tr = copy.copy(args)
+    tr.steps, tr.warmup = 3, 1
+    tr.scenes, tr.points = max(1, 64 // world), 200_000
+    tr.micro_scenes = min(8, tr.scenes)
+    res["train_step"] = train_step_measure(tr, rank, world, local_rank)
+    torch.cuda.empty_cache()
+    if world == 1:
+        al = copy.copy(args)
+        al.steps, al.warmup = 5, 3
+        res["attn_layer"] = attn_layer_measure(al)
+        torch.cuda.empty_cache()
+        pp = copy.copy(args)
+        pp.steps, pp.warmup, pp.points = 5, 3, POINTS_PER_SCENE
+        res["psh_pool"] = psh_pool_measure(pp)
+        torch.cuda.empty_cache()
+    if world > 1:
+        dist.barrier()
+    res["seconds"] = time.perf_counter() - t0
+    return res if rank == 0 else None
+
+
+def strong_scaling_measure(args, rank: int, world: int, local_rank: int):
+    """The 16 x 120k-point batch of the headline as ONE global batch: sharded by scene over the ranks
+    (parallel.shard_batch), forward on every rank's shard, output rows of all ranks gathered (parallel.gather_rows).
+    Fixed total work: strong scaling.  Reports ms/step and the gather's share."""
+    import torch.distributed as dist
+    from flash3dtransformer_b200 import parallel
+    from flash3dtransformer_b200.psh import batching
+    dev = torch.device(f"cuda:{local_rank}")
+    model = build_model(dev)
+    c16, seps = make_batch(0, SCENES_PER_GPU, POINTS_PER_SCENE)          # the same global batch on every rank
+    coords_all = torch.from_numpy(c16)
+    seps_all = torch.from_numpy(seps)
+    local, lseps, (r0, r1), scene0 = parallel.shard_batch(coords_all, seps_all, rank, world)
+    local = local.to(dev)
+    lseps_dev = batching.attach_host_seps(lseps.to(dev), lseps)
+    total_points = int(c16.shape[0])
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+
+    def step(timed):
+        bbox, mean_n = parallel.global_psh_stats(local, lseps_dev, total_scenes=SCENES_PER_GPU, total_points=total_points)
+        with torch.no_grad():
+            o = model(local, None, lseps_dev, bbox=bbox, mean_n=mean_n, scene_base=scene0)
+        if timed:
+            ev[2].record()
+        g = parallel.gather_rows(o)
+        if timed:
+            ev[3].record()
+        return g
+
+    for _ in range(args.warmup):
+        g = step(False)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    gather_ms = 0.0
+    ev[0].record()
+    for _ in range(args.steps):
+        g = step(True)
+        torch.cuda.synchronize()
+        gather_ms += ev[2].elapsed_time(ev[3])
+    ev[1].record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms = torch.tensor([ev[0].elapsed_time(ev[1]), gather_ms], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_per_step = ms[0].item() / args.steps
+    return {"metric": METRIC, "value": total_points / (ms_per_step * 1e-3), "unit": "points/s", "n_gpus": world,
+            "scaling": "strong", "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "gather_ms_per_step": ms[1].item() / args.steps, "gathered_rows": int(g.shape[0]),
+            "gathered_bytes": int(g.numel() * g.element_size()),
+            "config": {"workload": f"flash3d_backbone_fwd_5stage_{SCENES_PER_GPU}x{POINTS_PER_SCENE // 1000}k_global_batch",
+                       "parallelism": f"scene-sharded x{world}, outputs all-gathered"}}
 
 
 # ------------------------------------------------------------------------------- secondary workloads (1 GPU)
@@ -376,6 +508,10 @@ def _time_ms(fn, steps, warmup):
 
 
 def run_attn_layer(args):
+    print(json.dumps(attn_layer_measure(args)), flush=True)
+
+
+def attn_layer_measure(args):
     """One bucketed-attention layer forward + backward on 8 LiDAR-like scans of 120,000 points: dim 256, 8 heads x
     head_dim 32, bf16, bucket 512 (scope of one bucket).  Reports tokens/s and the attention kernels' TFLOP/s."""
     from flash3dtransformer_b200.lib import pshattn
@@ -431,7 +567,7 @@ def run_attn_layer(args):
                           "frac_of_peak": 2.5 * flops_f / (t_b * 1e-3) / 1e12 / peaks["tflops"]},
         "peak_tflops": peaks["tflops"], "peak_source": peaks["source"],
     }
-    print(json.dumps(line), flush=True)
+    return line
 
 
 def run_gemm_mix(args):
@@ -472,8 +608,16 @@ def run_gemm_mix(args):
 
 
 def run_train_step(args, rank: int, world: int, local_rank: int):
+    line = train_step_measure(args, rank, world, local_rank)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+
+
+def train_step_measure(args, rank: int, world: int, local_rank: int):
     """Backbone forward + backward + gradient all-reduce + SGD step (the backward configuration): `--scenes` scans of
-    `--points` points per GPU, scene-sharded; NCCL carries only the PSH statistics and the gradient all-reduce."""
+    `--points` points per GPU, scene-sharded; NCCL carries only the PSH bounding box and the gradient all-reduce, which
+    is issued bucket by bucket from gradient hooks while the backward pass of the last micro-batch is still running.
+    `grad_allreduce_exposed_ms_per_step` is the time between the end of that backward pass and the last bucket."""
     import torch.distributed as dist
     from flash3dtransformer_b200 import parallel
     from flash3dtransformer_b200.lib import _cabi, pshattn
@@ -483,6 +627,7 @@ def run_train_step(args, rank: int, world: int, local_rank: int):
     torch.cuda.set_device(dev)
     model = build_model(dev).train()
     opt = torch.optim.SGD(model.parameters(), lr=1e-3)
+    reducer = parallel.GradientBucketReducer(model.parameters())
     c16, seps = make_batch(rank, args.scenes, args.points)
     coords = torch.from_numpy(c16).to(dev)
     seps_dev = torch.from_numpy(seps).to(dev)
@@ -503,20 +648,24 @@ def run_train_step(args, rank: int, world: int, local_rank: int):
     t_ar = [0.0]
 
     def step(timed: bool):
-        opt.zero_grad(set_to_none=True)
-        bbox, mean_n = parallel.global_psh_stats(coords, seps_dev)
+        reducer.zero()
+        bbox, mean_n = parallel.global_psh_stats(coords, seps_dev, total_scenes=args.scenes * world,
+                                                 total_points=args.scenes * args.points * world)
         loss = None
-        for c, sp, base in chunks:
+        for i, (c, sp, base) in enumerate(chunks):
             out = model(c, None, sp, bbox=bbox, mean_n=mean_n, scene_base=base)
             part = out.float().square().mean() * (c.shape[0] / total_rows)
-            part.backward()
+            if i == len(chunks) - 1:
+                with reducer.reducing():          # buckets leave as soon as their last gradient exists
+                    part.backward()
+            else:
+                part.backward()
             loss = part.detach() if loss is None else loss + part.detach()
-        if world > 1:
-            if timed:
-                ev[2].record()
-            parallel.allreduce_gradients(model.parameters())
-            if timed:
-                ev[3].record()
+        if timed:
+            ev[2].record()
+        reducer.finish()
+        if timed:
+            ev[3].record()
         opt.step()
         return loss
 
@@ -531,9 +680,8 @@ def run_train_step(args, rank: int, world: int, local_rank: int):
     ev[0].record()
     for _ in range(args.steps):
         loss = step(True)
-        if world > 1:
-            torch.cuda.synchronize()
-            ar_ms += ev[2].elapsed_time(ev[3])
+        torch.cuda.synchronize()
+        ar_ms += ev[2].elapsed_time(ev[3])
     ev[1].record()
     torch.cuda.synchronize()
     if world > 1:
@@ -542,19 +690,25 @@ def run_train_step(args, rank: int, world: int, local_rank: int):
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     pshattn.device_status()
-    if rank == 0:
-        ms_per_step = ms[0].item() / args.steps
-        pts = args.scenes * args.points * world
-        print(json.dumps({"metric": "points/sec (Flash3D backbone fwd+bwd+SGD)", "value": pts / (ms_per_step * 1e-3), "unit": "points/s",
-                          "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
-                          "higher_is_better": True, "scaling": "weak", "dtype": "bf16", "data": "synthetic",
-                          "config": {"workload": f"flash3d_backbone_train_step_{args.scenes}x{args.points // 1000}k_per_gpu",
-                                     "micro_batch_scenes": micro, "parameters": n_params, "grad_allreduce_bytes": 4 * n_params},
-                          "peak_memory_gb": torch.cuda.max_memory_allocated(dev) / 1e9,
-                          "grad_allreduce_ms_per_step": ms[1].item() / args.steps, "loss": float(loss.detach())}), flush=True)
+    reducer.close()
+    ms_per_step = ms[0].item() / args.steps
+    pts = args.scenes * args.points * world
+    return {"metric": "points/sec (Flash3D backbone fwd+bwd+SGD)", "value": pts / (ms_per_step * 1e-3), "unit": "points/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "strong" if args.scenes * world == 64 else "weak", "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": f"flash3d_backbone_train_step_{args.scenes}x{args.points // 1000}k_per_gpu",
+                       "global_batch_scenes": args.scenes * world, "micro_batch_scenes": micro, "parameters": n_params,
+                       "grad_allreduce_bytes": 4 * n_params, "grad_buckets": len(reducer.buckets)},
+            "peak_memory_gb": torch.cuda.max_memory_allocated(dev) / 1e9,
+            "grad_allreduce_exposed_ms_per_step": ms[1].item() / args.steps, "loss": float(loss.detach())}
 
 
 def run_psh_pool(args):
+    print(json.dumps(psh_pool_measure(args)), flush=True)
+
+
+def psh_pool_measure(args):
     """PSH build + scatter, three rounds of stride-2 sub-bucket pooling and the matching unpools on 8 scenes of
     1,000,000 points with heavy-tailed (Zipf 1.5) voxel occupancy, feature dim 128 fp32.  Reports points/s and the
     algorithmic HBM GB/s of every kernel family."""
@@ -645,7 +799,7 @@ def run_psh_pool(args):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms, "higher_is_better": True, "dtype": "f32",
             "data": "synthetic", "config": {"workload": f"psh_pool_unpool_8x{pts // 1000}k_zipf_c128_fp32_bucket2048"},
             "kernels": fam, "peak_hbm_gbs": peaks["hbm_gbs"], "peak_source": peaks["source"]}
-    print(json.dumps(line), flush=True)
+    return line
 
 
 def main():
@@ -659,6 +813,7 @@ def main():
     ap.add_argument("--micro-scenes", type=int, default=0, help="train_step: scenes per micro-batch (gradient accumulation); 0 = all")
     ap.add_argument("--ref-points", type=int, default=20000, help="points of the CPU arm's bounded sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="backbone: skip the short runs of the other configurations")
     ap.add_argument("--workload", default="backbone", choices=["backbone", "attn_layer", "psh_pool", "gemm_mix", "train_step"],
                     help="backbone = the headline metric; the others are single-GPU side measurements")
     ap.add_argument("--layer-scenes", type=int, default=8, help="attn_layer: number of 120k-point scans (fewer for a profiler capture)")

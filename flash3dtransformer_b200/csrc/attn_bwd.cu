@@ -798,12 +798,8 @@ __global__ void attn_bwd_dq_convert_kernel(const float *__restrict__ acc, __nv_b
 template <int D>
 static int launch_attn_bwd(const void *Q, const void *K, const void *V, const void *dO, AttnBwdArgs a, int device, cudaStream_t st) {
   using C = BwdCfg<D>;
-  static bool attr[16] = {false};
   auto kern = attn_bwd_kernel<D>;
-  if (device < 16 && !attr[device]) {
-    F3D_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem));
-    attr[device] = true;
-  }
+  F3D_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(kern), device, C::kSmem));
   CUtensorMap mq, mk, mv, mdo;
   const uint64_t rows = (uint64_t)a.B * a.L;
   const uint64_t s1 = (uint64_t)D * 2, s2 = (uint64_t)a.H * D * 2;
@@ -825,12 +821,8 @@ template <int D>
 static int launch_attn_bwd_window(const void *Q, const void *K, const void *V, const void *dO, void *dQ, AttnBwdArgs a, int device,
                                   cudaStream_t st) {
   using C = BwdWinCfg<D>;
-  static bool attr[16] = {false};
   auto kern = attn_bwd_window_kernel<D>;
-  if (device < 16 && !attr[device]) {
-    F3D_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem));
-    attr[device] = true;
-  }
+  F3D_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(kern), device, C::kSmem));
   CUtensorMap mq, mk, mv, mdo;
   const uint64_t rows = (uint64_t)a.B * a.L;
   const uint64_t s1 = (uint64_t)D * 2, s2 = (uint64_t)a.H * D * 2;
@@ -863,7 +855,10 @@ extern "C" int f3d_buck_swin_bwd(const void *Q, const void *K, const void *V, co
   attn_bwd_delta_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(O), static_cast<const __nv_bfloat16 *>(dO),
                                                                        static_cast<float *>(Delta), rows, D);
   F3D_TRY(check_launch("buck_swin_bwd (delta)"));
-  if (num_scopes == 0) return F3D_OK;
+  if (num_scopes == 0) {          // no bucket is listed: dQ is all zero, dK and dV have no listed rows
+    F3D_CUDA_TRY(cudaMemsetAsync(dQ, 0, rows * D * sizeof(__nv_bfloat16), st));
+    return maybe_sync(st, "buck_swin_bwd");
+  }
   const long long window_tiles = (long long)scope_size * (bucket_size / 128);
   if (D <= 32 && window_tiles <= BwdWinCfg<32>::kMaxTiles) {
     // small windows: one CTA per (scope, head) keeps every dQ tile in tensor memory, no scratch and no reductions
@@ -873,11 +868,16 @@ extern "C" int f3d_buck_swin_bwd(const void *Q, const void *K, const void *V, co
                   B, L, H, num_scopes, scope_size, (int)bucket_size, (int)bucket_size / kBK, 1.4426950408889634f * scale, scale,
                   status_word(device)};
     if (!a.status) return F3D_ERR_CUDA;
+    // this kernel writes dQ only for the tokens of listed buckets; the general path below writes every row (zero where
+    // no scope lists the bucket).  Both give the same dQ: rows of unlisted buckets are cleared here when the table is too
+    // short to list every bucket once.
+    if ((long long)num_scopes * scope_size * (long long)bucket_size < (long long)L)
+      F3D_CUDA_TRY(cudaMemsetAsync(dQ, 0, rows * D * sizeof(__nv_bfloat16), st));
     F3D_TRY(D == 16 ? launch_attn_bwd_window<16>(Q, K, V, dO, dQ, a, device, st) : launch_attn_bwd_window<32>(Q, K, V, dO, dQ, a, device, st));
     return maybe_sync(st, "buck_swin_bwd");
   }
   void *acc = nullptr;
-  F3D_TRY(workspace(device, 2, rows * D * sizeof(float), &acc));
+  F3D_TRY(workspace(device, 2, rows * D * sizeof(float), st, &acc));
   F3D_CUDA_TRY(cudaMemsetAsync(acc, 0, rows * D * sizeof(float), st));
   const float scale = 1.f / sqrtf((float)D);
   AttnBwdArgs a{static_cast<const float *>(LSE), static_cast<const float *>(Delta), static_cast<float *>(acc),

@@ -320,12 +320,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 template <int D, int BKV>
 static int launch_attn_fwd(const void *Q, const void *K, const void *V, AttnFwdArgs a, int device, cudaStream_t st) {
   using C = AttnCfg<D, BKV>;
-  static bool attr[16] = {false};
   auto kern = attn_fwd_kernel<D, BKV>;
-  if (device < 16 && !attr[device]) {
-    F3D_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem));
-    attr[device] = true;
-  }
+  F3D_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(kern), device, C::kSmem));
   CUtensorMap mq, mk, mv;
   const uint64_t rows = (uint64_t)a.B * a.L;
   const uint64_t s1 = (uint64_t)D * 2, s2 = (uint64_t)a.H * D * 2;

@@ -23,11 +23,18 @@ namespace f3d {
 char *err_buf();                       // thread-local, 512 bytes
 int set_error(int code, const char *fmt, ...);
 
-// Grow-only scratch workspace, one per device and slot.  The returned pointer stays valid until a later
-// call on the same (device, slot) asks for more bytes.  All kernels of one entry point run on the
-// caller's stream, so reuse across calls on that stream is ordered.
-int workspace(int device, int slot, size_t bytes, void **out);
+// Grow-only scratch workspace, one block per (device, slot, stream).  The returned pointer stays valid until a later
+// call with the same key asks for more bytes.  All kernels of one entry point run on the caller's stream, so reuse
+// across calls on that stream is ordered; calls on different streams get different blocks and may overlap on the GPU.
+// When a block has to grow, only its own stream is waited for before the old block is freed.  What stays with the
+// caller, as with any CUDA stream: two host threads must not issue calls on the SAME stream at the same time.
+int workspace(int device, int slot, size_t bytes, cudaStream_t stream, void **out);
 void workspace_release_all();
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (kernel, device), for any device ordinal and from any
+// host thread.
+int ensure_dynamic_smem(const void *kernel, int device, int bytes);
+int sm_count(int device);              // multiprocessors of a device (cached)
 
 bool sync_flag();
 void count_launches(int n);            // kernels launched by this library since load (f3d_launch_count)

@@ -33,19 +33,51 @@ int set_error(int code, const char *fmt, ...) {
 bool sync_flag() { return g_sync.load() != 0; }
 uint64_t seed() { return g_seed.load(); }
 
-struct Slot { void *ptr = nullptr; size_t bytes = 0; };
+struct Slot { void *ptr = nullptr; size_t bytes = 0; unsigned long long last_use = 0; };
+struct SlotKey {
+  int device, slot;
+  cudaStream_t stream;
+  bool operator<(const SlotKey &o) const {
+    if (device != o.device) return device < o.device;
+    if (slot != o.slot) return slot < o.slot;
+    return stream < o.stream;
+  }
+};
 static std::mutex g_ws_mu;
-static std::map<std::pair<int, int>, Slot> g_ws;
+static std::map<SlotKey, Slot> g_ws;
+static unsigned long long g_ws_clock = 0;
+// blocks kept per (device, slot) before the least recently used one is given back: streams come and go, and a
+// handle value may belong to a stream that no longer exists
+constexpr int kMaxStreamsPerSlot = 8;
 
-int workspace(int device, int slot, size_t bytes, void **out) {
+int workspace(int device, int slot, size_t bytes, cudaStream_t stream, void **out) {
   std::lock_guard<std::mutex> lk(g_ws_mu);
-  Slot &s = g_ws[{device, slot}];
+  const SlotKey key{device, slot, stream};
+  auto it = g_ws.find(key);
+  if (it == g_ws.end()) {
+    // a new stream for this slot: evict the least recently used block when the slot holds too many.  Its stream may
+    // be gone, so nothing stream-specific is called on it; cudaFree waits for all work of the device by itself.
+    int held = 0;
+    auto lru = g_ws.end();
+    for (auto jt = g_ws.begin(); jt != g_ws.end(); ++jt)
+      if (jt->first.device == device && jt->first.slot == slot) {
+        ++held;
+        if (lru == g_ws.end() || jt->second.last_use < lru->second.last_use) lru = jt;
+      }
+    if (held >= kMaxStreamsPerSlot && lru != g_ws.end()) {
+      if (lru->second.ptr) F3D_CUDA_TRY(cudaFree(lru->second.ptr));
+      g_ws.erase(lru);
+    }
+    it = g_ws.emplace(key, Slot{}).first;
+  }
+  Slot &s = it->second;
+  s.last_use = ++g_ws_clock;
   if (s.bytes < bytes) {
     // round up so that slowly growing requests do not reallocate every call
     size_t want = bytes + bytes / 4 + 4096;
     if (s.ptr) {
-      // the old block may still be in use by kernels queued earlier: wait for the device first
-      F3D_CUDA_TRY(cudaDeviceSynchronize());
+      // only kernels queued on this stream can still be using the old block
+      F3D_CUDA_TRY(cudaStreamSynchronize(stream));
       F3D_CUDA_TRY(cudaFree(s.ptr));
       s.ptr = nullptr; s.bytes = 0;
     }
@@ -56,30 +88,59 @@ int workspace(int device, int slot, size_t bytes, void **out) {
   return F3D_OK;
 }
 
+static std::mutex g_attr_mu;
+static std::map<std::pair<const void *, int>, int> g_attr;
+
+int ensure_dynamic_smem(const void *kernel, int device, int bytes) {
+  std::lock_guard<std::mutex> lk(g_attr_mu);
+  auto key = std::make_pair(kernel, device);
+  auto it = g_attr.find(key);
+  if (it != g_attr.end() && it->second >= bytes) return F3D_OK;
+  F3D_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  g_attr[key] = bytes;
+  return F3D_OK;
+}
+
+static std::map<int, int> g_sms;
+
+int sm_count(int device) {
+  std::lock_guard<std::mutex> lk(g_attr_mu);
+  auto it = g_sms.find(device);
+  if (it != g_sms.end()) return it->second;
+  int n = 148;
+  cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device);
+  g_sms[device] = n;
+  return n;
+}
+
 static std::mutex g_st_mu;
-static int *g_status[16] = {nullptr};
+static std::map<int, int *> g_status;
 
 // Device word that kernels with bounded waits set (once, with atomicCAS) when a wait is abandoned.
 int *status_word(int device) {
   std::lock_guard<std::mutex> lk(g_st_mu);
-  if (device < 0 || device >= 16) { set_error(F3D_ERR_ARG, "device %d out of range", device); return nullptr; }
-  if (!g_status[device]) {
+  if (device < 0) { set_error(F3D_ERR_ARG, "device %d out of range", device); return nullptr; }
+  auto it = g_status.find(device);
+  if (it == g_status.end()) {
     int *p = nullptr;
     if (cudaMalloc(&p, 256) != cudaSuccess || cudaMemset(p, 0, 256) != cudaSuccess) {
       set_error(F3D_ERR_CUDA, "cannot allocate the device status word");
       return nullptr;
     }
-    g_status[device] = p;
+    it = g_status.emplace(device, p).first;
   }
-  return g_status[device];
+  return it->second;
 }
 
 void workspace_release_all() {
   std::lock_guard<std::mutex> lk(g_ws_mu);
+  int prev = -1;
+  cudaGetDevice(&prev);
   for (auto &kv : g_ws) {
-    if (kv.second.ptr) { cudaSetDevice(kv.first.first); cudaFree(kv.second.ptr); }
+    if (kv.second.ptr) { cudaSetDevice(kv.first.device); cudaFree(kv.second.ptr); }
   }
   g_ws.clear();
+  if (prev >= 0) cudaSetDevice(prev);
 }
 
 }  // namespace f3d

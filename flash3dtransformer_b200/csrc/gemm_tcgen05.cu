@@ -347,27 +347,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   if (warp == 1) { tc::tc_fence_after_sync(); tc::tmem_dealloc(tmem_base, kTmemCols); }
 }
 
-static int g_sm_count[16] = {0};
-
-static int sm_count(int device) {
-  if (device < 16 && g_sm_count[device]) return g_sm_count[device];
-  int n = 148;
-  cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device);
-  if (device < 16) g_sm_count[device] = n;
-  return n;
-}
-
 int *status_word(int device);   // device word, zero until a kernel reports an abandoned wait
 
 template <int BN>
 static int launch_gemm(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mc, const GemmArgs &g, int device,
                        cudaStream_t st) {
-  static bool attr[16] = {false};
   auto kern = gemm_bf16_tcgen05_kernel<BN>;
-  if (device < 16 && !attr[device]) {
-    F3D_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN>::kTotal));
-    attr[device] = true;
-  }
+  F3D_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(kern), device, GemmSmem<BN>::kTotal));
   int tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN);
   int grid = tiles < sm_count(device) ? tiles : sm_count(device);
   kern<<<grid, kGemmThreads, GemmSmem<BN>::kTotal, st>>>(ma, mb, mc, g);
@@ -455,7 +441,7 @@ extern "C" int f3d_gemm_sm_bf16(const void *A, const void *B, void *O, int M, in
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (M <= 0 || N <= 0 || K <= 0) return set_error(F3D_ERR_ARG, "gemm_sm_bf16: empty operand");
   void *bt = nullptr;
-  F3D_TRY(workspace(device, 1, (size_t)N * K * 2, &bt));
+  F3D_TRY(workspace(device, 1, (size_t)N * K * 2, st, &bt));
   dim3 grid((N + 31) / 32, (K + 31) / 32), block(32, 8);
   transpose_bf16_kernel<<<grid, block, 0, st>>>(static_cast<const __nv_bfloat16 *>(B), static_cast<__nv_bfloat16 *>(bt), K, N);
   F3D_TRY(check_launch("transpose"));

@@ -183,7 +183,7 @@ extern "C" int f3d_layernorm_bwd_bf16(const void *x, const void *grad_out, const
   uint32_t grid = (rows + rows_per_block - 1) / rows_per_block;
   if (grid > 148u * 8u) grid = 148u * 8u;
   void *partial = nullptr;
-  F3D_TRY(workspace(device, 3, (size_t)grid * 2 * C * sizeof(float), &partial));
+  F3D_TRY(workspace(device, 3, (size_t)grid * 2 * C * sizeof(float), st, &partial));
   auto xp = static_cast<const __nv_bfloat16 *>(x), gp = static_cast<const __nv_bfloat16 *>(grad_out);
   auto dxp = static_cast<__nv_bfloat16 *>(grad_x);
   auto wp = static_cast<const float *>(weight);

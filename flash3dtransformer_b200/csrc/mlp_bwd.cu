@@ -128,7 +128,7 @@ extern "C" int f3d_colsum_bf16(const void *x, void *out, uint64_t rows, uint32_t
   for (uint32_t c0 = 0; c0 < C; c0 += 2048) {
     const uint32_t cb = C - c0 < 2048 ? C - c0 : 2048;
     void *partial = nullptr;
-    F3D_TRY(workspace(device, 4, (size_t)blocks * 2048 * sizeof(float), &partial));
+    F3D_TRY(workspace(device, 4, (size_t)blocks * 2048 * sizeof(float), st, &partial));
     // a block is [row slots][chunks of 8 channels]
     const uint32_t chunks = cb / 8;
     const uint32_t threads = 256 / chunks * chunks;

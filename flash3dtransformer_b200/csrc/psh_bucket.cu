@@ -30,6 +30,8 @@
 // merged with match_any (warp-aggregated counting), per-warp counters live in shared memory, and coordinates
 // are staged into shared memory with 128-bit loads.
 #include "f3d_common.cuh"
+#include <map>
+#include <mutex>
 #include "psh_device.cuh"
 #include "../../include/f3d_b200.h"
 
@@ -743,17 +745,13 @@ static int psh_run(PshArgs a, const PshPlan &p, uint32_t *scratch, uint32_t max_
   a.tile_movers = w; w += rows;
   a.tile = p.tile; a.tiles_max = p.tiles_max; a.nbp = p.nbp;
 
-  static bool attr_done[16] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev < 16 && !attr_done[dev]) {
-    // opt in once per device to the large dynamic shared memory the rank kernels may ask for
-    F3D_CUDA_TRY(cudaFuncSetAttribute(psh_hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    F3D_CUDA_TRY(cudaFuncSetAttribute(psh_rankA_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    F3D_CUDA_TRY(cudaFuncSetAttribute(psh_resolveB_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    F3D_CUDA_TRY(cudaFuncSetAttribute(psh_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    attr_done[dev] = true;
-  }
+  // opt in once per device to the large dynamic shared memory the rank kernels may ask for
+  F3D_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(psh_hist_kernel), dev, 200 * 1024));
+  F3D_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(psh_rankA_kernel), dev, 200 * 1024));
+  F3D_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(psh_resolveB_kernel), dev, 200 * 1024));
+  F3D_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(psh_scatter_kernel), dev, 200 * 1024));
   if (p.smem_rank > 200 * 1024) return set_error(F3D_ERR_UNSUPPORTED, "num_bucket=%u needs %zu bytes of shared memory", a.nb, p.smem_rank);
 
   dim3 grid(p.tiles_max, a.batch);
@@ -780,23 +778,12 @@ static int psh_run(PshArgs a, const PshPlan &p, uint32_t *scratch, uint32_t max_
   return check_launch("psh kernels", (max_n > 0 ? 3 : 0) + (gx > 0 ? 1 : 0));
 }
 
-}  // namespace f3d
-
-using namespace f3d;
-
-extern "C" int f3d_batch_psh_scatter_pad_hash(
+// The kernel arguments of one PSH call from the C-ABI arguments (shared by the two entry points below).
+static PshArgs psh_pack_args(
     const void *coord, void *bucket_id, void *bucket_counter, void *bucket_offset, const void *batch_sep,
-    uint32_t total_N, uint32_t batch_size, uint32_t instance_max_N, uint32_t num_bucket, uint32_t bucket_divisor,
-    uint32_t bucket_size, uint32_t num_vox, const void *bbox_min, const void *bbox_max, const void *probe_offsets,
-    void *cumsum_counter, void *scatter_coord, uint32_t pad_to_N, float pad_num, uint32_t hash_type,
-    int device, void *stream) {
-  F3D_TRY(psh_validate(total_N, batch_size, num_bucket, bucket_divisor, bucket_size, num_vox, pad_to_N, hash_type));
-  DeviceGuard guard(device);
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (instance_max_N > total_N) instance_max_N = total_N;
-  PshPlan p = psh_plan(batch_size, instance_max_N, num_bucket);
-  void *scratch = nullptr;
-  F3D_TRY(workspace(device, 0, p.scratch_words * sizeof(uint32_t), &scratch));
+    uint32_t total_N, uint32_t batch_size, uint32_t num_bucket, uint32_t bucket_divisor, uint32_t bucket_size,
+    uint32_t num_vox, const void *bbox_min, const void *bbox_max, const void *probe_offsets, void *cumsum_counter,
+    void *scatter_coord, uint32_t pad_to_N, float pad_num, uint32_t hash_type) {
   PshArgs a{};
   a.coord = static_cast<const __half *>(coord);
   a.bucket_id = static_cast<uint16_t *>(bucket_id);
@@ -815,6 +802,29 @@ extern "C" int f3d_batch_psh_scatter_pad_hash(
   uint64_t sd = f3d::seed();
   a.key.k0 = (uint32_t)sd; a.key.k1 = (uint32_t)(sd >> 32);
   a.scene_base = f3d::scene_base();
+  return a;
+}
+
+}  // namespace f3d
+
+using namespace f3d;
+
+extern "C" int f3d_batch_psh_scatter_pad_hash(
+    const void *coord, void *bucket_id, void *bucket_counter, void *bucket_offset, const void *batch_sep,
+    uint32_t total_N, uint32_t batch_size, uint32_t instance_max_N, uint32_t num_bucket, uint32_t bucket_divisor,
+    uint32_t bucket_size, uint32_t num_vox, const void *bbox_min, const void *bbox_max, const void *probe_offsets,
+    void *cumsum_counter, void *scatter_coord, uint32_t pad_to_N, float pad_num, uint32_t hash_type,
+    int device, void *stream) {
+  F3D_TRY(psh_validate(total_N, batch_size, num_bucket, bucket_divisor, bucket_size, num_vox, pad_to_N, hash_type));
+  DeviceGuard guard(device);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (instance_max_N > total_N) instance_max_N = total_N;
+  PshPlan p = psh_plan(batch_size, instance_max_N, num_bucket);
+  void *scratch = nullptr;
+  F3D_TRY(workspace(device, 0, p.scratch_words * sizeof(uint32_t), st, &scratch));
+  PshArgs a = psh_pack_args(coord, bucket_id, bucket_counter, bucket_offset, batch_sep, total_N, batch_size, num_bucket,
+                            bucket_divisor, bucket_size, num_vox, bbox_min, bbox_max, probe_offsets, cumsum_counter,
+                            scatter_coord, pad_to_N, pad_num, hash_type);
   F3D_TRY(maybe_sync(st, "batch_psh_scatter_pad_hash"));
   F3D_TRY(psh_run(a, p, static_cast<uint32_t *>(scratch), instance_max_N, st));
   return maybe_sync(st, "batch_psh_scatter_pad_hash");
@@ -840,15 +850,18 @@ namespace f3d {
 // The symbol name above is only a host-side handle; kernels need the device address, looked up once per
 // device with that device current.
 static int static_scratch_ptr(int device, uint32_t **out) {
-  static uint32_t *ptrs[16] = {nullptr};
-  if (device < 0 || device >= 16) return set_error(F3D_ERR_ARG, "device %d out of range", device);
-  if (!ptrs[device]) {
+  static std::mutex mu;
+  static std::map<int, uint32_t *> ptrs;
+  if (device < 0) return set_error(F3D_ERR_ARG, "device %d out of range", device);
+  std::lock_guard<std::mutex> lk(mu);
+  auto it = ptrs.find(device);
+  if (it == ptrs.end()) {
     void *p = nullptr;
     cudaError_t e = cudaGetSymbolAddress(&p, g_psh_static_scratch);
     if (e != cudaSuccess) return set_error(F3D_ERR_CUDA, "cudaGetSymbolAddress(static scratch): %s", cudaGetErrorString(e));
-    ptrs[device] = static_cast<uint32_t *>(p);
+    it = ptrs.emplace(device, static_cast<uint32_t *>(p)).first;
   }
-  *out = ptrs[device];
+  *out = it->second;
   return F3D_OK;
 }
 }  // namespace f3d
@@ -871,23 +884,11 @@ extern "C" int f3d_batch_psh_scatter_pad_hash_noalloc(
                      p.scratch_words, batch_size, p.tiles_max, num_bucket, kStaticScratchWords);
   uint32_t *scratch = nullptr;
   F3D_TRY(static_scratch_ptr(device, &scratch));
-  PshArgs a{};
-  a.coord = static_cast<const __half *>(coord);
-  a.bucket_id = static_cast<uint16_t *>(bucket_id);
-  a.bucket_counter = static_cast<uint32_t *>(bucket_counter);
-  a.bucket_offset = static_cast<uint32_t *>(bucket_offset);
-  a.batch_sep = static_cast<const uint32_t *>(batch_sep);
-  a.cumsum_counter = static_cast<uint32_t *>(cumsum_counter);
-  a.scatter_coord = static_cast<__half *>(scatter_coord);
-  a.bbox_min = static_cast<const __half *>(bbox_min);
-  a.bbox_max = static_cast<const __half *>(bbox_max);
-  a.probe = static_cast<const int16_t *>(probe_offsets);
-  a.total_N = total_N; a.batch = batch_size; a.nb = num_bucket; a.divisor = bucket_divisor; a.cap = bucket_size;
-  a.num_vox = num_vox; a.hash_type = hash_type; a.pad_to = pad_to_N;
-  a.pad_bits = __half_as_ushort(__float2half_rn(pad_num));
-  a.coord_aligned = (reinterpret_cast<uintptr_t>(coord) % 16 == 0) ? 1 : 0;
-  uint64_t sd = f3d::seed();
-  a.key.k0 = (uint32_t)sd; a.key.k1 = (uint32_t)(sd >> 32);
-  a.scene_base = f3d::scene_base();
-  return psh_run(a, p, scratch, instance_max_N, st);
+  PshArgs a = psh_pack_args(coord, bucket_id, bucket_counter, bucket_offset, batch_sep, total_N, batch_size, num_bucket,
+                            bucket_divisor, bucket_size, num_vox, bbox_min, bbox_max, probe_offsets, cumsum_counter,
+                            scatter_coord, pad_to_N, pad_num, hash_type);
+  // the sync_stream debug switch is honoured like in the regular entry point (a stream synchronisation allocates nothing)
+  F3D_TRY(maybe_sync(st, "batch_psh_scatter_pad_hash_noalloc"));
+  F3D_TRY(psh_run(a, p, scratch, instance_max_N, st));
+  return maybe_sync(st, "batch_psh_scatter_pad_hash_noalloc");
 }

@@ -24,7 +24,7 @@ __global__ void __launch_bounds__(256) scatter_index_kernel(const uint16_t *__re
   const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= pad_to) return;
   if (i >= total_N) { out2in[i] = total_N + 3u; return; }
-  // scene of point i: first separator above i (separators are inclusive scene ends in ascending order)
+  // scene of point i: first separator above i (separators are cumulative point counts, i.e. exclusive scene ends, in ascending order)
   uint32_t lo = 0, hi = batch - 1;
   while (lo < hi) {
     const uint32_t mid = (lo + hi) >> 1;

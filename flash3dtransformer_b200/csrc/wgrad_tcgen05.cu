@@ -202,15 +202,6 @@ __global__ void __launch_bounds__(256) wgrad_reduce_kernel(const float *__restri
 
 using namespace f3d;
 
-static int sm_count_of(int device) {
-  static int n[16] = {0};
-  if (device < 16 && n[device]) return n[device];
-  int v = 148;
-  cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, device);
-  if (device < 16) n[device] = v;
-  return v;
-}
-
 extern "C" int f3d_linear_wgrad_bf16(const void *grad_out, const void *x, void *grad_weight, void *grad_bias, int M, int N, int K,
                                      int device, void *stream) {
   if (M <= 0 || N <= 0 || K <= 0) return set_error(F3D_ERR_ARG, "linear_wgrad: M, N, K must be positive (got %d, %d, %d)", M, N, K);
@@ -232,7 +223,7 @@ extern "C" int f3d_linear_wgrad_bf16(const void *grad_out, const void *x, void *
   const int total_blocks = (M + kWgRows - 1) / kWgRows;
   // one CTA per SM (a CTA's fixed costs - tensor-memory allocation, filling the ring, writing its partial tile - are
   // paid once per slab): as many slabs as fit one wave, at least four row blocks each
-  int slabs = sm_count_of(device) / tiles;
+  int slabs = sm_count(device) / tiles;
   if (slabs > (total_blocks + 3) / 4) slabs = (total_blocks + 3) / 4;
   if (slabs < 1) slabs = 1;
   a.blocks_per_slab = (total_blocks + slabs - 1) / slabs;
@@ -240,7 +231,7 @@ extern "C" int f3d_linear_wgrad_bf16(const void *grad_out, const void *x, void *
   void *scratch = nullptr;
   const size_t nw = (size_t)N * K, nb = grad_bias ? (size_t)N : 0;
   a.slab_stride = nw + nb;
-  F3D_TRY(workspace(device, 5, (size_t)a.slabs * a.slab_stride * sizeof(float), &scratch));
+  F3D_TRY(workspace(device, 5, (size_t)a.slabs * a.slab_stride * sizeof(float), st, &scratch));
   a.partial_w = static_cast<float *>(scratch);
   a.partial_b = grad_bias ? a.partial_w + nw : nullptr;
   a.status = status_word(device);
@@ -249,11 +240,7 @@ extern "C" int f3d_linear_wgrad_bf16(const void *grad_out, const void *x, void *
   F3D_TRY(encode_tmap_2d(&mg, 0, grad_out, (uint64_t)N, (uint64_t)M, (uint64_t)N * 2, 64, kWgRows, 128));
   F3D_TRY(encode_tmap_2d(&mx, 0, x, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, K == 32 ? 32 : 64, kWgRows, K == 32 ? 64 : 128));
   const int smem = kWgStages * (2 + a.x_panels) * kWgPanelBytes + 256 + 1024;
-  static int attr_smem[16] = {0};
-  if (device < 16 && attr_smem[device] < smem) {
-    F3D_CUDA_TRY(cudaFuncSetAttribute(wgrad_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kWgStages * 6 * kWgPanelBytes + 256 + 1024));
-    attr_smem[device] = kWgStages * 6 * kWgPanelBytes + 256 + 1024;
-  }
+  F3D_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(wgrad_tcgen05_kernel), device, kWgStages * 6 * kWgPanelBytes + 256 + 1024));
   dim3 grid(tiles, a.slabs);
   wgrad_tcgen05_kernel<<<grid, kWgThreads, smem, st>>>(mg, mx, a);
   F3D_TRY(check_launch("linear_wgrad"));

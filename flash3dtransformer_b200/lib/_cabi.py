@@ -75,6 +75,10 @@ def load() -> ctypes.CDLL:
     return lib
 
 
+def is_loaded() -> bool:
+    return _lib is not None
+
+
 def last_error() -> str:
     msg = load().f3d_last_error()
     return msg.decode("utf-8", "replace") if msg else ""

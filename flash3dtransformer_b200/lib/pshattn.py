@@ -84,9 +84,15 @@ class DeviceManagerSingleton:
         _cabi.load()
 
     def set_sync_stream(self, flag: bool) -> bool:
+        # switching the flag off on a process that has not loaded the library yet is a no-op (off is the initial state):
+        # building a model on a host without the CUDA library (the CPU restatement does) must not need it
+        if not flag and not _cabi.is_loaded():
+            return False
         return bool(_cabi.load().f3d_set_sync(1 if flag else 0))
 
     def get_sync_stream(self) -> bool:
+        if not _cabi.is_loaded():
+            return False
         return bool(_cabi.load().f3d_get_sync())
 
     # additions of this build

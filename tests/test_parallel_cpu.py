@@ -70,6 +70,47 @@ def _worker(rank, world, port, sizes):
         assert torch.allclose(lin.weight.grad, torch.full_like(lin.weight, 1.5))
         assert torch.allclose(lin.bias.grad, torch.full_like(lin.bias, 15.0))
         assert torch.allclose(extra.grad, torch.full((3,), 0.5))
+        # with the global batch known up front the statistics need no read-back and give the same values
+        (lo2, hi2), mean2 = parallel.global_psh_stats(local, lseps, total_scenes=len(sizes), total_points=int(sum(sizes)))
+        assert torch.equal(lo2, lo) and torch.equal(hi2, hi) and mean2 == mean_n
+        # overlapped reduction: buckets issued from gradient hooks during the backward, two micro-batches per step,
+        # a parameter that takes part in the loss on one rank only, and the same result as the plain all-reduce
+        torch.manual_seed(1)
+        net = torch.nn.Sequential(torch.nn.Linear(6, 16), torch.nn.GELU(), torch.nn.Linear(16, 16), torch.nn.GELU(),
+                                  torch.nn.Linear(16, 3))
+        side = torch.nn.Parameter(torch.ones(3))
+        plist = list(net.parameters()) + [side]
+        reducer = parallel.GradientBucketReducer(plist, bucket_bytes=256)
+        assert len(reducer.buckets) >= 3
+        g = torch.Generator().manual_seed(100 + rank)
+        xs = [torch.randn(5, 6, generator=g) for _ in range(2)]
+        for step in range(2):
+            reducer.zero()
+            for i, x in enumerate(xs):
+                loss = net(x).square().mean() + ((side * (step + 1)).sum() if rank == 0 else 0.0)
+                if i == len(xs) - 1:
+                    with reducer.reducing():
+                        loss.backward()
+                else:
+                    loss.backward()
+            reducer.finish()
+            got = [p.grad.clone() for p in plist]
+            # the same gradients by plain autograd + all-reduce
+            ref_net = [p.detach().clone().requires_grad_(True) for p in plist]
+            def fwd(x):
+                h = torch.nn.functional.gelu(x @ ref_net[0].t() + ref_net[1])
+                h = torch.nn.functional.gelu(h @ ref_net[2].t() + ref_net[3])
+                return h @ ref_net[4].t() + ref_net[5]
+            for x in xs:
+                (fwd(x).square().mean() + ((ref_net[6] * (step + 1)).sum() if rank == 0 else 0.0)).backward()
+            for q in ref_net:
+                if q.grad is None:
+                    q.grad = torch.zeros_like(q)
+                dist.all_reduce(q.grad)
+                q.grad /= world
+            for a, q in zip(got, ref_net):
+                assert torch.allclose(a, q.grad, atol=1e-6), step
+        reducer.close()
     finally:
         dist.destroy_process_group()
 
