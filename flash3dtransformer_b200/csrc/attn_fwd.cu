@@ -8,20 +8,24 @@
 // those buckets attend to each other with softmax(Q K^T / sqrt(D)) V; LSE is the natural-log row normaliser.
 // Buckets that no scope lists are left untouched.
 //
-// Kernel shape: one CTA = 128 query rows of one (scope, head, batch row); 192 threads:
-//   warp 0     TMA producer: Q tile once, then K/V tiles of 64 keys through a 4-stage ring (3-D tensor maps over
-//              [token, head, dim], swizzle width = min(128, 2*D) bytes)
-//   warp 1     owns tensor memory, issues S = Q K^T (M=128, N=64) and O += P V (A operand P read from tensor
-//              memory, V as MN-major B operand), commits mbarriers
-//   warps 2-5  softmax: one thread per query row; S is read with tcgen05.ld, the running maximum and sum are kept
-//              in the base-2 domain, P is written as bf16 with tcgen05.st, O is rescaled in tensor memory only
-//              when the row maximum moved, and the epilogue normalises and stores O and LSE
-// Tensor memory holds S (64 columns), P (32) and O (D) side by side: because P does not overwrite S, the MMA warp
-// issues the next tile's Q K^T as soon as the softmax threads have pulled S into registers, so the tensor pipe
-// computes S(j+1) while the warps exponentiate tile j, and the per-tile chain is the softmax arithmetic alone.
-// 128 columns (256 for D >= 64) and 40 KB of shared memory per CTA at D = 32 put four CTAs on an SM.  At D = 32
-// the kernel is bound by the special-function unit (one ex2 per score against 4*D = 128 tensor FLOPs) and by
-// instruction issue of the softmax warps, not by the tensor pipe.
+// Kernel shape: one CTA = NQ tiles of 128 query rows of one (scope, head, batch row) that share one stream of K/V
+// tiles (the library instantiates NQ = 1; the scope's query tiles must be a multiple of NQ); 32 + 128 * NQ threads:
+//   warp 0        one elected thread is both the TMA producer and the MMA issuer.  It loads the Q tiles once and K/V
+//                 tiles of 64 keys through a 4-stage ring (3-D tensor maps over [token, head, dim], swizzle width =
+//                 min(128, 2*D) bytes), issues S_t = Q_t K^T (M=128, N=64) and O_t += P_t V (A operand P read from
+//                 tensor memory, V as MN-major B operand) for every query tile t and commits mbarriers.  A ring stage
+//                 is refilled without a barrier of its own: when the softmax warps of every tile have delivered P of
+//                 key tile j, they had all seen O complete up to tile j-1, so the MMAs that read stage (j-1) % 4 are
+//                 done and key tile j+3 may land there.
+//   warps 1..4NQ  softmax, four warps per query tile, one thread per query row; S is read with tcgen05.ld, the
+//                 running maximum and sum are kept in the base-2 domain, P is written as bf16 with tcgen05.st, O is
+//                 rescaled in tensor memory only when the row maximum moved, and the epilogue normalises and stores O
+//                 and LSE
+// Per query tile, tensor memory holds S (64 columns), P (32) and O (D) side by side: because P does not overwrite S,
+// the next key tile's Q K^T is issued as soon as the softmax threads have pulled S into registers, so the tensor pipe
+// computes S(j+1) while the warps exponentiate tile j.  At D = 32 the kernel is bound by the special-function unit
+// (one ex2 per score against 4*D = 128 tensor FLOPs) and by instruction issue of the softmax warps, not by the tensor
+// pipe; a quarter of the exponentials are therefore computed on the FMA pipe (poly_exp2_pair).
 #include "f3d_common.cuh"
 #include "tc_sm100.cuh"
 #include "../../include/f3d_b200.h"
@@ -30,17 +34,13 @@ namespace f3d {
 
 int *status_word(int device);
 
-constexpr int kAttnThreads = 192;
-constexpr int kBQ = 128;      // query rows per CTA
+constexpr int kBQ = 128;      // query rows per tile
 constexpr int kBKV = 64;      // keys per tile
 constexpr int kKvStages = 4;
-// The producer runs three stages ahead of the MMAs; sleeping between its polls costs nothing and leaves the
-// issue slots to the softmax warps.
-constexpr uint32_t kProducerSleepNs = 500;
 
 struct AttnFwdArgs {
   __nv_bfloat16 *O; float *lse; const uint32_t *scopes;
-  int B, L, H, num_scopes, k, bucket, q_blocks_per_bucket;
+  int B, L, H, num_scopes, k, bucket, q_blocks_per_bucket;   // q_blocks_per_bucket = bucket / 128
   float scale_log2;          // log2(e) / sqrt(D)
   int *status;
 };
@@ -75,59 +75,91 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
   return r;
 }
 
-template <int D, int BKV> struct AttnCfg {
+// 2^x for a pair of non-positive arguments on the FMA pipe instead of the special-function unit: n = round(x) by the
+// magic-number addition (the sum x + 1.5 * 2^23 carries n in its low mantissa bits), f = x - n in [-0.5, 0.5], a cubic
+// for 2^f (largest relative error 7.5e-5, against the 3.9e-3 of the bf16 rounding P gets anyway), and n added to the
+// exponent field with integer arithmetic.  The integer maximum keeps the result at 2^-126 or above (times the cubic),
+// so arguments far below the range of an fp32 exponent come out as tiny numbers instead of wrapping around.
+__device__ __forceinline__ void poly_exp2_pair(uint64_t x2, float &e0, float &e1) {
+  const uint64_t magic2 = pack2(12582912.f, 12582912.f), nmagic2 = pack2(-12582912.f, -12582912.f);
+  const uint64_t t2 = add2(x2, magic2);
+  const uint64_t u2 = add2(t2, nmagic2);                              // n as a float, exact
+  const uint64_t f2 = fma2(u2, pack2(-1.f, -1.f), x2);                // x - n
+  uint64_t p2 = fma2(pack2(0.055171459913253784f, 0.055171459913253784f), f2, pack2(0.2426108568906784f, 0.2426108568906784f));
+  p2 = fma2(p2, f2, pack2(0.6932609677314758f, 0.6932609677314758f));
+  p2 = fma2(p2, f2, pack2(0.9999281167984009f, 0.9999281167984009f));
+  float t0, t1, p0, p1;
+  unpack2(t2, t0, t1);
+  unpack2(p2, p0, p1);
+  const int lowest = 0x4B400000 - 126;                                // bits of 1.5 * 2^23 - 126
+  const int n0 = max(__float_as_int(t0), lowest), n1 = max(__float_as_int(t1), lowest);
+  e0 = __int_as_float(__float_as_int(p0) + (n0 << 23));               // the bits of 1.5 * 2^23 vanish in the shift
+  e1 = __int_as_float(__float_as_int(p1) + (n1 << 23));
+}
+
+template <int D, int BKV, int NQ> struct AttnCfg {
   static constexpr int DCH = D < 64 ? D : 64;       // columns per swizzled row
   static constexpr int NDCH = D / DCH;
   static constexpr int RB = DCH * 2;                // bytes per swizzled row
   static constexpr uint64_t SWZ = RB == 128 ? tc::kSwizzle128 : (RB == 64 ? tc::kSwizzle64 : tc::kSwizzle32);
-  static constexpr int kQBytes = kBQ * D * 2;
+  static constexpr int kQBytes = kBQ * D * 2;       // one Q tile
   static constexpr int kTileBytes = BKV * D * 2;    // one K or V tile
   static constexpr int kStageBytes = 2 * kTileBytes;
-  static constexpr int kSmem = kQBytes + kKvStages * kStageBytes + 256 + 1024;
-  // Tensor memory columns: S (fp32 scores, BKV), P (bf16 probabilities, two per column, BKV / 2), O (fp32, D).
-  // P has columns of its own so that the next tile's S = Q K^T can be issued as soon as the softmax warps have
-  // read S, while they are still computing P.
+  static constexpr int kSmem = NQ * kQBytes + kKvStages * kStageBytes + 512 + 1024;
+  static constexpr int kThreads = 32 + 128 * NQ;
+  // Tensor memory columns of one query tile: S (fp32 scores, BKV), P (bf16 probabilities, two per column, BKV / 2),
+  // O (fp32, D).  P has columns of its own so that the next tile's S = Q K^T can be issued as soon as the softmax
+  // warps have read S, while they are still computing P.
   static constexpr uint32_t kPCol = BKV;
   static constexpr uint32_t kOCol = BKV + BKV / 2;
-  static constexpr uint32_t kTmemCols = (kOCol + D) <= 128 ? 128u : 256u;
-  static constexpr int kMinCtas = D <= 32 ? 4 : 2;
+  static constexpr uint32_t kTileCols = (kOCol + D) <= 128 ? 128u : 256u;
+  static constexpr uint32_t kTmemCols = kTileCols * NQ;
+  static constexpr int kMinCtas = (512 / (int)kTmemCols) < 4 ? (512 / (int)kTmemCols) : 4;
+  static_assert(kTmemCols <= 512, "tensor memory holds 512 columns");
 };
 
-template <int D, int BKV>
-__global__ void __launch_bounds__(kAttnThreads, (AttnCfg<D, BKV>::kMinCtas))
+// POLY8: of every eight pairs of scores, this many take their exponential from poly_exp2_pair (FMA pipe) and the rest
+// from ex2.approx (special-function unit), so that both pipes work on every row.
+template <int D, int BKV, int NQ, int POLY8>
+__global__ void __launch_bounds__((AttnCfg<D, BKV, NQ>::kThreads), (AttnCfg<D, BKV, NQ>::kMinCtas))
 attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, AttnFwdArgs a) {
-  using C = AttnCfg<D, BKV>;
+  using C = AttnCfg<D, BKV, NQ>;
   extern __shared__ unsigned char smem_raw[];
   unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char *sq = smem;
-  unsigned char *skv = smem + C::kQBytes;
+  unsigned char *skv = smem + NQ * C::kQBytes;
   uint64_t *bars = reinterpret_cast<uint64_t *>(skv + kKvStages * C::kStageBytes);
-  uint64_t *q_full = bars, *kv_full = bars + 1, *kv_empty = kv_full + kKvStages, *s_full = kv_empty + kKvStages;
-  uint64_t *p_full = s_full + 1, *o_full = p_full + 1, *s_free = o_full + 1;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(s_free + 1);
+  uint64_t *q_full = bars, *kv_full = bars + 1;
+  uint64_t *s_full = kv_full + kKvStages, *p_full = s_full + NQ, *o_full = p_full + NQ, *s_free = o_full + NQ;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(s_free + NQ);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // which query block
-  const int qb_lin = blockIdx.x;
-  const int qb = qb_lin % a.q_blocks_per_bucket;
-  const int bj = (qb_lin / a.q_blocks_per_bucket) % a.k;
-  const int scope = qb_lin / (a.q_blocks_per_bucket * a.k);
+  // which group of NQ query tiles: tiles of a scope are numbered in scope order, bucket slot major
+  const int tiles_per_scope = a.k * a.q_blocks_per_bucket;
+  const int groups_per_scope = tiles_per_scope / NQ;
+  const int scope = blockIdx.x / groups_per_scope;
+  const int tile0 = (blockIdx.x % groups_per_scope) * NQ;
   const int head = blockIdx.y, brow = blockIdx.z;
   const uint32_t *my_scope = a.scopes + (size_t)scope * a.k;
   const int tiles_per_bucket = a.bucket / BKV;
   const int num_tiles = a.k * tiles_per_bucket;
-  const int q_tok = (int)my_scope[bj] * a.bucket + qb * kBQ;      // first query token (inside batch row)
+  auto q_token = [&](int t) -> int {                    // first query token of tile t of this CTA (inside batch row)
+    const int ti = tile0 + t;
+    return (int)my_scope[ti / a.q_blocks_per_bucket] * a.bucket + (ti % a.q_blocks_per_bucket) * kBQ;
+  };
 
   if (threadIdx.x == 0) {
     tc::mbar_init(q_full, 1);
-    for (int s = 0; s < kKvStages; ++s) { tc::mbar_init(&kv_full[s], 1); tc::mbar_init(&kv_empty[s], 1); }
-    tc::mbar_init(s_full, 1); tc::mbar_init(p_full, 128); tc::mbar_init(o_full, 1); tc::mbar_init(s_free, 128);
+    for (int s = 0; s < kKvStages; ++s) tc::mbar_init(&kv_full[s], 1);
+    for (int t = 0; t < NQ; ++t) {
+      tc::mbar_init(&s_full[t], 1); tc::mbar_init(&p_full[t], 128); tc::mbar_init(&o_full[t], 1); tc::mbar_init(&s_free[t], 128);
+    }
     *abort_flag = 0;
     tc::mbar_fence_init();
   }
-  if (warp == 1) { tc::tmem_alloc(tmem_slot, C::kTmemCols); tc::tmem_relinquish(); }
+  if (warp == 0) { tc::tmem_alloc(tmem_slot, C::kTmemCols); tc::tmem_relinquish(); }
   tc::tc_fence_before_sync();
   __syncthreads();
   tc::tc_fence_after_sync();
@@ -137,14 +169,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   if (warp == 0) {
     if (tc::elect_one()) {
       tc::tma_prefetch_desc(&map_q); tc::tma_prefetch_desc(&map_k); tc::tma_prefetch_desc(&map_v);
-      tc::mbar_expect_tx(q_full, C::kQBytes);
+      tc::mbar_expect_tx(q_full, NQ * C::kQBytes);
 #pragma unroll
-      for (int c = 0; c < C::NDCH; ++c)
-        tc::tma_load_3d(sq + c * kBQ * C::RB, &map_q, q_full, c * C::DCH, head, brow * a.L + q_tok);
-      for (int j = 0; j < num_tiles; ++j) {
+      for (int t = 0; t < NQ; ++t)
+#pragma unroll
+        for (int c = 0; c < C::NDCH; ++c)
+          tc::tma_load_3d(sq + t * C::kQBytes + c * kBQ * C::RB, &map_q, q_full, c * C::DCH, head, brow * a.L + q_token(t));
+      auto load_kv = [&](int j) {
         const int s = j % kKvStages;
-        const uint32_t ph = (uint32_t)(j / kKvStages) & 1u;
-        if (!tc::mbar_wait(&kv_empty[s], ph ^ 1u, wc, 201, kProducerSleepNs)) break;
         const int key_tok = (int)my_scope[j / tiles_per_bucket] * a.bucket + (j % tiles_per_bucket) * BKV;
         unsigned char *sk = skv + s * C::kStageBytes, *sv = sk + C::kTileBytes;
         tc::mbar_expect_tx(&kv_full[s], C::kStageBytes);
@@ -153,76 +185,91 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           tc::tma_load_3d(sk + c * BKV * C::RB, &map_k, &kv_full[s], c * C::DCH, head, brow * a.L + key_tok);
           tc::tma_load_3d(sv + c * BKV * C::RB, &map_v, &kv_full[s], c * C::DCH, head, brow * a.L + key_tok);
         }
-      }
-    }
-  } else if (warp == 1) {
-    if (tc::elect_one()) {
+      };
+      for (int j = 0; j < kKvStages && j < num_tiles; ++j) load_kv(j);
+
       constexpr uint32_t idesc_s = tc::make_idesc_f16(kBQ, BKV, true, false, false);
       constexpr uint32_t idesc_o = tc::make_idesc_f16(kBQ, C::DCH, true, false, true);    // B (= V) is MN-major
-      const uint32_t s_tmem = tmem_base, p_tmem = tmem_base + C::kPCol, o_tmem = tmem_base + C::kOCol;
       const uint32_t q_addr = tc::smem_u32(sq);
-      // S_t = Q K_t^T: K-major operands, 8-row groups are 8*RB bytes apart
-      auto issue_s = [&](int t) -> bool {
-        const int s = t % kKvStages;
-        if (!tc::mbar_wait(&kv_full[s], (uint32_t)(t / kKvStages) & 1u, wc, 203)) return false;
-        tc::tc_fence_after_sync();
-        const uint32_t k_addr = tc::smem_u32(skv + s * C::kStageBytes);
+      // S_t = Q_t K^T of key tile j: K-major operands, 8-row groups are 8*RB bytes apart
+      auto issue_s = [&](int t, int j) {
+        const uint32_t k_addr = tc::smem_u32(skv + (j % kKvStages) * C::kStageBytes);
+        const uint32_t s_tmem = tmem_base + t * C::kTileCols;
 #pragma unroll
         for (int c = 0; c < C::NDCH; ++c) {
 #pragma unroll
           for (int kk = 0; kk < C::DCH / 16; ++kk) {
-            uint64_t ad = tc::make_smem_desc(q_addr + c * kBQ * C::RB + kk * 32, 16, 8 * C::RB, C::SWZ);
+            uint64_t ad = tc::make_smem_desc(q_addr + t * C::kQBytes + c * kBQ * C::RB + kk * 32, 16, 8 * C::RB, C::SWZ);
             uint64_t bd = tc::make_smem_desc(k_addr + c * BKV * C::RB + kk * 32, 16, 8 * C::RB, C::SWZ);
             tc::mma_f16_ss(s_tmem, ad, bd, idesc_s, (c | kk) != 0 ? 1u : 0u);
           }
         }
-        tc::mma_commit(s_full);
-        return true;
+        tc::mma_commit(&s_full[t]);
       };
-      bool ok = tc::mbar_wait(q_full, 0, wc, 202) && issue_s(0);
+      bool ok = tc::mbar_wait(q_full, 0, wc, 202) && tc::mbar_wait(&kv_full[0], 0, wc, 203);
+      if (ok) {
+        tc::tc_fence_after_sync();
+#pragma unroll
+        for (int t = 0; t < NQ; ++t) issue_s(t, 0);
+      }
       for (int j = 0; j < num_tiles && ok; ++j) {
         const int s = j % kKvStages;
         if (j + 1 < num_tiles) {
-          // the next scores may overwrite S once every softmax thread has read tile j
-          if (!tc::mbar_wait(s_free, (uint32_t)j & 1u, wc, 208)) { ok = false; break; }
-          if (!issue_s(j + 1)) { ok = false; break; }
+          if (!tc::mbar_wait(&kv_full[(j + 1) % kKvStages], (uint32_t)((j + 1) / kKvStages) & 1u, wc, 203)) { ok = false; break; }
+#pragma unroll
+          for (int t = 0; t < NQ; ++t) {
+            // the next scores may overwrite S once every softmax thread of the tile has read key tile j
+            if (!tc::mbar_wait(&s_free[t], (uint32_t)j & 1u, wc, 208)) { ok = false; break; }
+            tc::tc_fence_after_sync();
+            issue_s(t, j + 1);
+          }
+          if (!ok) break;
         }
-        // O += P V once the softmax warps have written P
-        if (!tc::mbar_wait(p_full, (uint32_t)j & 1u, wc, 204)) { ok = false; break; }
-        tc::tc_fence_after_sync();
         const uint32_t v_addr = tc::smem_u32(skv + s * C::kStageBytes) + C::kTileBytes;
 #pragma unroll
-        for (int c = 0; c < C::NDCH; ++c) {
+        for (int t = 0; t < NQ; ++t) {
+          // O_t += P_t V once the softmax warps of the tile have written P
+          if (!tc::mbar_wait(&p_full[t], (uint32_t)j & 1u, wc, 204)) { ok = false; break; }
+          tc::tc_fence_after_sync();
+          const uint32_t p_tmem = tmem_base + t * C::kTileCols + C::kPCol, o_tmem = tmem_base + t * C::kTileCols + C::kOCol;
 #pragma unroll
-          for (int kk = 0; kk < BKV / 16; ++kk) {
-            // 16 keys per MMA: V rows kk*16.. ; P columns kk*8.. (two bf16 per 32-bit column)
-            uint64_t bd = tc::make_smem_desc(v_addr + c * BKV * C::RB + kk * 16 * C::RB, 16, 8 * C::RB, C::SWZ);
-            tc::mma_f16_ts(o_tmem + c * C::DCH, p_tmem + kk * 8, bd, idesc_o, (j | kk) != 0 ? 1u : 0u);
+          for (int c = 0; c < C::NDCH; ++c) {
+#pragma unroll
+            for (int kk = 0; kk < BKV / 16; ++kk) {
+              // 16 keys per MMA: V rows kk*16.. ; P columns kk*8.. (two bf16 per 32-bit column)
+              uint64_t bd = tc::make_smem_desc(v_addr + c * BKV * C::RB + kk * 16 * C::RB, 16, 8 * C::RB, C::SWZ);
+              tc::mma_f16_ts(o_tmem + c * C::DCH, p_tmem + kk * 8, bd, idesc_o, (j | kk) != 0 ? 1u : 0u);
+            }
           }
+          tc::mma_commit(&o_full[t]);
         }
-        tc::mma_commit(&kv_empty[s]);
-        tc::mma_commit(o_full);
+        if (!ok) break;
+        // every tile has delivered P(j), so every tile had seen O complete up to key tile j-1: stage (j-1) % 4 is free
+        if (j >= 1 && j + kKvStages - 1 < num_tiles) load_kv(j + kKvStages - 1);
       }
     }
   } else {
-    const int q = warp & 3;
-    const int row = q * 32 + lane;                              // query row inside the tile = tensor-memory lane
+    const int t = (warp - 1) >> 2;                               // query tile of this warp
+    const int q = warp & 3;                                      // tensor-memory lane quarter this warp may access
+    const int row = q * 32 + lane;                               // query row inside the tile = tensor-memory lane
+    const int q_tok = q_token(t);
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
-    const uint32_t s_tmem = tmem_base + lane_off, p_tmem = tmem_base + C::kPCol + lane_off;
-    const uint32_t o_tmem = tmem_base + C::kOCol + lane_off;
+    const uint32_t tile_tmem = tmem_base + t * C::kTileCols + lane_off;
+    const uint32_t s_tmem = tile_tmem, p_tmem = tile_tmem + C::kPCol, o_tmem = tile_tmem + C::kOCol;
+    uint64_t *my_s_full = &s_full[t], *my_s_free = &s_free[t], *my_p_full = &p_full[t], *my_o_full = &o_full[t];
     float m_run = -INFINITY, l_run = 0.f;
     const uint64_t c2 = pack2(a.scale_log2, a.scale_log2);
     bool ok = true;
     for (int j = 0; j < num_tiles && ok; ++j) {
-      if (!tc::mbar_wait(s_full, (uint32_t)j & 1u, wc, 205)) { ok = false; break; }
+      if (!tc::mbar_wait(my_s_full, (uint32_t)j & 1u, wc, 205)) { ok = false; break; }
       tc::tc_fence_after_sync();
       uint32_t r0[32], r1[32];
       tc::tmem_ld_32x32b_x32(s_tmem, r0);
       tc::tmem_ld_32x32b_x32(s_tmem + 32, r1);
       tc::tmem_ld_wait();
-      // the scores are in registers: the MMA warp may start the next tile's Q K^T over them
+      // the scores are in registers: the next key tile's Q K^T may be issued over them
       tc::tc_fence_before_sync();
-      tc::mbar_arrive(s_free);
+      tc::mbar_arrive(my_s_free);
       // four independent chains of 3-input maxima instead of one 32 deep
       float mxa = -INFINITY, mxb = -INFINITY, mxc = -INFINITY, mxd = -INFINITY;
 #pragma unroll
@@ -243,25 +290,35 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
         const uint64_t xx = fma2(pack2(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1])), c2, m2);
-        float x0, x1;
-        unpack2(xx, x0, x1);
-        const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
+        float e0, e1;
+        if ((i & 7) < POLY8) {
+          poly_exp2_pair(xx, e0, e1);
+        } else {
+          float x0, x1;
+          unpack2(xx, x0, x1);
+          e0 = fast_exp2(x0); e1 = fast_exp2(x1);
+        }
         sum2 = add2(sum2, pack2(e0, e1));
         __nv_bfloat162 hh = __floats2bfloat162_rn(e0, e1);
         p[i] = *reinterpret_cast<uint32_t *>(&hh);
       }
       if (j > 0) {
         // P of the previous tile has been consumed and O is complete up to it: P may be overwritten, O rescaled
-        if (!tc::mbar_wait(o_full, (uint32_t)(j - 1) & 1u, wc, 206)) { ok = false; break; }
+        if (!tc::mbar_wait(my_o_full, (uint32_t)(j - 1) & 1u, wc, 206)) { ok = false; break; }
         tc::tc_fence_after_sync();
       }
       tc::tmem_st_32x32b_x16(p_tmem, p);
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
         const uint64_t xx = fma2(pack2(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1])), c2, m2);
-        float x0, x1;
-        unpack2(xx, x0, x1);
-        const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
+        float e0, e1;
+        if ((i & 7) < POLY8) {
+          poly_exp2_pair(xx, e0, e1);
+        } else {
+          float x0, x1;
+          unpack2(xx, x0, x1);
+          e0 = fast_exp2(x0); e1 = fast_exp2(x1);
+        }
         sum2 = add2(sum2, pack2(e0, e1));
         __nv_bfloat162 hh = __floats2bfloat162_rn(e0, e1);
         p[i] = *reinterpret_cast<uint32_t *>(&hh);
@@ -285,9 +342,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       }
       tc::tmem_st_wait();
       tc::tc_fence_before_sync();
-      tc::mbar_arrive(p_full);
+      tc::mbar_arrive(my_p_full);
     }
-    if (ok && tc::mbar_wait(o_full, (uint32_t)(num_tiles - 1) & 1u, wc, 207) && q_tok + row < a.L) {
+    if (ok && tc::mbar_wait(my_o_full, (uint32_t)(num_tiles - 1) & 1u, wc, 207) && q_tok + row < a.L) {
       tc::tc_fence_after_sync();
       const float inv = 1.f / l_run;
       const size_t tok = (size_t)brow * a.L + q_tok + row;
@@ -314,13 +371,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
     __syncthreads();
   }
-  if (warp == 1) { tc::tc_fence_after_sync(); tc::tmem_dealloc(tmem_base, C::kTmemCols); }
+  if (warp == 0) { tc::tc_fence_after_sync(); tc::tmem_dealloc(tmem_base, C::kTmemCols); }
 }
 
-template <int D, int BKV>
+template <int D, int BKV, int NQ, int POLY8 = 0>
 static int launch_attn_fwd(const void *Q, const void *K, const void *V, AttnFwdArgs a, int device, cudaStream_t st) {
-  using C = AttnCfg<D, BKV>;
-  auto kern = attn_fwd_kernel<D, BKV>;
+  using C = AttnCfg<D, BKV, NQ>;
+  auto kern = attn_fwd_kernel<D, BKV, NQ, POLY8>;
   F3D_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(kern), device, C::kSmem));
   CUtensorMap mq, mk, mv;
   const uint64_t rows = (uint64_t)a.B * a.L;
@@ -328,9 +385,18 @@ static int launch_attn_fwd(const void *Q, const void *K, const void *V, AttnFwdA
   F3D_TRY(encode_tmap_3d(&mq, 0, Q, D, a.H, rows, s1, s2, C::DCH, 1, kBQ, C::RB));
   F3D_TRY(encode_tmap_3d(&mk, 0, K, D, a.H, rows, s1, s2, C::DCH, 1, BKV, C::RB));
   F3D_TRY(encode_tmap_3d(&mv, 0, V, D, a.H, rows, s1, s2, C::DCH, 1, BKV, C::RB));
-  dim3 grid(a.num_scopes * a.k * a.q_blocks_per_bucket, a.H, a.B);
-  kern<<<grid, kAttnThreads, C::kSmem, st>>>(mq, mk, mv, a);
+  dim3 grid(a.num_scopes * (a.k * a.q_blocks_per_bucket / NQ), a.H, a.B);
+  kern<<<grid, C::kThreads, C::kSmem, st>>>(mq, mk, mv, a);
   return check_launch("buck_swin_fwd");
+}
+
+// Head sizes up to 32 are bound by the special-function unit: a quarter of their exponentials go to the FMA pipe
+// (measured at D = 32, window 4096: 0 / 12.5 / 25 / 37.5 / 50 % -> 439 / 448 / 462 / 446 / 413 TFLOP/s; beyond a quarter
+// the extra instructions cost more issue slots than the special-function slots they free).  One query tile per CTA:
+// two and four tiles per CTA sharing the K/V stream measured 2 % and 4 % slower (their exponential phases line up).
+template <int D>
+static int launch_attn_fwd_small(const void *Q, const void *K, const void *V, AttnFwdArgs a, int device, cudaStream_t st) {
+  return launch_attn_fwd<D, 64, 1, 2>(Q, K, V, a, device, st);
 }
 
 }  // namespace f3d
@@ -356,10 +422,10 @@ extern "C" int f3d_buck_swin_fwd(const void *Q, const void *K, const void *V, vo
   if (!a.status) return F3D_ERR_CUDA;
   int rc;
   switch (D) {
-    case 16: rc = launch_attn_fwd<16, 64>(Q, K, V, a, device, st); break;
-    case 32: rc = launch_attn_fwd<32, 64>(Q, K, V, a, device, st); break;
-    case 64: rc = launch_attn_fwd<64, 64>(Q, K, V, a, device, st); break;
-    default: rc = launch_attn_fwd<128, 64>(Q, K, V, a, device, st); break;
+    case 16: rc = launch_attn_fwd_small<16>(Q, K, V, a, device, st); break;
+    case 32: rc = launch_attn_fwd_small<32>(Q, K, V, a, device, st); break;
+    case 64: rc = launch_attn_fwd<64, 64, 1>(Q, K, V, a, device, st); break;
+    default: rc = launch_attn_fwd<128, 64, 1>(Q, K, V, a, device, st); break;
   }
   F3D_TRY(rc);
   return maybe_sync(st, "buck_swin_fwd");

@@ -26,9 +26,14 @@
 //            Arrivals on bucket c are ranked by input index and appended after round B's content of c.
 //
 // Each round is "tile histogram -> per-scene scan over tiles -> tile rank", so a point's rank needs no atomics
-// on global memory and no inter-CTA waiting.  Warps own contiguous index ranges; equal keys inside a warp are
-// merged with match_any (warp-aggregated counting), per-warp counters live in shared memory, and coordinates
-// are staged into shared memory with 128-bit loads.
+// on global memory and no inter-CTA waiting: seven launches (key + histogram, scan, round A ranks + probe walk, scan,
+// round B resolution, scan, round C ranks + scatter) over tiles of 2048 points, so that even one scan of 120,000
+// points spreads over 59 CTAs and a batch fills every SM.  The first-hash key of a point is computed once (kernel 1)
+// and kept as 16 bits in scratch; the rank kernels read keys, not coordinates.  The scan kernel turns a round's table
+// of per-tile counts into per-tile exclusive prefixes in place, one warp per (scene, bucket) column, and writes the
+// scene totals.  Warps own contiguous index ranges; equal keys inside a warp are merged with match_any
+// (warp-aggregated counting), per-warp counters live in shared memory, and coordinates are staged into shared memory
+// with 128-bit loads where they are needed (kernel 1, the probe walk of overflowing points, the scatter).
 #include "f3d_common.cuh"
 #include <map>
 #include <mutex>
@@ -44,7 +49,23 @@ constexpr int kPshThreads = 256;
 constexpr int kPshWarps = kPshThreads / 32;
 constexpr uint32_t kGroup = 256;            // points one warp stages at a time
 constexpr uint32_t kStageHalves = kGroup * 3 + 16;   // staged halves + room for the 16-byte alignment skew
+constexpr uint32_t kMinTile = 2048;
 constexpr uint32_t kMaxTile = 16384;
+
+// Jump constants of the probe streams, s_n = A^n s_0 + C_n (mod 2^32) for the linear congruential step
+// s <- 1664525 s + 1013904223: entry n - 1 holds (A^n, C_n), n = 1 .. 128, evaluated at compile time.
+struct LcgJumps { uint32_t a[kNumProbes], c[kNumProbes]; };
+constexpr LcgJumps make_lcg_jumps() {
+  LcgJumps j{};
+  uint32_t pa = 1u, pc = 0u;
+  for (uint32_t n = 0; n < kNumProbes; ++n) {
+    pa *= 1664525u;
+    pc = pc * 1664525u + 1013904223u;
+    j.a[n] = pa; j.c[n] = pc;
+  }
+  return j;
+}
+__constant__ LcgJumps g_lcg_jumps = make_lcg_jumps();
 
 struct PshArgs {
   const __half *coord; uint16_t *bucket_id; uint32_t *bucket_counter; uint32_t *bucket_offset;
@@ -52,13 +73,18 @@ struct PshArgs {
   const __half *bbox_min; const __half *bbox_max; const int16_t *probe;
   uint32_t total_N, batch, nb, nbp, divisor, cap, num_vox, hash_type, pad_to;
   uint32_t tile, tiles_max;
-  uint16_t pad_bits; uint16_t coord_aligned;
+  uint16_t pad_bits; uint16_t coord_aligned; uint16_t out_aligned;
   RngKey key;
   uint32_t scene_base;     // added to the scene index in the random-number counter (global scene id of a shard)
   // scratch
-  uint32_t *tabA, *tabB, *tabC;    // [batch*tiles_max][nbp] tile histograms of rounds A, B, C (raw counts)
-  uint32_t *count0, *kept, *cntB;  // [batch][nbp] per-scene totals published by the tile-0 CTA of each round
+  uint32_t *tabA, *tabB, *tabC;    // [batch][nbp][tiles_max] tile tables of rounds A, B, C: raw counts, then (after the
+                                   // round's scan) the exclusive prefix over the scene's earlier tiles.  A (scene,
+                                   // bucket) column is contiguous, so the scan reads and writes whole lines; the
+                                   // tile kernels touch one word per column
+  uint32_t *count0, *kept, *cntB;  // [batch][nbp] first-hash totals, kept counts, counts after round B
+  uint32_t *attB, *movC;           // [batch][nbp] scene totals of the round B attempts and the round C movers
   uint32_t *tile_pending, *tile_movers;                     // [batch*tiles_max]
+  uint16_t *keys;                  // [total_N] first-hash key of every point
 };
 
 // ---------------------------------------------------------------------------------------------------------
@@ -70,6 +96,7 @@ struct TileSmem {
   uint32_t *aux;       // [nbp]              block histogram of the next round / cached per-scene table
   uint32_t *aux2;      // [nbp]              second cached per-scene table
   uint32_t *aux3;      // [nbp]              third cached per-scene table
+  uint32_t *aux4;      // [nbp]              this tile's histogram of the next round (flushed with plain stores)
   uint16_t *keys;      // [tile]             key cache between the counting and the ranking sweep
 };
 
@@ -77,7 +104,7 @@ __host__ __device__ inline size_t tile_smem_bytes(uint32_t nbp, uint32_t tile) {
   size_t b = 0;
   b += (size_t)kPshWarps * kStageHalves * 2;
   b += ((size_t)kPshWarps * nbp * 2 + 15) / 16 * 16;
-  b += (size_t)nbp * 4 * 4;
+  b += (size_t)nbp * 4 * 5;
   b += (size_t)tile * 2;
   return b + 64;
 }
@@ -95,6 +122,8 @@ __device__ __forceinline__ TileSmem carve(unsigned char *base, uint32_t nbp, uin
   s.aux2 = reinterpret_cast<uint32_t *>(base);
   base += (size_t)nbp * 4;
   s.aux3 = reinterpret_cast<uint32_t *>(base);
+  base += (size_t)nbp * 4;
+  s.aux4 = reinterpret_cast<uint32_t *>(base);
   base += (size_t)nbp * 4;
   s.keys = reinterpret_cast<uint16_t *>(base);
   return s;
@@ -127,21 +156,23 @@ __device__ __forceinline__ uint32_t warp_stage(const PshArgs &a, uint32_t g, uin
   return 0u;
 }
 
-__device__ __forceinline__ void load_vox(const PshArgs &a, const uint16_t *st, uint32_t skew, uint32_t k,
-                                         const float (&lo)[3], const float (&hi)[3], uint32_t (&vox)[3]) {
+__device__ __forceinline__ void load_vox(const uint16_t *st, uint32_t skew, uint32_t k, const AxisScale (&ax)[3],
+                                         uint32_t (&vox)[3]) {
 #pragma unroll
-  for (int d = 0; d < 3; ++d) {
-    float c = __half2float(__ushort_as_half(st[skew + 3u * k + d]));
-    vox[d] = vox_axis(c, lo[d], hi[d], a.num_vox);
-  }
+  for (int d = 0; d < 3; ++d) vox[d] = vox_axis(__half2float(__ushort_as_half(st[skew + 3u * k + d])), ax[d]);
 }
 
-__device__ __forceinline__ void load_bbox(const PshArgs &a, float (&lo)[3], float (&hi)[3]) {
+__device__ __forceinline__ void load_axes(const PshArgs &a, AxisScale (&ax)[3]) {
 #pragma unroll
-  for (int d = 0; d < 3; ++d) { lo[d] = __half2float(a.bbox_min[d]); hi[d] = __half2float(a.bbox_max[d]); }
+  for (int d = 0; d < 3; ++d) ax[d] = make_axis_scale(__half2float(a.bbox_min[d]), __half2float(a.bbox_max[d]), a.num_vox);
 }
 
 struct TileInfo { uint32_t scene, tile, start, n, t0, cnt, row; bool live; };
+
+// word of a tile table for (scene, bucket column, tile)
+__device__ __forceinline__ size_t tab_at(const PshArgs &a, uint32_t scene, uint32_t col, uint32_t tile) {
+  return ((size_t)scene * a.nbp + col) * a.tiles_max + tile;
+}
 
 __device__ __forceinline__ TileInfo tile_info(const PshArgs &a) {
   TileInfo t;
@@ -192,25 +223,8 @@ __device__ __forceinline__ void warp_prefix(const TileSmem &s, uint32_t nbp) {
   }
 }
 
-// Column `col` of a scene's raw tile table: sum over the tiles before `my_tile` and over all tiles.  Every CTA of
-// a round recomputes these sums from the table (tiles <= 64 per scene by construction, all L2 hits) instead of
-// waiting for a separate scan launch.
-__device__ __forceinline__ void column_sums(const uint32_t *tab, uint32_t tiles, uint32_t nbp, uint32_t col, uint32_t my_tile,
-                                            uint32_t &prefix, uint32_t &total) {
-  uint32_t pre = 0, tot = 0, t = 0;
-  for (; t + 8 <= tiles; t += 8) {
-    uint32_t v[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] = __ldg(tab + (size_t)(t + j) * nbp + col);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) { tot += v[j]; if (t + j < my_tile) pre += v[j]; }
-  }
-  for (; t < tiles; ++t) { uint32_t v = __ldg(tab + (size_t)t * nbp + col); tot += v; if (t < my_tile) pre += v; }
-  prefix = pre; total = tot;
-}
-
 // ---------------------------------------------------------------------------------------------------------
-// K1: first-hash histogram of every tile
+// K1: first-hash key of every point (kept in scratch) and the key histogram of every tile
 __global__ void __launch_bounds__(kPshThreads) psh_hist_kernel(PshArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   TileSmem s = carve(smem_raw, a.nbp, 0);
@@ -219,11 +233,13 @@ __global__ void __launch_bounds__(kPshThreads) psh_hist_kernel(PshArgs a) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (uint32_t b = threadIdx.x; b < a.nbp; b += kPshThreads) s.aux[b] = 0;
   __syncthreads();
-  float lo[3], hi[3];
-  load_bbox(a, lo, hi);
+  AxisScale ax[3];
+  load_axes(a, ax);
+  const HashPlan hp = make_hash_plan(a.hash_type, a.divisor, a.nb);
   const uint32_t wt = a.tile / kPshWarps;
   const uint32_t w0 = warp * wt, w1 = min(w0 + wt, t.cnt);
   uint16_t *st = s.stage + warp * kStageHalves;
+  uint16_t *keys = a.keys + t.start + t.t0;
   for (uint32_t g = w0; g < w1; g += kGroup) {
     uint32_t gc = min(kGroup, w1 - g);
     uint32_t skew = warp_stage(a, t.start + t.t0 + g, gc, st, lane);
@@ -233,16 +249,16 @@ __global__ void __launch_bounds__(kPshThreads) psh_hist_kernel(PshArgs a) {
       uint32_t key = 0;
       if (valid) {
         uint32_t vox[3];
-        load_vox(a, st, skew, k, lo, hi, vox);
-        key = first_hash(a.hash_type, vox[0], vox[1], vox[2], a.divisor, a.nb);
+        load_vox(st, skew, k, ax, vox);
+        key = first_hash(hp, vox[0], vox[1], vox[2]);
+        keys[g + k] = (uint16_t)key;
       }
       uint32_t peers = __match_any_sync(0xFFFFFFFFu, valid ? key : 0xFFFFFFFFu);
       if (valid && (__ffs(peers) - 1) == lane) atomicAdd(&s.aux[key], (uint32_t)__popc(peers));
     }
   }
   __syncthreads();
-  uint32_t *row = a.tabA + (size_t)t.row * a.nbp;
-  for (uint32_t b = threadIdx.x; b < a.nbp; b += kPshThreads) row[b] = s.aux[b];
+  for (uint32_t b = threadIdx.x; b < a.nbp; b += kPshThreads) a.tabA[tab_at(a, t.scene, b, t.tile)] = s.aux[b];
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -277,6 +293,42 @@ __device__ __forceinline__ uint32_t scene_tiles(const PshArgs &a, uint32_t scene
 }
 
 // ---------------------------------------------------------------------------------------------------------
+// Scan of one round's tile table: a warp owns one (scene, bucket) column, turns the per-tile counts into exclusive
+// prefixes over the scene's tiles in place (32 tiles per step, warp shuffle scan) and writes the column total.
+// which = 0: round A (totals -> count0, kept), 1: round B attempts (-> attB), 2: round C movers (-> movC).
+__global__ void __launch_bounds__(kPshThreads) psh_scan_kernel(PshArgs a, int which) {
+  const int lane = threadIdx.x & 31;
+  const uint32_t col_lin = blockIdx.x * kPshWarps + (threadIdx.x >> 5);
+  if (col_lin >= a.batch * a.nbp) return;
+  const uint32_t scene = col_lin / a.nbp, col = col_lin % a.nbp;
+  const uint32_t tiles = scene_tiles(a, scene);
+  uint32_t *tab = (which == 0 ? a.tabA : (which == 1 ? a.tabB : a.tabC)) + tab_at(a, scene, col, 0);
+  uint32_t run = 0;
+  for (uint32_t t0 = 0; t0 < tiles; t0 += 32) {
+    const uint32_t t = t0 + lane;
+    const uint32_t v = t < tiles ? tab[t] : 0u;
+    uint32_t inc = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const uint32_t o = __shfl_up_sync(0xFFFFFFFFu, inc, d);
+      if (lane >= d) inc += o;
+    }
+    if (t < tiles) tab[t] = run + inc - v;
+    run += __shfl_sync(0xFFFFFFFFu, inc, 31);
+  }
+  if (lane == 0) {
+    if (which == 0) {
+      a.count0[col_lin] = run;
+      a.kept[col_lin] = (col == kRecycleBucket) ? run : min(run, a.cap);
+    } else if (which == 1) {
+      a.attB[col_lin] = run;
+    } else {
+      a.movC[col_lin] = run;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
 // K3: round A ranks, overflow detection, probe walk, round B histogram
 __global__ void __launch_bounds__(kPshThreads) psh_rankA_kernel(PshArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -286,66 +338,60 @@ __global__ void __launch_bounds__(kPshThreads) psh_rankA_kernel(PshArgs a) {
   if (!t.live) return;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   zero_whist(s, a.nbp);
+  // rank base of this tile (the scanned round A table) and the scene's kept counts: requested first, so that their
+  // latency runs under the counting sweep
+  const uint32_t so = t.scene * a.nbp;
+  for (uint32_t b = threadIdx.x; b < a.nbp; b += kPshThreads) {
+    s.aux4[b] = 0;
+    s.tbase[b] = a.tabA[tab_at(a, t.scene, b, t.tile)];
+    s.aux[b] = a.kept[so + b];
+  }
   if (threadIdx.x == 0) pending_cnt = 0;
   __syncthreads();
-  float lo[3], hi[3];
-  load_bbox(a, lo, hi);
+  AxisScale ax[3];
+  load_axes(a, ax);
+  const HashPlan hp = make_hash_plan(a.hash_type, a.divisor, a.nb);
   const float ratio = probe_ratio(a.num_vox, a.divisor);
   // LCG jump constants of this lane for the warp-wide phase of the walk: probe kSoloProbes + 32 j + lane uses the
   // stream state n = 32 j + lane + 1 steps after the solo probes, s_n = A^n s_0 + C_n (mod 2^32), C_n = c (A^(n-1) + ... + 1)
   constexpr uint32_t kSoloProbes = 8;
   constexpr uint32_t kWarpBatches = (kNumProbes - kSoloProbes + 31) / 32;
   uint32_t jump_a[kWarpBatches], jump_c[kWarpBatches];
-  {
-    uint32_t pa = 1u, pc = 0u, n = 0;
 #pragma unroll
-    for (uint32_t j = 0; j < kWarpBatches; ++j) {
-      const uint32_t want = j * 32 + lane + 1;
-      for (; n < want; ++n) { pa *= 1664525u; pc = pc * 1664525u + 1013904223u; }
-      jump_a[j] = pa; jump_c[j] = pc;
-    }
+  for (uint32_t j = 0; j < kWarpBatches; ++j) {
+    jump_a[j] = g_lcg_jumps.a[j * 32 + lane];      // n = 32 j + lane + 1 steps
+    jump_c[j] = g_lcg_jumps.c[j * 32 + lane];
   }
   const uint32_t wt = a.tile / kPshWarps;
   const uint32_t w0 = warp * wt, w1 = min(w0 + wt, t.cnt);
   uint16_t *st = s.stage + warp * kStageHalves;
   uint16_t *wh = s.whist + warp * a.nbp;
-  // sweep 1: keys and per-warp counts
+  // sweep 1: the keys kernel 1 left in scratch (a whole group of loads in flight) and per-warp counts
+  const uint16_t *gkeys = a.keys + t.start + t.t0;
   for (uint32_t g = w0; g < w1; g += kGroup) {
     uint32_t gc = min(kGroup, w1 - g);
-    uint32_t skew = warp_stage(a, t.start + t.t0 + g, gc, st, lane);
-    for (uint32_t it = 0; it < gc; it += 32) {
-      uint32_t k = it + lane;
-      bool valid = k < gc;
-      uint32_t key = 0;
-      if (valid) {
-        uint32_t vox[3];
-        load_vox(a, st, skew, k, lo, hi, vox);
-        key = first_hash(a.hash_type, vox[0], vox[1], vox[2], a.divisor, a.nb);
-        s.keys[g + k] = (uint16_t)key;
-      }
-      warp_count(wh, key, valid, lane);
+    constexpr int kBatches = kGroup / 32;
+    uint32_t kk[kBatches];
+#pragma unroll
+    for (int u = 0; u < kBatches; ++u) {
+      const uint32_t k = u * 32 + lane;
+      kk[u] = k < gc ? (uint32_t)gkeys[g + k] : 0u;
+    }
+#pragma unroll
+    for (int u = 0; u < kBatches; ++u) {
+      if ((uint32_t)u * 32 >= gc) break;
+      const uint32_t k = u * 32 + lane;
+      const bool valid = k < gc;
+      if (valid) s.keys[g + k] = (uint16_t)kk[u];
+      warp_count(wh, kk[u], valid, lane);
     }
   }
   __syncthreads();
   warp_prefix(s, a.nbp);
-  // rank base of this tile and the scene's kept counts, from the round A table
-  const uint32_t so = t.scene * a.nbp;
-  {
-    const uint32_t tiles = scene_tiles(a, t.scene);
-    const uint32_t *tab = a.tabA + (size_t)t.scene * a.tiles_max * a.nbp;
-    for (uint32_t b = threadIdx.x; b < a.nbp; b += kPshThreads) {
-      uint32_t pre, tot;
-      column_sums(tab, tiles, a.nbp, b, t.tile, pre, tot);
-      const uint32_t kept = (b == kRecycleBucket) ? tot : min(tot, a.cap);
-      s.tbase[b] = pre;
-      s.aux[b] = kept;
-      if (t.tile == 0) { a.count0[so + b] = tot; a.kept[so + b] = kept; }
-    }
-  }
   __syncthreads();
-  // sweep 2: ranks; overflowing points choose their attempt bucket and are counted into the round B table,
-  // whose row is accumulated with global atomics (rare path) after being zeroed by the host memset.
-  uint32_t *rowB = a.tabB + (size_t)t.row * a.nbp;
+  // sweep 2: ranks; overflowing points choose their attempt bucket and are counted into this tile's round B
+  // histogram in shared memory; the tile owns its word of every column of the round B table and writes the non-zero
+  // ones with plain stores at the end (the table was zeroed by the host memset).
   uint32_t my_pending = 0;
   for (uint32_t g = w0; g < w1; g += kGroup) {
     uint32_t gc = min(kGroup, w1 - g);
@@ -386,13 +432,13 @@ __global__ void __launch_bounds__(kPshThreads) psh_rankA_kernel(PshArgs a) {
       uint32_t found = a.nb;                           // a.nb = "no admissible probe" column
       bool open = marked;
       if (marked) {
-        load_vox(a, st, skew, k, lo, hi, vox);
+        load_vox(st, skew, k, ax, vox);
         probe_stream_init(a.key, t.scene + a.scene_base, pt, ps);
         uint32_t r[4], nvox[3];
         for (uint32_t p = 0; p < kSoloProbes; ++p) {
           probe_stream_next(ps, r);
           perturb_vox(r, a.num_vox, ratio, a.probe + 3u * p, vox, nvox);
-          const uint32_t c = first_hash(a.hash_type, nvox[0], nvox[1], nvox[2], a.divisor, a.nb);
+          const uint32_t c = first_hash(hp, nvox[0], nvox[1], nvox[2]);
           if (c != init && c != kRecycleBucket && s.aux[c] < a.cap) { found = c; open = false; break; }
         }
       }
@@ -419,7 +465,7 @@ __global__ void __launch_bounds__(kPshThreads) psh_rankA_kernel(PshArgs a) {
           uint32_t c = 0;
           if (p < kNumProbes) {
             perturb_vox(r, a.num_vox, ratio, a.probe + 3u * p, bvox, nvox);
-            c = first_hash(a.hash_type, nvox[0], nvox[1], nvox[2], a.divisor, a.nb);
+            c = first_hash(hp, nvox[0], nvox[1], nvox[2]);
             ok = c != binit && c != kRecycleBucket && s.aux[c] < a.cap;
           }
           const uint32_t hit = __ballot_sync(0xFFFFFFFFu, ok);
@@ -434,7 +480,7 @@ __global__ void __launch_bounds__(kPshThreads) psh_rankA_kernel(PshArgs a) {
         uint32_t gi = t.start + pt;
         a.bucket_id[gi] = (uint16_t)found;
         a.bucket_offset[gi] = kPending;
-        atomicAdd(&rowB[found], 1u);
+        atomicAdd(&s.aux4[found], 1u);
         ++my_pending;
       }
     }
@@ -442,6 +488,11 @@ __global__ void __launch_bounds__(kPshThreads) psh_rankA_kernel(PshArgs a) {
   if (my_pending) atomicAdd(&pending_cnt, my_pending);
   __syncthreads();
   if (threadIdx.x == 0) a.tile_pending[t.row] = pending_cnt;
+  if (pending_cnt)
+    for (uint32_t b = threadIdx.x; b < a.nbp; b += kPshThreads) {
+      const uint32_t c = s.aux4[b];
+      if (c) a.tabB[tab_at(a, t.scene, b, t.tile)] = c;
+    }
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -464,15 +515,12 @@ __global__ void __launch_bounds__(kPshThreads) psh_resolveB_kernel(PshArgs a) {
   // kept count (aux2), recycle offset of the first rejected attempt per bucket (aux3).  The tile-0 CTA also
   // publishes the bucket counts after round B.
   {
-    const uint32_t tiles = scene_tiles(a, t.scene);
-    const uint32_t *tab = a.tabB + (size_t)t.scene * a.tiles_max * a.nbp;
     uint32_t carry = 0;
     for (uint32_t b0 = 0; b0 < a.nbp; b0 += kPshThreads) {
       const uint32_t b = b0 + threadIdx.x;
       uint32_t rej = 0;
       if (b < a.nbp) {
-        uint32_t pre, att;
-        column_sums(tab, tiles, a.nbp, b, t.tile, pre, att);
+        const uint32_t pre = a.tabB[tab_at(a, t.scene, b, t.tile)], att = a.attB[so + b];
         const uint32_t kept = a.kept[so + b];
         const uint32_t fr = (b != kRecycleBucket && b < a.nb && kept < a.cap) ? a.cap - kept : 0u;
         const uint32_t acc = min(att, fr);
@@ -492,6 +540,7 @@ __global__ void __launch_bounds__(kPshThreads) psh_resolveB_kernel(PshArgs a) {
     return;
   }
   zero_whist(s, a.nbp);
+  for (uint32_t b = threadIdx.x; b < a.nbp; b += kPshThreads) s.aux4[b] = 0;
   if (threadIdx.x == 0) mover_cnt = 0;
   __syncthreads();
   const uint32_t wt = a.tile / kPshWarps;
@@ -525,10 +574,10 @@ __global__ void __launch_bounds__(kPshThreads) psh_resolveB_kernel(PshArgs a) {
   __syncthreads();
   warp_prefix(s, a.nbp);
   __syncthreads();
-  float lo[3], hi[3];
-  load_bbox(a, lo, hi);
+  AxisScale ax[3];
+  load_axes(a, ax);
+  const HashPlan hp = make_hash_plan(a.hash_type, a.divisor, a.nb);
   const float ratio = probe_ratio(a.num_vox, a.divisor);
-  uint32_t *rowC = a.tabC + (size_t)t.row * a.nbp;
   const uint32_t count0_recycle = a.count0[so + kRecycleBucket];
   uint32_t my_movers = 0;
   for (uint32_t it = w0; it < w1; it += 32) {
@@ -562,25 +611,30 @@ __global__ void __launch_bounds__(kPshThreads) psh_resolveB_kernel(PshArgs a) {
       uint32_t pt = t.t0 + k;
       uint32_t vox[3], nvox[3], r[4];
 #pragma unroll
-      for (int d = 0; d < 3; ++d) vox[d] = vox_axis(__half2float(a.coord[(size_t)gi * 3 + d]), lo[d], hi[d], a.num_vox);
+      for (int d = 0; d < 3; ++d) vox[d] = vox_axis(__half2float(a.coord[(size_t)gi * 3 + d]), ax[d]);
       psh_rand(a.key, t.scene + a.scene_base, pt, 128u, r);
       uint32_t p = r[0] % kNumProbes;
       psh_rand(a.key, t.scene + a.scene_base, pt, 129u, r);
       perturb_vox(r, a.num_vox, ratio, a.probe + 3u * p, vox, nvox);
-      uint32_t c = first_hash(a.hash_type, nvox[0], nvox[1], nvox[2], a.divisor, a.nb);
+      uint32_t c = first_hash(hp, nvox[0], nvox[1], nvox[2]);
       if (c == kRecycleBucket) {
         psh_rand(a.key, t.scene + a.scene_base, pt, 130u, r);
         c = 1u + r[0] % (a.nb - 1u);
       }
       a.bucket_id[gi] = (uint16_t)c;
       a.bucket_offset[gi] = kPending;
-      atomicAdd(&rowC[c], 1u);
+      atomicAdd(&s.aux4[c], 1u);
       ++my_movers;
     }
   }
   if (my_movers) atomicAdd(&mover_cnt, my_movers);
   __syncthreads();
   if (threadIdx.x == 0) a.tile_movers[t.row] = mover_cnt;
+  if (mover_cnt)
+    for (uint32_t b = threadIdx.x; b < a.nbp; b += kPshThreads) {
+      const uint32_t c = s.aux4[b];
+      if (c) a.tabC[tab_at(a, t.scene, b, t.tile)] = c;
+    }
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -617,15 +671,12 @@ __global__ void __launch_bounds__(kPshThreads) psh_scatter_kernel(PshArgs a) {
   // Round C totals of the scene: final bucket sizes, their exclusive cumsum (aux = first row of each bucket inside
   // the scene) and the rank base of this tile's movers (tbase).  The tile-0 CTA writes the two counter outputs.
   {
-    const uint32_t tiles = scene_tiles(a, t.scene);
-    const uint32_t *tab = a.tabC + (size_t)t.scene * a.tiles_max * a.nbp;
     uint32_t carry = 0;
     for (uint32_t b0 = 0; b0 < a.nbp; b0 += kPshThreads) {
       const uint32_t b = b0 + threadIdx.x;
       uint32_t fin = 0;
       if (b < a.nbp) {
-        uint32_t pre, mv;
-        column_sums(tab, tiles, a.nbp, b, t.tile, pre, mv);
+        const uint32_t pre = a.tabC[tab_at(a, t.scene, b, t.tile)], mv = a.movC[so + b];
         const uint32_t cb = a.cntB[so + b];
         if (b == kRecycleBucket) fin = (a.nb > 1) ? min(cb, a.cap) : cb;
         else if (b < a.nb) fin = cb + mv;
@@ -688,9 +739,19 @@ __global__ void __launch_bounds__(kPshThreads) psh_scatter_kernel(PshArgs a) {
       if (inb) {
         uint64_t row = (uint64_t)t.start + s.aux[id] + off;
         if (row < a.pad_to) {
+          // a row is 6 bytes: 4-byte aligned when the row index is even, else at 2 mod 4
           uint16_t *d3 = dst + row * 3ull;
           const uint16_t *s3 = st + skew + 3u * k;
-          d3[0] = s3[0]; d3[1] = s3[1]; d3[2] = s3[2];
+          const uint32_t c0 = s3[0], c1 = s3[1], c2 = s3[2];
+          if (!a.out_aligned) {
+            d3[0] = (uint16_t)c0; d3[1] = (uint16_t)c1; d3[2] = (uint16_t)c2;
+          } else if ((row & 1ull) == 0) {
+            *reinterpret_cast<uint32_t *>(d3) = c0 | (c1 << 16);
+            d3[2] = (uint16_t)c2;
+          } else {
+            d3[0] = (uint16_t)c0;
+            *reinterpret_cast<uint32_t *>(d3 + 1) = c1 | (c2 << 16);
+          }
         }
       }
     }
@@ -715,20 +776,28 @@ static int psh_validate(uint32_t total_N, uint32_t batch, uint32_t num_bucket, u
 
 struct PshPlan { uint32_t tile, tiles_max, nbp; size_t scratch_words; size_t smem_hist, smem_rank; };
 
-static PshPlan psh_plan(uint32_t batch, uint32_t max_n, uint32_t nb) {
+// Scratch of one call in 32-bit words: three tile tables, five per-scene tables, two per-tile flags, the 16-bit keys.
+static size_t psh_scratch_words(uint32_t batch, uint32_t tiles_max, uint32_t nbp, uint32_t total_n) {
+  const size_t rows = (size_t)batch * tiles_max;
+  return 3 * rows * nbp + 5 * (size_t)batch * nbp + 2 * rows + ((size_t)total_n + 1) / 2;
+}
+
+// Tiles of 2048 points; when `max_words` is given (the fixed scratch of the allocation-free entry point) the tile
+// doubles, up to 16384 points, until the tables fit.
+static PshPlan psh_plan(uint32_t batch, uint32_t max_n, uint32_t nb, uint32_t total_n, size_t max_words = 0) {
   PshPlan p;
   p.nbp = nb + 1;
-  uint32_t want = (max_n + 63) / 64;                 // aim for at most 64 tiles per scene
-  uint32_t tile = ((want + 2047) / 2048) * 2048;
-  if (tile < 2048) tile = 2048;
-  if (tile > kMaxTile) tile = kMaxTile;
-  p.tile = tile;
-  p.tiles_max = max_n ? (max_n + tile - 1) / tile : 1;
-  if (p.tiles_max == 0) p.tiles_max = 1;
-  size_t rows = (size_t)batch * p.tiles_max;
-  p.scratch_words = 3 * rows * p.nbp + 3 * (size_t)batch * p.nbp + 2 * rows;
+  uint32_t tile = kMinTile;
+  for (;;) {
+    p.tile = tile;
+    p.tiles_max = max_n ? (max_n + tile - 1) / tile : 1;
+    if (p.tiles_max == 0) p.tiles_max = 1;
+    p.scratch_words = psh_scratch_words(batch, p.tiles_max, p.nbp, total_n);
+    if (max_words == 0 || p.scratch_words <= max_words || tile >= kMaxTile) break;
+    tile *= 2;
+  }
   p.smem_hist = tile_smem_bytes(p.nbp, 0);
-  p.smem_rank = tile_smem_bytes(p.nbp, tile);
+  p.smem_rank = tile_smem_bytes(p.nbp, p.tile);
   return p;
 }
 
@@ -741,8 +810,11 @@ static int psh_run(PshArgs a, const PshPlan &p, uint32_t *scratch, uint32_t max_
   a.count0 = w; w += (size_t)a.batch * p.nbp;
   a.kept = w; w += (size_t)a.batch * p.nbp;
   a.cntB = w; w += (size_t)a.batch * p.nbp;
+  a.attB = w; w += (size_t)a.batch * p.nbp;
+  a.movC = w; w += (size_t)a.batch * p.nbp;
   a.tile_pending = w; w += rows;
   a.tile_movers = w; w += rows;
+  a.keys = reinterpret_cast<uint16_t *>(w);
   a.tile = p.tile; a.tiles_max = p.tiles_max; a.nbp = p.nbp;
 
   int dev = 0;
@@ -755,13 +827,17 @@ static int psh_run(PshArgs a, const PshPlan &p, uint32_t *scratch, uint32_t max_
   if (p.smem_rank > 200 * 1024) return set_error(F3D_ERR_UNSUPPORTED, "num_bucket=%u needs %zu bytes of shared memory", a.nb, p.smem_rank);
 
   dim3 grid(p.tiles_max, a.batch);
+  const unsigned scan_blocks = (unsigned)(((size_t)a.batch * p.nbp + kPshWarps - 1) / kPshWarps);
   // the round A table is fully rewritten by the histogram kernel for live tiles; the round B and C tables are
   // accumulated with atomics and must start at zero (they are adjacent: one memset)
   if (max_n > 0) {
     F3D_CUDA_TRY(cudaMemsetAsync(a.tabB, 0, 2 * rows * p.nbp * sizeof(uint32_t), st));
     psh_hist_kernel<<<grid, kPshThreads, p.smem_hist, st>>>(a);
+    psh_scan_kernel<<<scan_blocks, kPshThreads, 0, st>>>(a, 0);
     psh_rankA_kernel<<<grid, kPshThreads, p.smem_rank, st>>>(a);
+    psh_scan_kernel<<<scan_blocks, kPshThreads, 0, st>>>(a, 1);
     psh_resolveB_kernel<<<grid, kPshThreads, p.smem_rank, st>>>(a);
+    psh_scan_kernel<<<scan_blocks, kPshThreads, 0, st>>>(a, 2);
   } else {
     F3D_CUDA_TRY(cudaMemsetAsync(a.bucket_counter, 0, (size_t)a.batch * a.nb * 4, st));
     F3D_CUDA_TRY(cudaMemsetAsync(a.cumsum_counter, 0, (size_t)a.batch * a.nb * 4, st));
@@ -775,7 +851,7 @@ static int psh_run(PshArgs a, const PshPlan &p, uint32_t *scratch, uint32_t max_
     a.tiles_max = p.tiles_max;
     psh_scatter_kernel<<<grid2, kPshThreads, p.smem_rank, st>>>(a);
   }
-  return check_launch("psh kernels", (max_n > 0 ? 3 : 0) + (gx > 0 ? 1 : 0));
+  return check_launch("psh kernels", (max_n > 0 ? 6 : 0) + (gx > 0 ? 1 : 0));
 }
 
 // The kernel arguments of one PSH call from the C-ABI arguments (shared by the two entry points below).
@@ -799,6 +875,7 @@ static PshArgs psh_pack_args(
   a.num_vox = num_vox; a.hash_type = hash_type; a.pad_to = pad_to_N;
   a.pad_bits = __half_as_ushort(__float2half_rn(pad_num));
   a.coord_aligned = (reinterpret_cast<uintptr_t>(coord) % 16 == 0) ? 1 : 0;
+  a.out_aligned = (reinterpret_cast<uintptr_t>(scatter_coord) % 4 == 0) ? 1 : 0;
   uint64_t sd = f3d::seed();
   a.key.k0 = (uint32_t)sd; a.key.k1 = (uint32_t)(sd >> 32);
   a.scene_base = f3d::scene_base();
@@ -819,7 +896,7 @@ extern "C" int f3d_batch_psh_scatter_pad_hash(
   DeviceGuard guard(device);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (instance_max_N > total_N) instance_max_N = total_N;
-  PshPlan p = psh_plan(batch_size, instance_max_N, num_bucket);
+  PshPlan p = psh_plan(batch_size, instance_max_N, num_bucket, total_N);
   void *scratch = nullptr;
   F3D_TRY(workspace(device, 0, p.scratch_words * sizeof(uint32_t), st, &scratch));
   PshArgs a = psh_pack_args(coord, bucket_id, bucket_counter, bucket_offset, batch_sep, total_N, batch_size, num_bucket,
@@ -876,7 +953,7 @@ extern "C" int f3d_batch_psh_scatter_pad_hash_noalloc(
   DeviceGuard guard(device);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (instance_max_N > total_N) instance_max_N = total_N;
-  PshPlan p = psh_plan(batch_size, instance_max_N, num_bucket);
+  PshPlan p = psh_plan(batch_size, instance_max_N, num_bucket, total_N, kStaticScratchWords);
   if (p.scratch_words > kStaticScratchWords)
     return set_error(F3D_ERR_UNSUPPORTED,
                      "batch_psh_scatter_pad_hash_noalloc: this batch needs %zu scratch words (batch %u x %u tiles x %u "

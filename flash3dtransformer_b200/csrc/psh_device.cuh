@@ -32,6 +32,33 @@ __device__ __forceinline__ uint32_t vox_axis(float c, float lo, float hi, uint32
   return (uint32_t)fmaxf(0.f, fminf(floorf(t), top));
 }
 
+// The same voxel index for many points of one axis: the divisor hi - lo is a constant, so its correctly rounded
+// reciprocal is taken once and every quotient costs five FMA-pipe instructions instead of a division.  a * r is
+// within two units in the last place of a / d; one residual correction q + (a - q d) r makes it faithful, and the
+// second one rounds it correctly (the classical residual-correction division: the residual is exact under FMA and
+// r is the correctly rounded reciprocal), so the result has the bits of __fdiv_rn.  A zero divisor (flat axis) takes
+// the division itself.
+struct AxisScale { float lo, d, r, nv, top; };
+
+__device__ __forceinline__ AxisScale make_axis_scale(float lo, float hi, uint32_t num_vox) {
+  AxisScale s;
+  s.lo = lo; s.d = __fsub_rn(hi, lo); s.r = __frcp_rn(s.d); s.nv = (float)num_vox; s.top = (float)(num_vox - 1u);
+  return s;
+}
+
+__device__ __forceinline__ uint32_t vox_axis(float c, const AxisScale &s) {
+  const float a = __fmul_rn(__fsub_rn(c, s.lo), s.nv);
+  float q;
+  if (s.d != 0.f) {
+    q = __fmul_rn(a, s.r);
+    q = __fmaf_rn(__fmaf_rn(-q, s.d, a), s.r, q);
+    q = __fmaf_rn(__fmaf_rn(-q, s.d, a), s.r, q);
+  } else {
+    q = __fdiv_rn(a, s.d);
+  }
+  return (uint32_t)fmaxf(0.f, fminf(floorf(q), s.top));
+}
+
 // x < 1024: bit i moves to bit 3i
 __device__ __forceinline__ uint32_t spread3(uint32_t x) {
   x = (x | (x << 16)) & 0x030000FFu;
@@ -59,6 +86,27 @@ __device__ __forceinline__ uint32_t first_hash(uint32_t hash_type, uint32_t vx, 
     default:           h = ((vx ^ vy ^ vz) & 0xFFFFu) % num_bucket; break;
   }
   return h < num_bucket ? h : num_bucket - 1u;   // guard for divisors that do not cover the range
+}
+
+// The same hash with the division / remainder turned into a shift / mask when the divisor (div hashes) or the bucket
+// count (mod hashes) is a power of two, which is what the host's plan always produces (num_bucket is rounded to a
+// power of two and the divisor is ceil(65535 / num_bucket)).  `shift` < 0 selects the general path.
+struct HashPlan { uint32_t hash_type, divisor, num_bucket; int shift; };
+
+__device__ __forceinline__ HashPlan make_hash_plan(uint32_t hash_type, uint32_t divisor, uint32_t num_bucket) {
+  HashPlan p{hash_type, divisor, num_bucket, -1};
+  const uint32_t v = (hash_type == H_ZORDER_DIV || hash_type == H_XORSUM_DIV) ? divisor : num_bucket;
+  if (v && (v & (v - 1u)) == 0u) p.shift = 31 - __clz(v);
+  return p;
+}
+
+__device__ __forceinline__ uint32_t first_hash(const HashPlan &p, uint32_t vx, uint32_t vy, uint32_t vz) {
+  if (p.shift < 0) return first_hash(p.hash_type, vx, vy, vz, p.divisor, p.num_bucket);
+  const bool zorder = p.hash_type == H_ZORDER_DIV || p.hash_type == H_ZORDER_MOD;
+  const uint32_t code = zorder ? zorder16(vx, vy, vz) : ((vx ^ vy ^ vz) & 0xFFFFu);
+  const bool div = p.hash_type == H_ZORDER_DIV || p.hash_type == H_XORSUM_DIV;
+  const uint32_t h = div ? (code >> p.shift) : (code & (p.num_bucket - 1u));
+  return h < p.num_bucket ? h : p.num_bucket - 1u;
 }
 
 // Philox4x32-10 (Salmon et al., SC'11): counter (c0..c3), key (k0,k1) -> four 32-bit words.

@@ -90,9 +90,10 @@ int f3d_batch_psh_scatter_pad_hash(
  * synchronisation of cudaMalloc / cudaFree).  It has no counterpart in the reference.  The scratch tables live in a
  * fixed 4 MiB device array inside the library (held on every GPU that loads it); the call performs no cudaMalloc,
  * cudaFree or other allocating call.  Limits: the batch must satisfy
- *     3*B*T*(NB+1) + 3*B*(NB+1) + 2*B*T <= 1,048,576   with B = batch_size, NB = num_bucket,
- *     T = ceil(instance_max_N / tile), tile = clamp(2048*ceil(instance_max_N / 131072), 2048, 16384),
- * otherwise F3D_STATUS_UNSUPPORTED is returned (8 scans of 120,000 points with 256 buckets need 372k words).
+ *     3*B*T*(NB+1) + 5*B*(NB+1) + 2*B*T + ceil(total_N / 2) <= 1,048,576   with B = batch_size, NB = num_bucket,
+ *     T = ceil(instance_max_N / tile), tile = 2048, doubled (up to 16384) while the sum does not fit,
+ * otherwise F3D_STATUS_UNSUPPORTED is returned (8 scans of 120,000 points with 256 buckets need 855k words at
+ * tile 2048; the last term holds one 16-bit key per point).
  * The first call on a device looks up the array's device address (cudaGetSymbolAddress) and sets a kernel attribute;
  * with the driver's lazy module loading that first call is also where the library's code and the array itself are
  * brought onto the device, so the no-allocation guarantee holds from the second call on: make one warm-up call per

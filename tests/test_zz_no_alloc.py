@@ -66,7 +66,7 @@ def test_noalloc_entry_point_refuses_oversized_batches(cuda_device):
     c16 = np.zeros((sum(sizes), 3), dtype=np.float16)
     c16[:, 0] = np.linspace(0, 1, c16.shape[0])
     seps = np.cumsum(sizes)
-    nb, div = 2048, 32                                      # 16 scenes x 35 tiles x 2049 columns do not fit 4 MiB
+    nb, div = 2048, 32                                      # 16 scenes x 5 tiles x 2049 columns + the keys do not fit 4 MiB
     buf = _buffers(cuda_device, c16, seps, nb, c16.shape[0])
     with pytest.raises(RuntimeError, match="fixed scratch"):
         pshattn.batch_psh_scatter_pad_hash_noalloc(
