@@ -75,6 +75,13 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
   return r;
 }
 
+// two fp32 values as a packed pair in the kernel's 16-bit element type (P in tensor memory, O in global memory)
+template <bool F16> __device__ __forceinline__ uint32_t pack_p2(float a, float b) {
+  if (F16) { __half2 h = __floats2half2_rn(a, b); return *reinterpret_cast<uint32_t *>(&h); }
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t *>(&h);
+}
+
 // 2^x for a pair of non-positive arguments on the FMA pipe instead of the special-function unit: n = round(x) by the
 // magic-number addition (the sum x + 1.5 * 2^23 carries n in its low mantissa bits), f = x - n in [-0.5, 0.5], a cubic
 // for 2^f (largest relative error 7.5e-5, against the 3.9e-3 of the bf16 rounding P gets anyway), and n added to the
@@ -120,7 +127,7 @@ template <int D, int BKV, int NQ> struct AttnCfg {
 
 // POLY8: of every eight pairs of scores, this many take their exponential from poly_exp2_pair (FMA pipe) and the rest
 // from ex2.approx (special-function unit), so that both pipes work on every row.
-template <int D, int BKV, int NQ, int POLY8>
+template <int D, int BKV, int NQ, int POLY8, bool F16>
 __global__ void __launch_bounds__((AttnCfg<D, BKV, NQ>::kThreads), (AttnCfg<D, BKV, NQ>::kMinCtas))
 attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, AttnFwdArgs a) {
@@ -188,8 +195,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       };
       for (int j = 0; j < kKvStages && j < num_tiles; ++j) load_kv(j);
 
-      constexpr uint32_t idesc_s = tc::make_idesc_f16(kBQ, BKV, true, false, false);
-      constexpr uint32_t idesc_o = tc::make_idesc_f16(kBQ, C::DCH, true, false, true);    // B (= V) is MN-major
+      constexpr uint32_t idesc_s = tc::make_idesc_f16(kBQ, BKV, !F16, false, false);
+      constexpr uint32_t idesc_o = tc::make_idesc_f16(kBQ, C::DCH, !F16, false, true);    // B (= V) is MN-major
       const uint32_t q_addr = tc::smem_u32(sq);
       // S_t = Q_t K^T of key tile j: K-major operands, 8-row groups are 8*RB bytes apart
       auto issue_s = [&](int t, int j) {
@@ -299,8 +306,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           e0 = fast_exp2(x0); e1 = fast_exp2(x1);
         }
         sum2 = add2(sum2, pack2(e0, e1));
-        __nv_bfloat162 hh = __floats2bfloat162_rn(e0, e1);
-        p[i] = *reinterpret_cast<uint32_t *>(&hh);
+        p[i] = pack_p2<F16>(e0, e1);
       }
       if (j > 0) {
         // P of the previous tile has been consumed and O is complete up to it: P may be overwritten, O rescaled
@@ -320,8 +326,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           e0 = fast_exp2(x0); e1 = fast_exp2(x1);
         }
         sum2 = add2(sum2, pack2(e0, e1));
-        __nv_bfloat162 hh = __floats2bfloat162_rn(e0, e1);
-        p[i] = *reinterpret_cast<uint32_t *>(&hh);
+        p[i] = pack_p2<F16>(e0, e1);
       }
       tc::tmem_st_32x32b_x16(p_tmem + 16, p);
       float sum, sum_hi;
@@ -355,9 +360,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         tc::tmem_ld_32x32b_x16(o_tmem + c, o);
         tc::tmem_ld_wait();
         uint4 w[2];
-        __nv_bfloat162 *h2 = reinterpret_cast<__nv_bfloat162 *>(w);
+        uint32_t *h2 = reinterpret_cast<uint32_t *>(w);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) h2[i] = __floats2bfloat162_rn(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv);
+        for (int i = 0; i < 8; ++i) h2[i] = pack_p2<F16>(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv);
         *reinterpret_cast<uint4 *>(op + c) = w[0];
         *reinterpret_cast<uint4 *>(op + c + 8) = w[1];
       }
@@ -374,17 +379,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   if (warp == 0) { tc::tc_fence_after_sync(); tc::tmem_dealloc(tmem_base, C::kTmemCols); }
 }
 
-template <int D, int BKV, int NQ, int POLY8 = 0>
+template <int D, int BKV, int NQ, int POLY8, bool F16>
 static int launch_attn_fwd(const void *Q, const void *K, const void *V, AttnFwdArgs a, int device, cudaStream_t st) {
   using C = AttnCfg<D, BKV, NQ>;
-  auto kern = attn_fwd_kernel<D, BKV, NQ, POLY8>;
+  auto kern = attn_fwd_kernel<D, BKV, NQ, POLY8, F16>;
+  const int dt = F16 ? 1 : 0;
   F3D_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(kern), device, C::kSmem));
   CUtensorMap mq, mk, mv;
   const uint64_t rows = (uint64_t)a.B * a.L;
   const uint64_t s1 = (uint64_t)D * 2, s2 = (uint64_t)a.H * D * 2;
-  F3D_TRY(encode_tmap_3d(&mq, 0, Q, D, a.H, rows, s1, s2, C::DCH, 1, kBQ, C::RB));
-  F3D_TRY(encode_tmap_3d(&mk, 0, K, D, a.H, rows, s1, s2, C::DCH, 1, BKV, C::RB));
-  F3D_TRY(encode_tmap_3d(&mv, 0, V, D, a.H, rows, s1, s2, C::DCH, 1, BKV, C::RB));
+  F3D_TRY(encode_tmap_3d(&mq, dt, Q, D, a.H, rows, s1, s2, C::DCH, 1, kBQ, C::RB));
+  F3D_TRY(encode_tmap_3d(&mk, dt, K, D, a.H, rows, s1, s2, C::DCH, 1, BKV, C::RB));
+  F3D_TRY(encode_tmap_3d(&mv, dt, V, D, a.H, rows, s1, s2, C::DCH, 1, BKV, C::RB));
   dim3 grid(a.num_scopes * (a.k * a.q_blocks_per_bucket / NQ), a.H, a.B);
   kern<<<grid, C::kThreads, C::kSmem, st>>>(mq, mk, mv, a);
   return check_launch("buck_swin_fwd");
@@ -394,19 +400,25 @@ static int launch_attn_fwd(const void *Q, const void *K, const void *V, AttnFwdA
 // (measured at D = 32, window 4096: 0 / 12.5 / 25 / 37.5 / 50 % -> 439 / 448 / 462 / 446 / 413 TFLOP/s; beyond a quarter
 // the extra instructions cost more issue slots than the special-function slots they free).  One query tile per CTA:
 // two and four tiles per CTA sharing the K/V stream measured 2 % and 4 % slower (their exponential phases line up).
-template <int D>
-static int launch_attn_fwd_small(const void *Q, const void *K, const void *V, AttnFwdArgs a, int device, cudaStream_t st) {
-  return launch_attn_fwd<D, 64, 1, 2>(Q, K, V, a, device, st);
+template <bool F16>
+static int launch_attn_fwd_any(int D, const void *Q, const void *K, const void *V, AttnFwdArgs a, int device, cudaStream_t st) {
+  switch (D) {
+    case 16: return launch_attn_fwd<16, 64, 1, 2, F16>(Q, K, V, a, device, st);
+    case 32: return launch_attn_fwd<32, 64, 1, 2, F16>(Q, K, V, a, device, st);
+    case 64: return launch_attn_fwd<64, 64, 1, 0, F16>(Q, K, V, a, device, st);
+    default: return launch_attn_fwd<128, 64, 1, 0, F16>(Q, K, V, a, device, st);
+  }
 }
 
 }  // namespace f3d
 
 using namespace f3d;
 
-extern "C" int f3d_buck_swin_fwd(const void *Q, const void *K, const void *V, void *O, void *LSE, const void *scope_buckets,
-                                 int B, int L, int H, int D, int num_scopes, int scope_size, uint32_t bucket_size,
-                                 int device, void *stream) {
+static int buck_swin_fwd_impl(const void *Q, const void *K, const void *V, void *O, void *LSE, const void *scope_buckets,
+                              int B, int L, int H, int D, int num_scopes, int scope_size, uint32_t bucket_size, int dtype,
+                              int device, void *stream) {
   if (B <= 0 || L <= 0 || H <= 0) return set_error(F3D_ERR_ARG, "buck_swin_fwd: empty tensor");
+  if (dtype != 0 && dtype != 1) return set_error(F3D_ERR_UNSUPPORTED, "buck_swin_fwd: element type %d (0 = bf16 and 1 = fp16 are supported)", dtype);
   if (D != 16 && D != 32 && D != 64 && D != 128) return set_error(F3D_ERR_UNSUPPORTED, "buck_swin_fwd: head_dim %d (16, 32, 64, 128 are supported)", D);
   if (bucket_size == 0 || bucket_size % kBQ) return set_error(F3D_ERR_UNSUPPORTED, "buck_swin_fwd: bucket_size %u must be a positive multiple of %d", bucket_size, kBQ);
   if (L % (int)bucket_size) return set_error(F3D_ERR_ARG, "buck_swin_fwd: sequence length %d is not a multiple of bucket_size %u", L, bucket_size);
@@ -420,13 +432,18 @@ extern "C" int f3d_buck_swin_fwd(const void *Q, const void *K, const void *V, vo
                 B, L, H, num_scopes, scope_size, (int)bucket_size, (int)bucket_size / kBQ,
                 1.4426950408889634f / sqrtf((float)D), status_word(device)};
   if (!a.status) return F3D_ERR_CUDA;
-  int rc;
-  switch (D) {
-    case 16: rc = launch_attn_fwd_small<16>(Q, K, V, a, device, st); break;
-    case 32: rc = launch_attn_fwd_small<32>(Q, K, V, a, device, st); break;
-    case 64: rc = launch_attn_fwd<64, 64, 1>(Q, K, V, a, device, st); break;
-    default: rc = launch_attn_fwd<128, 64, 1>(Q, K, V, a, device, st); break;
-  }
-  F3D_TRY(rc);
+  F3D_TRY(dtype == 1 ? launch_attn_fwd_any<true>(D, Q, K, V, a, device, st) : launch_attn_fwd_any<false>(D, Q, K, V, a, device, st));
   return maybe_sync(st, "buck_swin_fwd");
+}
+
+extern "C" int f3d_buck_swin_fwd(const void *Q, const void *K, const void *V, void *O, void *LSE, const void *scope_buckets,
+                                 int B, int L, int H, int D, int num_scopes, int scope_size, uint32_t bucket_size,
+                                 int device, void *stream) {
+  return buck_swin_fwd_impl(Q, K, V, O, LSE, scope_buckets, B, L, H, D, num_scopes, scope_size, bucket_size, 0, device, stream);
+}
+
+extern "C" int f3d_buck_swin_fwd_dtype(const void *Q, const void *K, const void *V, void *O, void *LSE, const void *scope_buckets,
+                                       int B, int L, int H, int D, int num_scopes, int scope_size, uint32_t bucket_size,
+                                       int dtype, int device, void *stream) {
+  return buck_swin_fwd_impl(Q, K, V, O, LSE, scope_buckets, B, L, H, D, num_scopes, scope_size, bucket_size, dtype, device, stream);
 }

@@ -1,4 +1,6 @@
-// bf16 GEMM for the per-token projections: C[M,N] = A[M,K] . W[N,K]^T (+ bias) (+ residual), fp32 accumulation.
+// bf16 (or fp16) GEMM for the per-token projections: C[M,N] = A[M,K] . W[N,K]^T (+ bias) (+ residual), fp32
+// accumulation.  The element type is a template switch: it sets the operand format of the MMA instruction descriptor
+// and the conversions of the epilogue; A, W, the residual and C share it.
 //
 // Replaces the cuBLAS calls behind nn.Linear in the reference's attention block (qkv and proj,
 // flash3dxfmr/layers/buck_swin.py:159,163,185-194) and the toy mma.sync kernel gemm_sm_bf16_ker
@@ -98,7 +100,22 @@ __device__ __forceinline__ void swiglu_pair(uint64_t gate2, uint64_t up2, float 
   gunpack2(gmul2(gfma2(h2, gpack2(t0, t1), h2), up2), o0, o1);
 }
 
-template <int BN>
+// two fp32 values to a packed pair of 16-bit outputs, and back, in the kernel's element type
+template <bool F16> __device__ __forceinline__ uint32_t pack_out2(float a, float b) {
+  if (F16) { __half2 h = __floats2half2_rn(a, b); return *reinterpret_cast<uint32_t *>(&h); }
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t *>(&h);
+}
+template <bool F16> __device__ __forceinline__ float2 unpack_in2(uint32_t w) {
+  if (F16) return __half22float2(*reinterpret_cast<const __half2 *>(&w));
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&w));
+}
+template <bool F16> __device__ __forceinline__ float unpack_in1(const __nv_bfloat16 *p) {
+  if (F16) return __half2float(*reinterpret_cast<const __half *>(p));
+  return __bfloat162float(*p);
+}
+
+template <int BN, bool F16>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                          const __grid_constant__ CUtensorMap map_c, GemmArgs g) {
@@ -180,7 +197,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     }
   } else if (warp == 1) {
     if (tc::elect_one()) {
-      constexpr uint32_t idesc = tc::make_idesc_f16(BM, BN, true, false, false);
+      constexpr uint32_t idesc = tc::make_idesc_f16(BM, BN, !F16, false, false);
       uint32_t it = 0, t_local = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t_local) {
@@ -284,13 +301,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               const uint4 w = __ldg(reinterpret_cast<const uint4 *>(rp + j));
-              const __nv_bfloat162 *h2 = reinterpret_cast<const __nv_bfloat162 *>(&w);
+              const uint32_t *h2 = reinterpret_cast<const uint32_t *>(&w);
 #pragma unroll
-              for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h2[e]); gunpack2(gadd2(gpack2(v[j + 2 * e], v[j + 2 * e + 1]), gpack2(f.x, f.y)), v[j + 2 * e], v[j + 2 * e + 1]); }
+              for (int e = 0; e < 4; ++e) { const float2 f = unpack_in2<F16>(h2[e]); gunpack2(gadd2(gpack2(v[j + 2 * e], v[j + 2 * e + 1]), gpack2(f.x, f.y)), v[j + 2 * e], v[j + 2 * e + 1]); }
             }
           } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) if (oc0 + j < g.N) v[j] += __bfloat162float(rp[j]);
+            for (int j = 0; j < 32; ++j) if (oc0 + j < g.N) v[j] += unpack_in1<F16>(rp + j);
           }
         }
         if (g.direct_store) {
@@ -300,9 +317,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
               const int oc = oc0 + j;
               if (oc >= g.N) continue;
               uint4 w;
-              __nv_bfloat162 *h2 = reinterpret_cast<__nv_bfloat162 *>(&w);
+              uint32_t *h2 = reinterpret_cast<uint32_t *>(&w);
 #pragma unroll
-              for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(v[j + 2 * e], v[j + 2 * e + 1]);
+              for (int e = 0; e < 4; ++e) h2[e] = pack_out2<F16>(v[j + 2 * e], v[j + 2 * e + 1]);
               *reinterpret_cast<uint4 *>(g.c_ptr + (size_t)(oc / g.split_n) * g.split_stride + (size_t)row * g.split_n + oc % g.split_n) = w;
             }
           }
@@ -316,9 +333,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           uint4 w;
-          __nv_bfloat162 *h2 = reinterpret_cast<__nv_bfloat162 *>(&w);
+          uint32_t *h2 = reinterpret_cast<uint32_t *>(&w);
 #pragma unroll
-          for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(v[j * 8 + 2 * e], v[j * 8 + 2 * e + 1]);
+          for (int e = 0; e < 4; ++e) h2[e] = pack_out2<F16>(v[j * 8 + 2 * e], v[j * 8 + 2 * e + 1]);
           tc::sts128(tc::smem_u32(ob) + lane * 64 + ((j ^ ((lane >> 1) & 3)) * 16), w);
         }
         tc::fence_proxy_async();
@@ -349,10 +366,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 
 int *status_word(int device);   // device word, zero until a kernel reports an abandoned wait
 
-template <int BN>
+template <int BN, bool F16>
 static int launch_gemm(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mc, const GemmArgs &g, int device,
                        cudaStream_t st) {
-  auto kern = gemm_bf16_tcgen05_kernel<BN>;
+  auto kern = gemm_bf16_tcgen05_kernel<BN, F16>;
   F3D_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(kern), device, GemmSmem<BN>::kTotal));
   int tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN);
   int grid = tiles < sm_count(device) ? tiles : sm_count(device);
@@ -360,9 +377,12 @@ static int launch_gemm(const CUtensorMap &ma, const CUtensorMap &mb, const CUten
   return check_launch("gemm_bf16_tcgen05");
 }
 
-// C (bf16, nsplit matrices of [M, split_n] with leading dimension split_n, `split_stride` elements apart)
+// C (nsplit matrices of [M, split_n] with leading dimension split_n, `split_stride` elements apart); dtype 0 = bf16,
+// 1 = fp16 for A, W, residual and C
 int linear_bf16(const void *A, int lda, const void *W, int ldw, const void *bias, const void *residual, int ldr, void *C,
-                long long split_stride, int M, int N, int K, int nsplit, int epilogue, int device, cudaStream_t st, int ksplit = 1) {
+                long long split_stride, int M, int N, int K, int nsplit, int epilogue, int device, cudaStream_t st, int ksplit = 1,
+                int dtype = 0) {
+  if (dtype != 0 && dtype != 1) return set_error(F3D_ERR_UNSUPPORTED, "gemm: element type %d (0 = bf16 and 1 = fp16 are supported)", dtype);
   if (M <= 0 || N <= 0 || K <= 0) return set_error(F3D_ERR_ARG, "gemm: M, N, K must be positive (got %d, %d, %d)", M, N, K);
   if (K % 8 || lda % 8 || ldw % 8) return set_error(F3D_ERR_ARG, "gemm: K and the leading dimensions must be multiples of 8 (TMA 16-byte rule)");
   if (nsplit < 1 || N % nsplit) return set_error(F3D_ERR_ARG, "gemm: N=%d is not divisible into %d splits", N, nsplit);
@@ -383,19 +403,27 @@ int linear_bf16(const void *A, int lda, const void *W, int ldw, const void *bias
   const int direct = (nsplit > 1 && split_n % 32) ? 1 : 0;      // a 32-column task must not straddle two outputs
   if (reinterpret_cast<uintptr_t>(C) % 16) return set_error(F3D_ERR_ARG, "gemm: output pointer is not 16-byte aligned");
   CUtensorMap ma, mb, mc;
-  F3D_TRY(encode_tmap_2d(&ma, 0, A, (uint64_t)K, (uint64_t)M * ksplit, (uint64_t)lda * 2, BK, BM, 128));
+  F3D_TRY(encode_tmap_2d(&ma, dtype, A, (uint64_t)K, (uint64_t)M * ksplit, (uint64_t)lda * 2, BK, BM, 128));
   int b_box_rows = epilogue == EPI_SWIGLU ? BN / 2 : BN;
-  F3D_TRY(encode_tmap_2d(&mb, 0, W, (uint64_t)K, (uint64_t)N * ksplit, (uint64_t)ldw * 2, BK, b_box_rows, 128));
-  F3D_TRY(encode_tmap_3d(&mc, 0, C, (uint64_t)split_n, (uint64_t)M, (uint64_t)nsplit, (uint64_t)split_n * 2,
+  F3D_TRY(encode_tmap_2d(&mb, dtype, W, (uint64_t)K, (uint64_t)N * ksplit, (uint64_t)ldw * 2, BK, b_box_rows, 128));
+  F3D_TRY(encode_tmap_3d(&mc, dtype, C, (uint64_t)split_n, (uint64_t)M, (uint64_t)nsplit, (uint64_t)split_n * 2,
                          (uint64_t)split_stride * 2, 32, 32, 1, 64));
   GemmArgs g{M, N, K, nsplit, split_n, static_cast<const float *>(bias), static_cast<const __nv_bfloat16 *>(residual), ldr,
              epilogue, direct, static_cast<__nv_bfloat16 *>(C), split_stride, status_word(device), ksplit};
   if (!g.status) return F3D_ERR_CUDA;
+  if (dtype == 1) {
+    switch (BN) {
+      case 32: return launch_gemm<32, true>(ma, mb, mc, g, device, st);
+      case 64: return launch_gemm<64, true>(ma, mb, mc, g, device, st);
+      case 128: return launch_gemm<128, true>(ma, mb, mc, g, device, st);
+      default: return launch_gemm<256, true>(ma, mb, mc, g, device, st);
+    }
+  }
   switch (BN) {
-    case 32: return launch_gemm<32>(ma, mb, mc, g, device, st);
-    case 64: return launch_gemm<64>(ma, mb, mc, g, device, st);
-    case 128: return launch_gemm<128>(ma, mb, mc, g, device, st);
-    default: return launch_gemm<256>(ma, mb, mc, g, device, st);
+    case 32: return launch_gemm<32, false>(ma, mb, mc, g, device, st);
+    case 64: return launch_gemm<64, false>(ma, mb, mc, g, device, st);
+    case 128: return launch_gemm<128, false>(ma, mb, mc, g, device, st);
+    default: return launch_gemm<256, false>(ma, mb, mc, g, device, st);
   }
 }
 
@@ -412,6 +440,17 @@ extern "C" int f3d_linear_bf16(const void *A, const void *W, const void *bias, c
   F3D_TRY(linear_bf16(A, K, W, K, bias, residual, out_n, C, (long long)M * (out_n / (nsplit > 0 ? nsplit : 1)), M, N, K, nsplit,
                       epilogue, device, st));
   return maybe_sync(st, "linear_bf16");
+}
+
+extern "C" int f3d_linear_dtype(const void *A, const void *W, const void *bias, const void *residual, void *C, int M, int N,
+                                int K, int nsplit, int epilogue, int dtype, int device, void *stream) {
+  DeviceGuard guard(device);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  F3D_TRY(maybe_sync(st, "linear"));
+  int out_n = epilogue == EPI_SWIGLU ? N / 2 : N;
+  F3D_TRY(linear_bf16(A, K, W, K, bias, residual, out_n, C, (long long)M * (out_n / (nsplit > 0 ? nsplit : 1)), M, N, K, nsplit,
+                      epilogue, device, st, 1, dtype));
+  return maybe_sync(st, "linear");
 }
 
 extern "C" int f3d_linear_ksplit_bf16(const void *A, const void *W, const void *bias, const void *residual, void *C, int M, int N,

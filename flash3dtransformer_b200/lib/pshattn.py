@@ -332,13 +332,16 @@ def gemm_sm_bf16(A, B, O) -> None:
 
 def linear_bf16(x, weight, bias, out, residual=None, nsplit=1, epilogue=EPI_NONE) -> None:
     """out = x @ weight^T (+ bias) (+ residual) on the tcgen05 GEMM; `out` holds nsplit contiguous
-    [M, N/nsplit] matrices (nsplit=3: Q, K, V).  Not part of the reference's operator module: the reference leaves
-    these projections to nn.Linear / cuBLAS (flash3dxfmr/layers/buck_swin.py:159,163)."""
+    [M, N/nsplit] matrices (nsplit=3: Q, K, V).  x, weight, residual and out share one element type, bfloat16 or
+    float16 (float16 is the element type of the reference's CPU-runnable configuration; forward only).  Not part of
+    the reference's operator module: the reference leaves these projections to nn.Linear / cuBLAS
+    (flash3dxfmr/layers/buck_swin.py:159,163)."""
     tensors, names = [x, weight, out], ["x", "weight", "out"]
     if residual is not None:
         tensors.append(residual); names.append("residual")
     dev = _check_tensors(tensors, names)
-    _check_dtype(tensors, names, torch.bfloat16)
+    _require(x.dtype in (torch.bfloat16, torch.float16), f"Tensor x has dtype {x.dtype}; bfloat16 and float16 are supported")
+    _check_dtype(tensors, names, x.dtype)
     m, k = x.shape
     n = weight.shape[0]
     _require(weight.shape[1] == k, f"weight must be [N,{k}], got {tuple(weight.shape)}")
@@ -354,9 +357,12 @@ def linear_bf16(x, weight, bias, out, residual=None, nsplit=1, epilogue=EPI_NONE
     if residual is not None:
         _require(tuple(residual.shape) == (m, out_n), f"residual must be [{m},{out_n}]")
         rptr = _ptr(residual)
-    st = _cabi.load().f3d_linear_bf16(_ptr(x), _ptr(weight), bptr, rptr, _ptr(out), m, n, k, int(nsplit), int(epilogue),
-                                      _dev_index(dev), _stream(dev))
+    st = _cabi.load().f3d_linear_dtype(_ptr(x), _ptr(weight), bptr, rptr, _ptr(out), m, n, k, int(nsplit), int(epilogue),
+                                       _FEAT_DTYPES[x.dtype], _dev_index(dev), _stream(dev))
     _cabi.check(st, "linear_bf16")
+
+
+linear = linear_bf16          # the element type follows the tensors
 
 
 def wgrad_supported(n: int, k: int) -> bool:
@@ -409,9 +415,10 @@ def linear_ksplit_bf16(x, weight, out, bias=None, residual=None) -> None:
 
 
 # --------------------------------------------------------------------------------------- bucketed attention
-def _check_qkv(tensors, names):
+def _check_qkv(tensors, names, dtypes=(torch.bfloat16,)):
     dev = _check_tensors(tensors, names)
-    _check_dtype(tensors, names, torch.bfloat16)
+    _require(tensors[0].dtype in dtypes, f"Tensor {names[0]} has dtype {tensors[0].dtype}; supported: {', '.join(str(d) for d in dtypes)}")
+    _check_dtype(tensors, names, tensors[0].dtype)
     shape = tuple(tensors[0].shape)
     _require(len(shape) == 4, f"Expect {names[0]} with four axes [B, L, H, D], but got shape={shape}")
     for t, n in zip(tensors, names):
@@ -421,16 +428,17 @@ def _check_qkv(tensors, names):
 
 def buck_swin_fwd(Q, K, V, O, L, Scope_buckets, bucket_size) -> None:
     """f3d::buck_swin_fwd (declared src/f3d_frontend.cu:90-92; caller flash3dxfmr/layers/buck_swin.py:57).
-    O[B,L,H,D] and the log-sum-exp L[B,L,H] are written in place."""
-    dev, (b, l, h, d) = _check_qkv([Q, K, V, O], ["Q", "K", "V", "O"])
+    O[B,L,H,D] and the log-sum-exp L[B,L,H] are written in place.  Q, K, V, O are bfloat16 or float16 (all the
+    same)."""
+    dev, (b, l, h, d) = _check_qkv([Q, K, V, O], ["Q", "K", "V", "O"], (torch.bfloat16, torch.float16))
     _check_tensors([L, Scope_buckets], ["L", "Scope_buckets"])
     _check_dtype([L], ["L"], torch.float32)
     _check_dtype([Scope_buckets], ["Scope_buckets"], torch.uint32)
     _require(tuple(L.shape) == (b, l, h), f"L must be [{b},{l},{h}], got {tuple(L.shape)}")
     _require(Scope_buckets.dim() == 2, "Scope_buckets must be [num_scopes, scope_size]")
-    st = _cabi.load().f3d_buck_swin_fwd(_ptr(Q), _ptr(K), _ptr(V), _ptr(O), _ptr(L), _ptr(Scope_buckets), b, l, h, d,
-                                        Scope_buckets.shape[0], Scope_buckets.shape[1], int(bucket_size),
-                                        _dev_index(dev), _stream(dev))
+    st = _cabi.load().f3d_buck_swin_fwd_dtype(_ptr(Q), _ptr(K), _ptr(V), _ptr(O), _ptr(L), _ptr(Scope_buckets), b, l, h, d,
+                                              Scope_buckets.shape[0], Scope_buckets.shape[1], int(bucket_size),
+                                              _FEAT_DTYPES[Q.dtype], _dev_index(dev), _stream(dev))
     _cabi.check(st, "buck_swin_fwd")
 
 

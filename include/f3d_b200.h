@@ -208,6 +208,12 @@ int f3d_device_status(int device);
 int f3d_linear_bf16(const void *A, const void *W, const void *bias, const void *residual, void *C, int M, int N, int K,
                     int nsplit, int epilogue, int device, void *stream);
 
+/* f3d_linear_bf16 with the element type as an argument: dtype F3D_DTYPE_BF16 or F3D_DTYPE_FP16 for A, W, residual and
+ * C (bias stays fp32, accumulation fp32).  The reference states its CPU-runnable configuration in fp16 features; this
+ * entry point and f3d_buck_swin_fwd_dtype serve it (forward only). */
+int f3d_linear_dtype(const void *A, const void *W, const void *bias, const void *residual, void *C, int M, int N, int K,
+                     int nsplit, int epilogue, int dtype, int device, void *stream);
+
 /* replaces f3d::gemm_sm_bf16 (src/psh/gemm_dispatcher.cu:26-80; binding src/f3d_frontend.cu:135): O[M,N] = A[M,K] . B[K,N],
  * bf16 in/out, fp32 accumulation; synchronises the stream like the reference (:77).  Any M; N, K multiples of 8. */
 int f3d_gemm_sm_bf16(const void *A, const void *B, void *O, int M, int N, int K, int device, void *stream);
@@ -224,6 +230,13 @@ int f3d_gemm_sm_bf16(const void *A, const void *B, void *O, int M, int N, int K,
 int f3d_buck_swin_fwd(const void *Q, const void *K, const void *V, void *O, void *LSE, const void *scope_buckets,
                       int B, int L, int H, int D, int num_scopes, int scope_size, uint32_t bucket_size,
                       int device, void *stream);
+
+/* f3d_buck_swin_fwd with the element type of Q, K, V, O as an argument (F3D_DTYPE_BF16 or F3D_DTYPE_FP16; the
+ * probabilities that enter the second product are rounded to the same type).  Forward only: f3d_buck_swin_bwd takes
+ * bf16. */
+int f3d_buck_swin_fwd_dtype(const void *Q, const void *K, const void *V, void *O, void *LSE, const void *scope_buckets,
+                            int B, int L, int H, int D, int num_scopes, int scope_size, uint32_t bucket_size, int dtype,
+                            int device, void *stream);
 
 /* LayerNorm over the last dimension of bf16 [rows, C] with fp32 weight/bias [C] and an optional exact GELU.
  * Stands in for the te.LayerNorm / nn.LayerNorm steps of XFMR and the pooling wrappers
