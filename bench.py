@@ -161,8 +161,19 @@ class FamilyTimer:
             by = 2.0 * (m * k + out.numel() + (0 if residual is None else residual.numel()))
             return 2.0 * m * n * k, by
 
+        def gemm_fused(x, w, bias, out, residual=None, nsplit=1, epilogue=0, ln_stats=None, ln_colsum=None, ln_eps=1e-5,
+                       stats_out=None):
+            m, k = x.shape
+            n = w.shape[0]
+            by = 2.0 * (m * k + out.numel() + (0 if residual is None else residual.numel()))
+            by += 8.0 * m * ((ln_stats is not None) + (stats_out is not None))       # row sums read / written
+            return 2.0 * m * n * k, by
+
         def ln(x, w, b, out, eps=1e-5, gelu=False):
             return 0.0, 4.0 * x.numel()
+
+        def stats(x, st):
+            return 0.0, 2.0 * x.numel() + 8.0 * x.shape[0]
 
         def pool(coord, feat, seps, maxn, S, nv, bmin, bmax, sid, soff, rsep, rcoord, rfeat, ind, ht, op):
             n = coord.shape[0]
@@ -180,7 +191,9 @@ class FamilyTimer:
 
         self._wrap("buck_swin_fwd", attn, "attention_fwd")
         self._wrap("linear_bf16", gemm, "gemm")
+        self._wrap("linear_fused", gemm_fused, "gemm")
         self._wrap("layernorm_bf16", ln, "layernorm")
+        self._wrap("row_stats_bf16", stats, "layernorm")
         self._wrap("batch_subbuck_reduce", pool, "subbuck_pool")
         self._wrap("additive_unpool_fwd", unpool, "unpool")
         self._wrap("batch_psh_scatter_pad_hash", psh, "psh_scatter")

@@ -15,6 +15,15 @@
 //               32x32 block in swizzled shared memory and writes it with a TMA store
 // Up to four accumulators (at most 512 tensor-memory columns) let the epilogues of earlier tiles overlap the MMAs of
 // the following ones.
+// LayerNorm folded into the projection (optional): with W' = W diag(gamma), s[n] = sum_k W'[n,k] and
+// b'[n] = b[n] + sum_k beta[k] W[n,k] prepared by the host, LayerNorm(x) W^T + b = rstd (x W'^T - mean s) + b'.  The
+// MMAs run on the raw rows; the epilogue reads each row's (sum, sum of squares) from `ln_stats`, and applies
+// rstd * acc - (mean * rstd) * s + b' per column.  Those row sums are themselves a by-product of the GEMM that wrote x:
+// with `stats_out` the epilogue adds up each output row and its squares, so a chain projection -> LayerNorm ->
+// projection needs neither a LayerNorm kernel nor a pass over x for statistics.  The sums are the same bits on every
+// run: a warp adds its tasks of a tile in column order, the three warps of a lane quadrant leave their partial sums in
+// shared memory and the last one to finish adds them in a fixed order and stores the row's pair (with more than one
+// column tile per row, N > 256, the tiles' pairs meet in an atomic add: two addends commute, so N <= 512 stays exact).
 // Outputs may be split column-wise into `nsplit` separate [M, N/nsplit] matrices (Q, K, V written directly in
 // the [L, H*D] layout the attention kernel reads, instead of three .contiguous() copies,
 // flash3dxfmr/layers/buck_swin.py:188-190).
@@ -47,6 +56,10 @@ struct GemmArgs {
   long long split_stride;
   int *status;
   int ksplit;            // > 1: A is [ksplit, M, K], W is [ksplit, N, K] and the products of the slices are summed
+  const float2 *ln_stats;   // [M] (sum, sum of squares) of every row of A over its K channels, or null: folded LayerNorm
+  const float *ln_colsum;   // [N] column sums s of the scaled weight (with ln_stats)
+  float ln_eps, ln_inv_k;
+  float2 *stats_out;        // [M] or null: (sum, sum of squares) of every output row, accumulated with atomic adds
 };
 
 template <int BN> struct GemmSmem {
@@ -57,7 +70,9 @@ template <int BN> struct GemmSmem {
   static constexpr int kOutBytes = kEpiWarps * 2 /*buffers*/ * 32 * 64;    // 32 rows x 32 bf16 per buffer
   static constexpr int kAcc = BN >= 256 ? 2 : 4;        // accumulator buffers in tensor memory (kAcc * BN <= 512 columns)
   static constexpr int kBarBytes = 256;
-  static constexpr int kTotal = kStages * kStageBytes + kOutBytes + kBarBytes + 1024 /*alignment slack*/;
+  // partial row sums of the epilogue warps: [accumulator][quadrant][warp of the quadrant][32 rows] pairs + counters
+  static constexpr int kStatBytes = kAcc * 4 * (kEpiWarps / 4) * 32 * 8 + kAcc * 4 * 4;
+  static constexpr int kTotal = kStages * kStageBytes + kOutBytes + kBarBytes + kStatBytes + 1024 /*alignment slack*/;
 };
 
 __device__ __forceinline__ float gelu_tanh(float x) {
@@ -131,6 +146,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   uint64_t *full = bars, *empty = bars + kStages, *acc_full = bars + 2 * kStages, *acc_empty = bars + 2 * kStages + kAcc;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 2 * kAcc);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  float2 *stat_slots = reinterpret_cast<float2 *>(out_base + S::kOutBytes + S::kBarBytes);
+  int *stat_cnt = reinterpret_cast<int *>(stat_slots + kAcc * 4 * (kEpiWarps / 4) * 32);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = (g.M + BM - 1) / BM, n_tiles = (g.N + BN - 1) / BN;
@@ -141,6 +158,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { tc::mbar_init(&full[s], 1); tc::mbar_init(&empty[s], 1); }
     for (int a = 0; a < kAcc; ++a) { tc::mbar_init(&acc_full[a], 1); tc::mbar_init(&acc_empty[a], kEpiWarps); }
+    for (int a = 0; a < kAcc * 4; ++a) stat_cnt[a] = 0;
     *abort_flag = 0;
     tc::mbar_fence_init();
   }
@@ -238,6 +256,17 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       tc::tc_fence_after_sync();
       const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
       const int row = m0 + q * 32 + lane;
+      // folded LayerNorm: this thread's row contributes rstd and -mean * rstd to every column
+      float ln_rstd = 1.f, ln_nmr = 0.f;
+      if (g.ln_stats) {
+        const float2 st = row < g.M ? __ldg(g.ln_stats + row) : make_float2(0.f, 0.f);
+        const float mean = st.x * g.ln_inv_k;
+        const float var = fmaxf(fmaf(-mean, mean, st.y * g.ln_inv_k), 0.f);
+        ln_rstd = rsqrtf(var + g.ln_eps);
+        ln_nmr = -mean * ln_rstd;
+      }
+      const uint64_t rstd2 = gpack2(ln_rstd, ln_rstd), nmr2 = gpack2(ln_nmr, ln_nmr);
+      uint64_t tile_sum2 = gpack2(0.f, 0.f), tile_sq2 = gpack2(0.f, 0.f);     // row sums over this warp's tasks of the tile
       // this warp's tasks of the tile: numbers congruent to `sub` modulo kSub, `task` being the tile's first
       for (int c0 = (int)((sub + kSub - task % kSub) % kSub) * 32; c0 < out_cols; c0 += 32 * (int)kSub) {
         float v[32];
@@ -248,7 +277,21 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           tc::tmem_ld_32x32b_x32(t_row + c0, r);
           tc::tmem_ld_32x32b_x32(t_row + BN / 2 + c0, u);
           tc::tmem_ld_wait();
-          if (g.bias) {
+          if (g.ln_stats) {
+            // gate = rstd * acc_g + nmr * s_g + b'_g (likewise up); the host always supplies b' in this mode
+            const float4 *pg = reinterpret_cast<const float4 *>(g.bias + oc0), *pu = reinterpret_cast<const float4 *>(g.bias + g.N / 2 + oc0);
+            const float4 *sg = reinterpret_cast<const float4 *>(g.ln_colsum + oc0), *su = reinterpret_cast<const float4 *>(g.ln_colsum + g.N / 2 + oc0);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float4 a4 = __ldg(pg + j), b4 = __ldg(pu + j), c4 = __ldg(sg + j), d4 = __ldg(su + j);
+              swiglu_pair(gfma2(gpack2(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1])), rstd2, gfma2(gpack2(c4.x, c4.y), nmr2, gpack2(a4.x, a4.y))),
+                          gfma2(gpack2(__uint_as_float(u[4 * j]), __uint_as_float(u[4 * j + 1])), rstd2, gfma2(gpack2(d4.x, d4.y), nmr2, gpack2(b4.x, b4.y))),
+                          v[4 * j], v[4 * j + 1]);
+              swiglu_pair(gfma2(gpack2(__uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])), rstd2, gfma2(gpack2(c4.z, c4.w), nmr2, gpack2(a4.z, a4.w))),
+                          gfma2(gpack2(__uint_as_float(u[4 * j + 2]), __uint_as_float(u[4 * j + 3])), rstd2, gfma2(gpack2(d4.z, d4.w), nmr2, gpack2(b4.z, b4.w))),
+                          v[4 * j + 2], v[4 * j + 3]);
+            }
+          } else if (g.bias) {
             const float4 *pg = reinterpret_cast<const float4 *>(g.bias + oc0);
             const float4 *pu = reinterpret_cast<const float4 *>(g.bias + g.N / 2 + oc0);
 #pragma unroll
@@ -271,7 +314,18 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           tc::tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-          if (g.bias) {
+          if (g.ln_stats) {
+            // v = rstd * acc + (nmr * s + b'); columns past N are never stored, so only the loads are guarded
+            const float4 *bp = reinterpret_cast<const float4 *>(g.bias + oc0), *sp4 = reinterpret_cast<const float4 *>(g.ln_colsum + oc0);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              if (oc0 + 4 * j < g.N) {
+                const float4 b4 = __ldg(bp + j), c4 = __ldg(sp4 + j);
+                gunpack2(gfma2(gpack2(v[4 * j], v[4 * j + 1]), rstd2, gfma2(gpack2(c4.x, c4.y), nmr2, gpack2(b4.x, b4.y))), v[4 * j], v[4 * j + 1]);
+                gunpack2(gfma2(gpack2(v[4 * j + 2], v[4 * j + 3]), rstd2, gfma2(gpack2(c4.z, c4.w), nmr2, gpack2(b4.z, b4.w))), v[4 * j + 2], v[4 * j + 3]);
+              }
+            }
+          } else if (g.bias) {
             const float4 *bp = reinterpret_cast<const float4 *>(g.bias + oc0);
             if (oc0 + 32 <= g.N) {                               // common case: no guards inside the loop
 #pragma unroll
@@ -308,6 +362,17 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j) if (oc0 + j < g.N) v[j] += unpack_in1<F16>(rp + j);
+          }
+        }
+        if (g.stats_out) {
+          // row sums of this task's columns for the LayerNorm that follows (the next projection folds it in)
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            if (oc0 + j < g.N) {
+              const uint64_t v2 = gpack2(v[j], v[j + 1]);
+              tile_sum2 = gadd2(tile_sum2, v2);
+              tile_sq2 = gfma2(v2, v2, tile_sq2);
+            }
           }
         }
         if (g.direct_store) {
@@ -348,6 +413,37 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         obuf ^= 1u;
       }
       task += (uint32_t)(out_cols / 32);
+      if (g.stats_out) {
+        // leave this warp's partial sums in its slot; the last warp of the quadrant to get here adds the slots in a
+        // fixed order.  The slots of an accumulator are free again before its next tile: every epilogue warp arrives
+        // on acc_empty only after this block.
+        float s0, s1, q0, q1;
+        gunpack2(tile_sum2, s0, s1);
+        gunpack2(tile_sq2, q0, q1);
+        float2 *slots = stat_slots + ((size_t)(acc * 4 + q) * kSub) * 32;
+        slots[sub * 32 + lane] = make_float2(s0 + s1, q0 + q1);
+        __threadfence_block();
+        __syncwarp();
+        int last = 0;
+        if (lane == 0) last = atomicAdd(&stat_cnt[acc * 4 + q], 1) == (int)kSub - 1;
+        last = __shfl_sync(0xFFFFFFFFu, last, 0);
+        if (last) {
+          __threadfence_block();
+          float2 tot = make_float2(0.f, 0.f);
+#pragma unroll
+          for (uint32_t w = 0; w < kSub; ++w) { const float2 pw = slots[w * 32 + lane]; tot.x += pw.x; tot.y += pw.y; }
+          if (row < g.M) {
+            if (n_tiles == 1) {
+              g.stats_out[row] = tot;
+            } else {
+              atomicAdd(&g.stats_out[row].x, tot.x);
+              atomicAdd(&g.stats_out[row].y, tot.y);
+            }
+          }
+          __syncwarp();
+          if (lane == 0) stat_cnt[acc * 4 + q] = 0;
+        }
+      }
       tc::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(&acc_empty[acc]);
@@ -377,11 +473,18 @@ static int launch_gemm(const CUtensorMap &ma, const CUtensorMap &mb, const CUten
   return check_launch("gemm_bf16_tcgen05");
 }
 
+struct LinearFusion {
+  const void *ln_stats = nullptr;    // folded LayerNorm: row sums of A, with the column sums of the scaled weight
+  const void *ln_colsum = nullptr;
+  float ln_eps = 1e-5f;
+  void *stats_out = nullptr;         // row sums of the output
+};
+
 // C (nsplit matrices of [M, split_n] with leading dimension split_n, `split_stride` elements apart); dtype 0 = bf16,
 // 1 = fp16 for A, W, residual and C
 int linear_bf16(const void *A, int lda, const void *W, int ldw, const void *bias, const void *residual, int ldr, void *C,
                 long long split_stride, int M, int N, int K, int nsplit, int epilogue, int device, cudaStream_t st, int ksplit = 1,
-                int dtype = 0) {
+                int dtype = 0, LinearFusion fu = LinearFusion()) {
   if (dtype != 0 && dtype != 1) return set_error(F3D_ERR_UNSUPPORTED, "gemm: element type %d (0 = bf16 and 1 = fp16 are supported)", dtype);
   if (M <= 0 || N <= 0 || K <= 0) return set_error(F3D_ERR_ARG, "gemm: M, N, K must be positive (got %d, %d, %d)", M, N, K);
   if (K % 8 || lda % 8 || ldw % 8) return set_error(F3D_ERR_ARG, "gemm: K and the leading dimensions must be multiples of 8 (TMA 16-byte rule)");
@@ -395,12 +498,19 @@ int linear_bf16(const void *A, int lda, const void *W, int ldw, const void *bias
   if (ksplit < 1 || (ksplit > 1 && (epilogue == EPI_SWIGLU || lda != K || ldw != K)))
     return set_error(F3D_ERR_ARG, "gemm: %d slices along K need dense operands and no SwiGLU epilogue", ksplit);
   if ((long long)ksplit * M > 0x7FFFFFFFll) return set_error(F3D_ERR_UNSUPPORTED, "gemm: %d slices of %d rows exceed the copy coordinates", ksplit, M);
+  if (fu.ln_stats && (!fu.ln_colsum || !bias || ksplit != 1 || N % 4))
+    return set_error(F3D_ERR_ARG, "gemm: a folded LayerNorm needs the column sums, the folded bias, one K slice and N %% 4 == 0");
+  if (fu.stats_out && (nsplit != 1 || epilogue == EPI_SWIGLU))
+    return set_error(F3D_ERR_ARG, "gemm: output row sums need a single plain output matrix");
+
   int BN = 256;
   if (epilogue == EPI_SWIGLU) BN = (N % 256 == 0) ? 256 : 128;
   else if (N <= 32) BN = 32;
   else if (N <= 64) BN = 64;
   else if (N <= 128 || (nsplit > 1 && split_n % 256)) BN = 128;
   const int direct = (nsplit > 1 && split_n % 32) ? 1 : 0;      // a 32-column task must not straddle two outputs
+  // rows that span several column tiles add their tiles' sums into a cleared buffer; one tile stores them
+  if (fu.stats_out && N > BN) F3D_CUDA_TRY(cudaMemsetAsync(fu.stats_out, 0, (size_t)M * sizeof(float2), st));
   if (reinterpret_cast<uintptr_t>(C) % 16) return set_error(F3D_ERR_ARG, "gemm: output pointer is not 16-byte aligned");
   CUtensorMap ma, mb, mc;
   F3D_TRY(encode_tmap_2d(&ma, dtype, A, (uint64_t)K, (uint64_t)M * ksplit, (uint64_t)lda * 2, BK, BM, 128));
@@ -409,7 +519,9 @@ int linear_bf16(const void *A, int lda, const void *W, int ldw, const void *bias
   F3D_TRY(encode_tmap_3d(&mc, dtype, C, (uint64_t)split_n, (uint64_t)M, (uint64_t)nsplit, (uint64_t)split_n * 2,
                          (uint64_t)split_stride * 2, 32, 32, 1, 64));
   GemmArgs g{M, N, K, nsplit, split_n, static_cast<const float *>(bias), static_cast<const __nv_bfloat16 *>(residual), ldr,
-             epilogue, direct, static_cast<__nv_bfloat16 *>(C), split_stride, status_word(device), ksplit};
+             epilogue, direct, static_cast<__nv_bfloat16 *>(C), split_stride, status_word(device), ksplit,
+             static_cast<const float2 *>(fu.ln_stats), static_cast<const float *>(fu.ln_colsum), fu.ln_eps, 1.f / (float)K,
+             static_cast<float2 *>(fu.stats_out)};
   if (!g.status) return F3D_ERR_CUDA;
   if (dtype == 1) {
     switch (BN) {
@@ -451,6 +563,20 @@ extern "C" int f3d_linear_dtype(const void *A, const void *W, const void *bias, 
   F3D_TRY(linear_bf16(A, K, W, K, bias, residual, out_n, C, (long long)M * (out_n / (nsplit > 0 ? nsplit : 1)), M, N, K, nsplit,
                       epilogue, device, st, 1, dtype));
   return maybe_sync(st, "linear");
+}
+
+extern "C" int f3d_linear_fused(const void *A, const void *W, const void *bias, const void *residual, void *C, int M, int N,
+                                int K, int nsplit, int epilogue, int dtype, const void *ln_stats, const void *ln_colsum,
+                                float ln_eps, void *stats_out, int device, void *stream) {
+  DeviceGuard guard(device);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  F3D_TRY(maybe_sync(st, "linear_fused"));
+  int out_n = epilogue == EPI_SWIGLU ? N / 2 : N;
+  LinearFusion fu;
+  fu.ln_stats = ln_stats; fu.ln_colsum = ln_colsum; fu.ln_eps = ln_eps; fu.stats_out = stats_out;
+  F3D_TRY(linear_bf16(A, K, W, K, bias, residual, out_n, C, (long long)M * (out_n / (nsplit > 0 ? nsplit : 1)), M, N, K, nsplit,
+                      epilogue, device, st, 1, dtype, fu));
+  return maybe_sync(st, "linear_fused");
 }
 
 extern "C" int f3d_linear_ksplit_bf16(const void *A, const void *W, const void *bias, const void *residual, void *C, int M, int N,

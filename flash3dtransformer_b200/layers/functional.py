@@ -36,6 +36,57 @@ def _fp32_bias(b: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
     return b.detach() if b.dtype == torch.float32 else b.detach().float()
 
 
+_FOLD_CACHE = {}
+
+
+def folded_layernorm(weight, bias, gamma, beta):
+    """(W' bf16 [N, K], s fp32 [N], b' fp32 [N]) for LayerNorm(gamma, beta) followed by y = x W^T + b:
+    W' = W diag(gamma) rounded to bf16, s = row sums of W' as stored, b' = b + W beta.  Cached until one of the four
+    parameters is modified in place."""
+    key = (id(weight), id(gamma))
+    ver = (weight._version, gamma._version, beta._version, bias._version if bias is not None else -1, weight.device)
+    hit = _FOLD_CACHE.get(key)
+    if hit is not None and hit[0] == ver and hit[4] is weight:
+        return hit[1], hit[2], hit[3]
+    with torch.no_grad():
+        w32 = weight.detach().float()
+        wf = (w32 * gamma.detach().float()[None, :]).to(torch.bfloat16).contiguous()
+        s = wf.float().sum(dim=1).contiguous()
+        bf = w32 @ beta.detach().float()
+        if bias is not None:
+            bf = bf + bias.detach().float()
+        bf = bf.contiguous()
+    _FOLD_CACHE[key] = (ver, wf, s, bf, weight)
+    return wf, s, bf
+
+
+def row_stats(x):
+    """fp32 [rows, 2] row sums of a bf16 [rows, C] tensor (for a LayerNorm folded into the next projection)."""
+    stats = torch.empty(x.shape[0], 2, dtype=torch.float32, device=x.device)
+    pshattn.row_stats_bf16(x, stats)
+    return stats
+
+
+def linear_inference(x, weight, bias, residual=None, nsplit=1, epilogue=pshattn.EPI_NONE, ln=None, ln_stats=None,
+                     want_stats=False):
+    """Forward-only projection on the fused GEMM.  `ln` = (gamma, beta, eps) folds that LayerNorm of x into the GEMM
+    (`ln_stats` = row sums of x).  Returns out, or (out, row sums of out) with `want_stats`."""
+    m = x.shape[0]
+    if ln is not None:
+        w, s, b = folded_layernorm(weight, bias, ln[0], ln[1])
+        eps = ln[2]
+    else:
+        w, s, b, eps = bf16_weight(weight), None, _fp32_bias(bias), 1e-5
+    n = w.shape[0]
+    out_n = n // 2 if epilogue == pshattn.EPI_SWIGLU else n
+    shape = (nsplit, m, out_n // nsplit) if nsplit > 1 else (m, out_n)
+    out = torch.empty(shape, dtype=torch.bfloat16, device=x.device)
+    stats = torch.empty(m, 2, dtype=torch.float32, device=x.device) if want_stats else None
+    pshattn.linear_fused(x, w, b, out, residual=residual, nsplit=nsplit, epilogue=epilogue, ln_stats=ln_stats if ln is not None else None,
+                         ln_colsum=s, ln_eps=eps, stats_out=stats)
+    return (out, stats) if want_stats else out
+
+
 class CoordEmbedFn(Function):
     """y = x W^T + b for fp16 coordinates x [rows, 3]: the native embedding kernel (no gradient flows into x)."""
 

@@ -50,11 +50,42 @@ class XFMR(nn.Module):
         if f3ddev.get_nvtx():
             nvtx.range_push(self.NVTX_SCOPE)
         feat = reduced_feat if reduced_feat.dtype == torch.bfloat16 else reduced_feat.to(torch.bfloat16)
-        x = F3.apply_norm(self.norm, feat)
-        mid = self.bwa(x.view(1, n, c), scope_bucks, residual=feat).view(n, c)
-        out = self.mlp(mid, residual=mid)
+        if self._can_fold(feat):
+            out = self._forward_folded(feat, reduced_feat, scope_bucks, n, c)
+        else:
+            x = F3.apply_norm(self.norm, feat)
+            mid = self.bwa(x.view(1, n, c), scope_bucks, residual=feat).view(n, c)
+            out = self.mlp(mid, residual=mid)
         if f3ddev.get_nvtx():
             nvtx.range_pop()
+        return out
+
+    def _can_fold(self, feat) -> bool:
+        """Inference on the GPU with an affine nn.LayerNorm in front of the attention and the SwiGLU MLP: both
+        LayerNorms fold into the projections that follow them."""
+        norm = self.norm
+        return (not torch.is_grad_enabled() and feat.is_cuda and feat.shape[1] % 8 == 0 and isinstance(norm, nn.LayerNorm)
+                and norm.elementwise_affine and norm.bias is not None and tuple(norm.normalized_shape) == (feat.shape[1],)
+                and self.mlp.mlp.activation == "swiglu" and feat.shape[1] <= 2048)
+
+    def _forward_folded(self, feat, given, scope_bucks, n, c):
+        """LN -> QKV, attention, proj + residual, LN -> fc1 (SwiGLU), fc2 + residual as four GEMMs and the attention
+        kernel: no LayerNorm kernel runs.  Each LayerNorm is applied in the epilogue of the projection behind it from the
+        row sums that the projection in front of it accumulated; the sums of this block's output travel with the
+        returned tensor to the next block, and only a block whose input came from elsewhere (embedding, pooling,
+        unpooling) computes them with a pass of its own."""
+        stats = getattr(given, "_f3d_row_stats", None)
+        if stats is None or stats.shape[0] != n:
+            stats = F3.row_stats(feat)
+        bwa, m = self.bwa, self.mlp.mlp
+        qkv = F3.linear_inference(feat, bwa.qkv.weight, bwa.qkv.bias, nsplit=3, ln=(self.norm.weight, self.norm.bias, self.norm.eps),
+                                  ln_stats=stats)
+        attn_out = buck_swin.BuckSwinPackedFunction.apply(qkv, (1, n, bwa.num_heads, bwa.head_dim), scope_bucks, bwa.attn.buck_size)
+        mid, mid_stats = F3.linear_inference(attn_out.view(n, c), bwa.proj.weight, bwa.proj.bias, residual=feat, want_stats=True)
+        h = F3.linear_inference(mid, m.fc1_weight, m.fc1_bias, epilogue=F3.pshattn.EPI_SWIGLU,
+                                ln=(m.layer_norm_weight, m.layer_norm_bias, m.eps), ln_stats=mid_stats)
+        out, out_stats = F3.linear_inference(h, m.fc2_weight, m.fc2_bias, residual=mid, want_stats=True)
+        out._f3d_row_stats = out_stats
         return out
 
 

@@ -40,6 +40,8 @@ PROTOTYPES = {
     "f3d_linear_bf16": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _int, _int, _int, _int, _int, _vp]),
     "f3d_linear_dtype": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _int, _int, _int, _int, _int, _int, _vp]),
     "f3d_buck_swin_fwd_dtype": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _int, _int, _int, _int, _int, _int, _u32, _int, _int, _vp]),
+    "f3d_linear_fused": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _int, _int, _int, _int, _int, _vp, _vp, _f32, _vp, _int, _vp]),
+    "f3d_row_stats_bf16": (_int, [_vp, _vp, _u32, _u32, _int, _vp]),
     "f3d_gemm_sm_bf16": (_int, [_vp, _vp, _vp, _int, _int, _int, _int, _vp]),
     "f3d_buck_swin_fwd": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _int, _int, _int, _int, _int, _int, _u32, _int, _vp]),
     "f3d_layernorm_bf16": (_int, [_vp, _vp, _vp, _vp, _u32, _u32, _f32, _int, _int, _vp]),

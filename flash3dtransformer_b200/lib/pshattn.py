@@ -365,6 +365,50 @@ def linear_bf16(x, weight, bias, out, residual=None, nsplit=1, epilogue=EPI_NONE
 linear = linear_bf16          # the element type follows the tensors
 
 
+def linear_fused(x, weight, bias, out, residual=None, nsplit=1, epilogue=EPI_NONE, ln_stats=None, ln_colsum=None,
+                 ln_eps=1e-5, stats_out=None) -> None:
+    """linear_bf16 with a LayerNorm folded in (`ln_stats` fp32 [M, 2] row sums of x, `weight` already scaled by the
+    LayerNorm weight, `ln_colsum` fp32 [N] its row sums, `bias` fp32 [N] with the LayerNorm bias folded in) and / or the
+    row sums of the output written to `stats_out` fp32 [M, 2] for the LayerNorm that follows.  See f3d_linear_fused."""
+    tensors, names = [x, weight, out], ["x", "weight", "out"]
+    for t, n in ((residual, "residual"),):
+        if t is not None:
+            tensors.append(t); names.append(n)
+    dev = _check_tensors(tensors, names)
+    _require(x.dtype in (torch.bfloat16, torch.float16), f"Tensor x has dtype {x.dtype}; bfloat16 and float16 are supported")
+    _check_dtype(tensors, names, x.dtype)
+    m, k = x.shape
+    n = weight.shape[0]
+    _require(weight.shape[1] == k, f"weight must be [N,{k}], got {tuple(weight.shape)}")
+    out_n = n // 2 if epilogue == EPI_SWIGLU else n
+    _require(out.numel() == m * out_n, f"out must hold {m}x{out_n} elements, got {out.numel()}")
+    _require(residual is None or tuple(residual.shape) == (m, out_n), f"residual must be [{m},{out_n}]")
+    f32 = [t for t in (bias, ln_stats, ln_colsum, stats_out) if t is not None]
+    if f32:
+        _check_tensors(f32, ["fp32 side input"] * len(f32))
+        _check_dtype(f32, ["fp32 side input"] * len(f32), torch.float32)
+    _require(bias is None or bias.numel() == n, f"bias must have {n} elements")
+    if ln_stats is not None:
+        _require(ln_colsum is not None and bias is not None, "a folded LayerNorm needs ln_colsum and the folded bias")
+        _require(ln_stats.numel() == 2 * m and ln_colsum.numel() == n, f"ln_stats must be [{m},2] and ln_colsum [{n}]")
+    _require(stats_out is None or stats_out.numel() == 2 * m, f"stats_out must be [{m},2]")
+    opt = lambda t: _ptr(t) if t is not None else ctypes.c_void_p(0)
+    st = _cabi.load().f3d_linear_fused(_ptr(x), _ptr(weight), opt(bias), opt(residual), _ptr(out), m, n, k, int(nsplit),
+                                       int(epilogue), _FEAT_DTYPES[x.dtype], opt(ln_stats), opt(ln_colsum), float(ln_eps),
+                                       opt(stats_out), _dev_index(dev), _stream(dev))
+    _cabi.check(st, "linear_fused")
+
+
+def row_stats_bf16(x, stats) -> None:
+    """stats fp32 [rows, 2] = (sum, sum of squares) of every row of x bf16 [rows, C]."""
+    dev = _check_tensors([x, stats], ["x", "stats"])
+    _check_dtype([x], ["x"], torch.bfloat16)
+    _check_dtype([stats], ["stats"], torch.float32)
+    _require(x.dim() == 2 and stats.numel() == 2 * x.shape[0], "x must be [rows, C] and stats [rows, 2]")
+    st = _cabi.load().f3d_row_stats_bf16(_ptr(x), _ptr(stats), x.shape[0], x.shape[1], _dev_index(dev), _stream(dev))
+    _cabi.check(st, "row_stats_bf16")
+
+
 def wgrad_supported(n: int, k: int) -> bool:
     """Shapes linear_wgrad_bf16 takes: N a multiple of 8, K = 32 or a multiple of 64."""
     return n % 8 == 0 and (k == 32 or k % 64 == 0)

@@ -214,6 +214,25 @@ int f3d_linear_bf16(const void *A, const void *W, const void *bias, const void *
 int f3d_linear_dtype(const void *A, const void *W, const void *bias, const void *residual, void *C, int M, int N, int K,
                      int nsplit, int epilogue, int dtype, int device, void *stream);
 
+/* f3d_linear_dtype with a LayerNorm folded in and / or row sums of the output written out.  In the reference every
+ * projection of a transformer block is preceded by a LayerNorm kernel of its own (te.LayerNorm / LayerNormMLP,
+ * flash3dxfmr/layers/stage.py:95, flash3dxfmr/layers/elem_wise.py:22-26); here the chain
+ * projection -> LayerNorm -> projection runs as two GEMMs and nothing else:
+ *   stats_out  fp32 [M,2] or NULL: (sum, sum of squares) of every output row (after bias and residual, before the
+ *              rounding to the output type), added up by the epilogue in a fixed order (same bits on every run for
+ *              N <= 512); needs nsplit == 1 and no SwiGLU
+ *   ln_stats   fp32 [M,2] or NULL: (sum, sum of squares) of every row of A over its K channels - the stats_out of the
+ *              GEMM that produced A, or f3d_row_stats_bf16.  With it the call computes LayerNorm(A) W0^T + b0 for a
+ *              LayerNorm with weight gamma and bias beta, given W = W0 diag(gamma) (same element type as A),
+ *              ln_colsum fp32 [N] = row sums of that scaled W as stored, bias fp32 [N] = b0 + W0 beta, ln_eps. */
+int f3d_linear_fused(const void *A, const void *W, const void *bias, const void *residual, void *C, int M, int N, int K,
+                     int nsplit, int epilogue, int dtype, const void *ln_stats, const void *ln_colsum, float ln_eps,
+                     void *stats_out, int device, void *stream);
+
+/* stats fp32 [rows,2] = (sum, sum of squares) over the C channels of every row of x bf16 [rows, C]: the ln_stats input
+ * of f3d_linear_fused for rows that no GEMM of this library produced.  C a multiple of 8, <= 2048. */
+int f3d_row_stats_bf16(const void *x, void *stats, uint32_t rows, uint32_t C, int device, void *stream);
+
 /* replaces f3d::gemm_sm_bf16 (src/psh/gemm_dispatcher.cu:26-80; binding src/f3d_frontend.cu:135): O[M,N] = A[M,K] . B[K,N],
  * bf16 in/out, fp32 accumulation; synchronises the stream like the reference (:77).  Any M; N, K multiples of 8. */
 int f3d_gemm_sm_bf16(const void *A, const void *B, void *O, int M, int N, int K, int device, void *stream);
