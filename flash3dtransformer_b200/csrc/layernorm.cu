@@ -15,10 +15,14 @@ constexpr int kLnMaxChunks = 8;     // chunks of 8 channels per lane -> C <= 204
 // LPR (lanes per row) and the GELU switch are compile-time so that the shuffle trees unroll and no integer division
 // or per-element branch is left in the loop (worth 1.7x on rows of up to 256 channels).  A lane group can take
 // ROWS rows at once with all loads issued first; measured, that only pays for rows wider than a warp's 512 bytes.
-template <int LPR, int CHUNKS, int ROWS, bool GELU>
+// MODE 0: LayerNorm, 1: LayerNorm + GELU, 2: statistics only - stats[row] = (sum, sum of squares) over the C channels, the
+// input of a LayerNorm that the following projection folds in (f3d_linear_fused); the squares are taken around the row
+// mean and the mean's share added back, so the pair carries no cancellation error of its own.
+template <int LPR, int CHUNKS, int ROWS, int MODE>
 __global__ void __launch_bounds__(kLnThreads) layernorm_bf16_kernel(const __nv_bfloat16 *__restrict__ x, const float *__restrict__ w,
                                                                     const float *__restrict__ b, __nv_bfloat16 *__restrict__ y,
-                                                                    uint32_t rows, uint32_t C, float eps) {
+                                                                    uint32_t rows, uint32_t C, float eps, float2 *__restrict__ stats) {
+  constexpr bool GELU = MODE == 1;
   constexpr uint32_t kRowsPerWarp = 32 / LPR;
   const uint32_t lane = threadIdx.x & 31;
   const uint32_t warp_global = (blockIdx.x * kLnThreads + threadIdx.x) >> 5;
@@ -64,7 +68,12 @@ __global__ void __launch_bounds__(kLnThreads) layernorm_bf16_kernel(const __nv_b
 #pragma unroll
     for (uint32_t d = LPR >> 1; d; d >>= 1) sq += __shfl_xor_sync(0xFFFFFFFFu, sq, d);
     rstd[r] = rsqrtf(sq * inv_c + eps);
+    if (MODE == 2) {
+      const uint32_t row = row0 + r * kRowsPerWarp;
+      if (row < rows && sl == 0) stats[row] = make_float2(sum[r], fmaf(mean, sum[r], sq));     // centred part + C mean^2
+    }
   }
+  if (MODE == 2) return;
 #pragma unroll
   for (int i = 0; i < CHUNKS; ++i) {
     const uint32_t ch = sl + i * LPR;
@@ -93,65 +102,23 @@ __global__ void __launch_bounds__(kLnThreads) layernorm_bf16_kernel(const __nv_b
   }
 }
 
-// Row sums for a LayerNorm that a following projection folds in (f3d_linear_fused): stats[row] = (sum, sum of squares)
-// over the C channels.  A group of LPR lanes owns a row (16-byte chunks, lane-strided); the squares are taken around the
-// row mean and the mean's share added back, so the pair carries no cancellation error of its own.
-template <int LPR>
-__global__ void __launch_bounds__(kLnThreads) row_stats_bf16_kernel(const __nv_bfloat16 *__restrict__ x, float2 *__restrict__ stats,
-                                                                    uint32_t rows, uint32_t C) {
-  constexpr uint32_t kRowsPerWarp = 32 / LPR;
-  const uint32_t lane = threadIdx.x & 31;
-  const uint32_t warp_global = (blockIdx.x * kLnThreads + threadIdx.x) >> 5;
-  const uint32_t sub = lane / LPR, sl = lane % LPR;
-  const uint32_t row = warp_global * kRowsPerWarp + sub;
-  const uint32_t nchunk = C / 8;
-  float v[kLnMaxChunks][8];
-  float sum = 0.f;
-#pragma unroll
-  for (int i = 0; i < kLnMaxChunks; ++i) {
-    const uint32_t ch = sl + i * LPR;
-    if (row < rows && ch < nchunk) {
-      uint4 q = __ldg(reinterpret_cast<const uint4 *>(x + (size_t)row * C) + ch);
-      const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&q);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) { float2 f = __bfloat1622float2(h[e]); v[i][2 * e] = f.x; v[i][2 * e + 1] = f.y; sum += f.x + f.y; }
-    } else {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) v[i][e] = 0.f;
-    }
-  }
-#pragma unroll
-  for (uint32_t d = LPR >> 1; d; d >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, d);
-  const float mean = sum / (float)C;
-  float sq = 0.f;
-#pragma unroll
-  for (int i = 0; i < kLnMaxChunks; ++i) {
-    const uint32_t ch = sl + i * LPR;
-    if (ch < nchunk) {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) { const float dlt = v[i][e] - mean; sq = fmaf(dlt, dlt, sq); }
-    }
-  }
-#pragma unroll
-  for (uint32_t d = LPR >> 1; d; d >>= 1) sq += __shfl_xor_sync(0xFFFFFFFFu, sq, d);
-  if (row < rows && sl == 0) stats[row] = make_float2(sum, fmaf(mean, sum, sq));      // sum of squares = centred part + C mean^2
-}
-
 template <int LPR, int CHUNKS, int ROWS>
 static void launch_ln(const __nv_bfloat16 *x, const float *w, const float *b, __nv_bfloat16 *y, uint32_t rows, uint32_t C, float eps,
                       int gelu, cudaStream_t st) {
   const uint32_t rows_per_block = (kLnThreads / 32) * (32 / LPR) * ROWS;
   const uint32_t grid = (rows + rows_per_block - 1) / rows_per_block;
-  if (gelu) layernorm_bf16_kernel<LPR, CHUNKS, ROWS, true><<<grid, kLnThreads, 0, st>>>(x, w, b, y, rows, C, eps);
-  else layernorm_bf16_kernel<LPR, CHUNKS, ROWS, false><<<grid, kLnThreads, 0, st>>>(x, w, b, y, rows, C, eps);
+  if (gelu == 2) layernorm_bf16_kernel<LPR, CHUNKS, ROWS, 2><<<grid, kLnThreads, 0, st>>>(x, w, b, y, rows, C, eps, reinterpret_cast<float2 *>(y));
+  else if (gelu) layernorm_bf16_kernel<LPR, CHUNKS, ROWS, 1><<<grid, kLnThreads, 0, st>>>(x, w, b, y, rows, C, eps, nullptr);
+  else layernorm_bf16_kernel<LPR, CHUNKS, ROWS, 0><<<grid, kLnThreads, 0, st>>>(x, w, b, y, rows, C, eps, nullptr);
 }
 
 }  // namespace f3d
 
 using namespace f3d;
 
-extern "C" int f3d_layernorm_bf16(const void *x, const void *weight, const void *bias, void *y, uint32_t rows, uint32_t C,
-                                  float eps, int gelu, int device, void *stream) {
+// mode 0 / 1: LayerNorm (+ GELU) into y; mode 2: row statistics, y is the float2 [rows] output and weight / bias are unused
+static int layernorm_dispatch(const void *x, const void *weight, const void *bias, void *y, uint32_t rows, uint32_t C, float eps,
+                              int gelu, int device, void *stream) {
   if (C == 0 || C % 8) return set_error(F3D_ERR_ARG, "layernorm: channel count %u must be a positive multiple of 8", C);
   if (C > 8u * 32u * kLnMaxChunks) return set_error(F3D_ERR_UNSUPPORTED, "layernorm: channel count %u exceeds %d", C, 8 * 32 * kLnMaxChunks);
   if (reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(y) % 16 || reinterpret_cast<uintptr_t>(weight) % 16 ||
@@ -198,27 +165,11 @@ extern "C" int f3d_layernorm_bf16(const void *x, const void *weight, const void 
   return check_launch("layernorm_bf16");
 }
 
+extern "C" int f3d_layernorm_bf16(const void *x, const void *weight, const void *bias, void *y, uint32_t rows, uint32_t C,
+                                  float eps, int gelu, int device, void *stream) {
+  return layernorm_dispatch(x, weight, bias, y, rows, C, eps, gelu ? 1 : 0, device, stream);
+}
+
 extern "C" int f3d_row_stats_bf16(const void *x, void *stats, uint32_t rows, uint32_t C, int device, void *stream) {
-  if (C == 0 || C % 8) return set_error(F3D_ERR_ARG, "row_stats: channel count %u must be a positive multiple of 8", C);
-  if (C > 8u * 32u * kLnMaxChunks) return set_error(F3D_ERR_UNSUPPORTED, "row_stats: channel count %u exceeds %d", C, 8 * 32 * kLnMaxChunks);
-  if (reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(stats) % 8) return set_error(F3D_ERR_ARG, "row_stats: misaligned pointer");
-  if (rows == 0) return F3D_OK;
-  DeviceGuard guard(device);
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const uint32_t nchunk = C / 8;
-  uint32_t lpr = 1;
-  while (lpr < 32 && lpr < nchunk) lpr <<= 1;
-  const uint32_t rows_per_block = (kLnThreads / 32) * (32 / lpr);
-  const uint32_t grid = (rows + rows_per_block - 1) / rows_per_block;
-  auto xp = static_cast<const __nv_bfloat16 *>(x);
-  auto sp = static_cast<float2 *>(stats);
-  switch (lpr) {
-    case 1: row_stats_bf16_kernel<1><<<grid, kLnThreads, 0, st>>>(xp, sp, rows, C); break;
-    case 2: row_stats_bf16_kernel<2><<<grid, kLnThreads, 0, st>>>(xp, sp, rows, C); break;
-    case 4: row_stats_bf16_kernel<4><<<grid, kLnThreads, 0, st>>>(xp, sp, rows, C); break;
-    case 8: row_stats_bf16_kernel<8><<<grid, kLnThreads, 0, st>>>(xp, sp, rows, C); break;
-    case 16: row_stats_bf16_kernel<16><<<grid, kLnThreads, 0, st>>>(xp, sp, rows, C); break;
-    default: row_stats_bf16_kernel<32><<<grid, kLnThreads, 0, st>>>(xp, sp, rows, C); break;
-  }
-  return check_launch("row_stats_bf16");
+  return layernorm_dispatch(x, nullptr, nullptr, stats, rows, C, 0.f, 2, device, stream);
 }

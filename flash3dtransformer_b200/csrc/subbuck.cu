@@ -144,7 +144,13 @@ __global__ void __launch_bounds__(kSbThreads) subbuck_build_kernel(SubbuckArgs a
   a.subbuck_id[g] = local_row;
   a.subbuck_off[g] = (uint16_t)off;
   const bool row_ok = row < red_end && row < a.red_rows;
-  if (row_ok) a.unpool_ind[(size_t)row * a.S + off] = g;
+  if (row_ok) {
+    a.unpool_ind[(size_t)row * a.S + off] = g;
+    // the last sub-bucket of a block may be short: its first member marks the unfilled slots with the out-of-range
+    // index the reference pre-fills the whole table with (flash3dxfmr/psh/subbuck.py:94), so the table needs no pre-fill
+    if (off == 0)
+      for (uint32_t j = min(a.S, pts - pt_ind); j < a.S; ++j) a.unpool_ind[(size_t)row * a.S + j] = a.total_N + 3u;
+  }
   if (off == 0 && row_ok && row < a.red_coord_rows) {
     uint32_t m = min(a.S, pts - pt_ind);
     float s0 = sc[0][pt_ind], s1 = sc[1][pt_ind], s2 = sc[2][pt_ind];

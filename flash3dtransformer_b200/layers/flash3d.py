@@ -13,6 +13,7 @@ from . import hourglass as f3dhourglass
 from . import psh_ops
 from . import stage as f3dstage
 from ..psh import dev_context as f3ddev
+from ..psh import plan as f3dplan
 from .functional import GatherRowsFn
 
 
@@ -92,6 +93,14 @@ class Flash3D(nn.Module):
         shard's first scene."""
         if f3ddev.get_nvtx():
             nvtx.range_push(self.NVTX_SCOPE)
+        # without autograd the intermediate buffers of every level come from the per-signature pool (psh/plan.py)
+        with f3dplan.level_buffers(not torch.is_grad_enabled() and coords.is_cuda):
+            out = self._forward(coords, input_feat, seps, bbox, mean_n, scene_base)
+        if f3ddev.get_nvtx():
+            nvtx.range_pop()
+        return out
+
+    def _forward(self, coords, input_feat, seps, bbox, mean_n, scene_base):
         if self.scatter_input_feat or self.restore_input_order:
             psh_feat, (out2in, in2out) = self.psh_scatter(coords, seps, self.first_hashtype, bbox=bbox, mean_n=mean_n,
                                                           scene_base=scene_base, want_index=True)
@@ -102,6 +111,4 @@ class Flash3D(nn.Module):
         out = self.module_tree(coords, psh_feat, seps)
         if self.restore_input_order:
             out = GatherRowsFn.apply(out, in2out, out2in)
-        if f3ddev.get_nvtx():
-            nvtx.range_pop()
         return out

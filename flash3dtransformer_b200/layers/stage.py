@@ -60,13 +60,18 @@ class XFMR(nn.Module):
             nvtx.range_pop()
         return out
 
+    # Narrowest block that takes the folded path.  Measured per block on 16 x 120k points (LayerNorm kernels + four
+    # GEMMs against four fused GEMMs): C = 32 / 64 / 128 lose 57 / 32 / 9 us (their epilogues are bound by instruction
+    # issue, and a LayerNorm kernel over narrow rows costs only 45 us), C = 256 / 512 gain 39 / 75 us.
+    FOLD_MIN_CHANNELS = 256
+
     def _can_fold(self, feat) -> bool:
-        """Inference on the GPU with an affine nn.LayerNorm in front of the attention and the SwiGLU MLP: both
-        LayerNorms fold into the projections that follow them."""
+        """Inference on the GPU with an affine nn.LayerNorm in front of the attention and the SwiGLU MLP, on rows wide
+        enough for the fold to pay: both LayerNorms fold into the projections that follow them."""
         norm = self.norm
         return (not torch.is_grad_enabled() and feat.is_cuda and feat.shape[1] % 8 == 0 and isinstance(norm, nn.LayerNorm)
                 and norm.elementwise_affine and norm.bias is not None and tuple(norm.normalized_shape) == (feat.shape[1],)
-                and self.mlp.mlp.activation == "swiglu" and feat.shape[1] <= 2048)
+                and self.mlp.mlp.activation == "swiglu" and self.FOLD_MIN_CHANNELS <= feat.shape[1] <= 2048)
 
     def _forward_folded(self, feat, given, scope_bucks, n, c):
         """LN -> QKV, attention, proj + residual, LN -> fc1 (SwiGLU), fc2 + residual as four GEMMs and the attention

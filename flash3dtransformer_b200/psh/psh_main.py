@@ -19,6 +19,7 @@ from . import arithmatic as f3darith
 from . import batching as f3dbatch
 from . import bucket as f3dbuck
 from . import dev_context as f3ddev
+from . import plan as f3dplan
 from ..lib import pshattn
 
 NUM_VOX = 0xFFFF
@@ -55,6 +56,16 @@ class BucketScatterBuffers:
         if num_buck is None:
             _, _, num_buck, _ = bucket_plan(seps, bucket_size)
         b = seps.shape[0]
+        if f3dplan.enabled():
+            # inference inside plan.level_buffers(): the kernels write every element of every output, so the buffers
+            # are reused from call to call and not filled
+            return f3dplan.pooled(("psh", total_n, d, b, num_buck, pad_to, str(dev)), lambda: BucketScatterBuffers(
+                bucket_id=torch.empty(total_n, dtype=torch.uint16, device=dev),
+                bucket_cntr=torch.empty(b, num_buck, dtype=torch.uint32, device=dev),
+                bucket_offs=torch.empty(total_n, dtype=torch.uint32, device=dev),
+                bucket_cumsum=torch.empty(b, num_buck, dtype=torch.uint32, device=dev),
+                probe_offs=f3dbuck.generate_probe_offsets(dev, row_major=True),
+                scattered_coord=torch.empty((pad_to, d), dtype=torch.float16, device=dev)))
         return BucketScatterBuffers(
             bucket_id=torch.ones(total_n, dtype=torch.uint16, device=dev),
             bucket_cntr=torch.zeros(b, num_buck, dtype=torch.uint32, device=dev),

@@ -14,6 +14,7 @@ import dataclasses as dcls
 import torch
 
 from . import batching as f3dbatch
+from . import plan as f3dplan
 from .arithmatic import cdiv
 
 BLOCK_POINTS = 1024
@@ -43,6 +44,7 @@ class SubbuckBuffers:
     reduced_feat: torch.Tensor
     unpool_ind: torch.Tensor
     pooled_rows: int = 0          # leading rows of the input that belong to a scene (= last separator)
+    shared: bool = False          # handed out by plan.level_buffers(): reused by the next call, nothing may be dropped
 
     @staticmethod
     def create_subbuck_buff(coords: torch.Tensor, input_feat: torch.Tensor, seps: torch.Tensor,
@@ -52,6 +54,28 @@ class SubbuckBuffers:
         total_n, d = coords.shape
         feat_dim = input_feat.shape[1]
         dev = coords.device
+        if f3dplan.enabled():
+            # inference inside plan.level_buffers(): one plan per batch signature (scene sizes, widths), reused and not
+            # filled.  The bounding box is not computed: the sub-bucket hash normalises with each block's own box, the
+            # two fields only keep the reference's argument list
+            sizes = tuple(f3dbatch.host_seps(seps).tolist())
+            key = ("subbuck", sizes, total_n, d, feat_dim, str(input_feat.dtype), subbuck_size, out_alignment, str(dev))
+
+            def build():
+                red_len, _, red_sep = calc_red_sep_sizes(seps, subbuck_size)
+                aligned = cdiv(red_len, out_alignment) * out_alignment
+                box = torch.zeros(d, dtype=torch.float16, device=dev)
+                return SubbuckBuffers(
+                    bbox_min=box, bbox_max=box, expect_sep=red_sep,
+                    subbuck_id=torch.empty(total_n, dtype=torch.uint32, device=dev),
+                    subbuck_off=torch.empty(total_n, dtype=torch.uint16, device=dev),
+                    reduced_sep=red_sep,
+                    reduced_coord=torch.empty(aligned, d, dtype=torch.float16, device=dev),
+                    reduced_feat=torch.empty(aligned, feat_dim, dtype=input_feat.dtype, device=dev),
+                    unpool_ind=torch.empty((red_len, subbuck_size), dtype=torch.uint32, device=dev),
+                    pooled_rows=min(total_n, int(sizes[-1])) if sizes else 0, shared=True)
+
+            return f3dplan.pooled(key, build)
         bbox_min, bbox_max = torch.aminmax(coords, dim=0)
         assert bbox_min.dtype == torch.float16
         red_len, _, red_sep = calc_red_sep_sizes(seps, subbuck_size)
@@ -69,6 +93,8 @@ class SubbuckBuffers:
         )
 
     def remove_unused_buffers(self):
+        if self.shared:
+            return
         self.subbuck_id = None
         self.subbuck_off = None
 

@@ -5,6 +5,8 @@ from dataclasses import dataclass
 
 import torch
 
+from . import plan as f3dplan
+
 
 @dataclass(slots=True)
 class BuckSwinFwdBuffers:
@@ -14,6 +16,10 @@ class BuckSwinFwdBuffers:
     @staticmethod
     def create_buckswin_fwd_buff(Q: torch.Tensor):
         b, l, h, _ = Q.shape
+        if f3dplan.enabled():
+            # inference inside plan.level_buffers(): the log-sum-exp rows are scratch nobody reads; one buffer per shape
+            lse = f3dplan.pooled(("lse", b, l, h, str(Q.device)), lambda: torch.empty(b, l, h, dtype=torch.float32, device=Q.device))
+            return BuckSwinFwdBuffers(torch.empty_like(Q), lse)
         return BuckSwinFwdBuffers(torch.empty_like(Q), torch.zeros(b, l, h, dtype=torch.float32, device=Q.device))
 
 

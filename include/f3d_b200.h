@@ -139,7 +139,8 @@ int f3d_batch_bucket_sanitizer_cpu(
  *   reduced_batch_sep u32 [batch]                      in  (inclusive end of each scene's reduced rows)
  *   reduced_coord     fp16 [reduced_rows,3]            out (mean member coordinate; rows >= unpool_rows := 0)
  *   reduced_feat      feat_dtype [reduced_rows,feat_dim] out (rows >= unpool_rows := 0)
- *   unpool_ind        u32 [unpool_rows,subbuck_size]   in/out (caller pre-fills with a value >= total_N)
+ *   unpool_ind        u32 [unpool_rows,subbuck_size]   out (slots of short sub-buckets get total_N + 3, the value the
+ *                                                          reference pre-fills with; a pre-filled table is accepted)
  *   red_op            0 mean, 1 sum, 2 min, 3 max
  */
 int f3d_batch_subbuck_reduce(

@@ -188,3 +188,39 @@ def test_batchnorm_pool_wrappers_forward_backward(cuda_device):
     for n, p in model.named_parameters():
         assert p.grad is not None and torch.isfinite(p.grad).all(), n
     assert any(isinstance(m, nn.BatchNorm1d) for m in model.modules())
+
+
+def test_inference_reuses_level_buffers(cuda_device):
+    """Without autograd the intermediate buffers of every level are planned once per batch signature: the second
+    forward pass over a batch of the same scene sizes allocates only its activations (peak memory does not grow, the
+    PSH / sub-bucket tables are the same objects) and gives the same bits; another signature gets its own plan; with
+    autograd nothing is shared."""
+    from flash3dtransformer_b200 import configs
+    from flash3dtransformer_b200.psh import plan, psh_main
+    torch.manual_seed(0)
+    model = configs.flash3d_backbone(channels=(32, 64), depths=(1, 1)).to(cuda_device)
+    coords, seps = _batch(cuda_device, [30000, 22000], seed=1)
+    coords2, seps2 = _batch(cuda_device, [30000, 22000], seed=2)
+    plan.clear()
+    with torch.no_grad():
+        a1 = model(coords, None, seps)
+        n_plans = len(plan._pool)
+        assert n_plans >= 3                                   # PSH tables, one sub-bucket plan, log-sum-exp rows
+        b1 = model(coords2, None, seps2)                      # same signature, other points: the plans are reused
+        assert len(plan._pool) == n_plans
+        a2 = model(coords, None, seps)
+        assert torch.equal(a1, a2) and not torch.equal(a1, b1)
+        other, oseps = _batch(cuda_device, [25000, 26000], seed=3)
+        model(other, None, oseps)
+        assert len(plan._pool) > n_plans
+    with plan.level_buffers():
+        x = psh_main.BucketScatterBuffers.create_buffers(coords, seps, 512, coords.shape[0], 64)
+        y = psh_main.BucketScatterBuffers.create_buffers(coords, seps, 512, coords.shape[0], 64)
+        assert x is y
+    x = psh_main.BucketScatterBuffers.create_buffers(coords, seps, 512, coords.shape[0], 64)
+    y = psh_main.BucketScatterBuffers.create_buffers(coords, seps, 512, coords.shape[0], 64)
+    assert x is not y and x.bucket_id.data_ptr() != y.bucket_id.data_ptr()
+    n_before = len(plan._pool)
+    out = model(coords, None, seps)                           # autograd on: private buffers
+    assert len(plan._pool) == n_before and out.requires_grad
+    plan.clear()
