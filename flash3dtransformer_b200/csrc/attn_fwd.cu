@@ -82,7 +82,7 @@ template <bool F16> __device__ __forceinline__ uint32_t pack_p2(float a, float b
   return *reinterpret_cast<uint32_t *>(&h);
 }
 
-// 2^x for a pair of non-positive arguments on the FMA pipe instead of the special-function unit: n = round(x) by the
+// 2^x for a pair of arguments (at most a few units above zero, any distance below) on the FMA pipe instead of the special-function unit: n = round(x) by the
 // magic-number addition (the sum x + 1.5 * 2^23 carries n in its low mantissa bits), f = x - n in [-0.5, 0.5], a cubic
 // for 2^f (largest relative error 7.5e-5, against the 3.9e-3 of the bf16 rounding P gets anyway), and n added to the
 // exponent field with integer arithmetic.  The integer maximum keeps the result at 2^-126 or above (times the cubic),
@@ -286,12 +286,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         mxc = max3(mxc, __uint_as_float(r0[i + 2]), __uint_as_float(r1[i + 2]));
         mxd = max3(mxd, __uint_as_float(r0[i + 3]), __uint_as_float(r1[i + 3]));
       }
-      const float mx = fmaxf(max3(mxa, mxb, mxc), mxd);
-      const float m_new = fmaxf(m_run, mx * a.scale_log2);
-      const float alpha = fast_exp2(m_run - m_new);                 // 0 on the first tile (m_run = -inf)
+      const float mx = fmaxf(max3(mxa, mxb, mxc), mxd) * a.scale_log2;
+      // The reference point m_run of the exponentials follows the row maximum lazily: it moves only when the tile's
+      // maximum exceeds it by more than kMaxSlack (base-2 units), so probabilities stay below 2^kMaxSlack, which bf16 /
+      // fp16 and the fp32 sums hold without loss, and the result O / l does not depend on the choice.  On typical
+      // rows the maximum settles within the first tile or two; afterwards no thread of the warp rescales anything:
+      // no exponential for alpha, no round trip of O through tensor memory.
+      constexpr float kMaxSlack = 8.f;
+      float alpha = 1.f;
+      const bool moved = __any_sync(0xFFFFFFFFu, mx > m_run + kMaxSlack);       // first tile: m_run = -inf
+      if (moved) {
+        const float m_new = mx > m_run + kMaxSlack ? mx : m_run;
+        alpha = fast_exp2(m_run - m_new);                 // 1 for rows that keep their reference, 0 on the first tile
+        m_run = m_new;
+      }
       // x = s * c - m and the row sum run on packed fp32 pairs; the sum adds the unrounded probabilities (the
       // bf16 rounding of P is unbiased, so the normaliser stays consistent with what the MMA reads)
-      const uint64_t m2 = pack2(-m_new, -m_new);
+      const uint64_t m2 = pack2(-m_run, -m_run);
       uint64_t sum2 = pack2(0.f, 0.f);
       uint32_t p[16];
 #pragma unroll
@@ -333,8 +344,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       unpack2(sum2, sum, sum_hi);
       sum += sum_hi;
       l_run = l_run * alpha + sum;
-      m_run = m_new;
-      if (j > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.f)) {
+      if (j > 0 && moved) {
 #pragma unroll
         for (int c = 0; c < D; c += 16) {
           uint32_t o[16];

@@ -9,6 +9,23 @@
 
 namespace f3d {
 
+// GELU with the error function, x * Phi(x): erf by the five-term rational approximation of Abramowitz & Stegun 7.1.26
+// (one reciprocal, one exponential and six multiply-adds; absolute error of erf below 5e-7, of the result below 5e-7,
+// three orders of magnitude under the bf16 rounding of the output).  The library erff made the fused LayerNorm + GELU
+// compute-bound at a quarter of the memory bandwidth.
+__device__ __forceinline__ float gelu_erf(float x) {
+  const float z = fabsf(x) * 0.7071067811865476f;
+  float t, e;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.3275911f, z, 1.f)));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-z * z * 1.4426950408889634f));
+  float p = fmaf(1.061405429f, t, -1.453152027f);
+  p = fmaf(p, t, 1.421413741f);
+  p = fmaf(p, t, -0.284496736f);
+  p = fmaf(p, t, 0.254829592f);
+  const float erf_abs = fmaf(-p * t, e, 1.f);
+  return 0.5f * x * (1.f + copysignf(erf_abs, x));
+}
+
 constexpr int kLnThreads = 256;
 constexpr int kLnMaxChunks = 8;     // chunks of 8 channels per lane -> C <= 2048
 
@@ -90,7 +107,7 @@ __global__ void __launch_bounds__(kLnThreads) layernorm_bf16_kernel(const __nv_b
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         float t = fmaf(v[r][i][e] * rstd[r], ww[e], bb[e]);
-        if (GELU) t = 0.5f * t * (1.f + erff(t * 0.7071067811865476f));
+        if (GELU) t = gelu_erf(t);
         o[e] = t;
       }
       uint4 q;
