@@ -3,8 +3,11 @@
 //                produced (flash3dxfmr's LayerNormMLP comes from TransformerEngine with activation "swiglu",
 //                flash3dxfmr/layers/elem_wise.py; its backward is TransformerEngine's):
 //                    d_gate = g * up * s * (1 + gate * (1 - s)),  d_up = g * gate * s,  s = sigmoid(gate)
+//   gelu_bwd     gradient of out = gelu(y) with respect to y, exact (error function; the LayerNorm + GELU of the pooling
+//                and unpooling wrappers, flash3dxfmr/layers/hourglass.py:101-103, 181-185) or tanh form (the GELU
+//                epilogue of the projection GEMM)
 //   colsum       bias gradient: fp32 column sums of a bf16 [rows, C] matrix, added in a fixed order
-// Both are HBM-bound streams: 16-byte loads and stores, one thread per 8 channels.
+// All are HBM-bound streams: 16-byte loads and stores, one thread per 8 channels.
 #include "f3d_common.cuh"
 #include "../../include/f3d_b200.h"
 
@@ -33,6 +36,34 @@ __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const __nv_bfloat16 *__
   }
   *(reinterpret_cast<uint4 *>(dy + r * 2 * F) + c) = wg;
   *(reinterpret_cast<uint4 *>(dy + r * 2 * F + F) + c) = wu;
+}
+
+template <bool TANH> __device__ __forceinline__ float gelu_grad(float x) {
+  if (TANH) {
+    // gelu(x) = x/2 (1 + tanh(u)), u = k (x + 0.044715 x^3), k = sqrt(2/pi)
+    const float k = 0.7978845608028654f, x2 = x * x;
+    const float t = tanhf(k * x * fmaf(0.044715f, x2, 1.f));
+    return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * k * fmaf(3.f * 0.044715f, x2, 1.f);
+  }
+  // gelu(x) = x Phi(x): Phi(x) + x phi(x)
+  return 0.5f * (1.f + erff(x * 0.7071067811865476f)) + x * 0.3989422804014327f * __expf(-0.5f * x * x);
+}
+
+template <bool TANH>
+__global__ void __launch_bounds__(256) gelu_bwd_kernel(const __nv_bfloat16 *__restrict__ y, const __nv_bfloat16 *__restrict__ g,
+                                                       __nv_bfloat16 *__restrict__ dy, size_t chunks) {
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= chunks) return;
+  const uint4 qy = __ldg(reinterpret_cast<const uint4 *>(y) + idx), qg = __ldg(reinterpret_cast<const uint4 *>(g) + idx);
+  const __nv_bfloat162 *hy = reinterpret_cast<const __nv_bfloat162 *>(&qy), *hg = reinterpret_cast<const __nv_bfloat162 *>(&qg);
+  uint4 w;
+  __nv_bfloat162 *o = reinterpret_cast<__nv_bfloat162 *>(&w);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 a = __bfloat1622float2(hy[e]), b = __bfloat1622float2(hg[e]);
+    o[e] = __floats2bfloat162_rn(b.x * gelu_grad<TANH>(a.x), b.y * gelu_grad<TANH>(a.y));
+  }
+  *(reinterpret_cast<uint4 *>(dy) + idx) = w;
 }
 
 // partial[b][c] = sum over the rows of block b; blocks stride over the rows
@@ -112,6 +143,23 @@ extern "C" int f3d_swiglu_bwd_bf16(const void *pre_act, const void *grad_out, vo
   swiglu_bwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(pre_act), static_cast<const __nv_bfloat16 *>(grad_out),
                                                                 static_cast<__nv_bfloat16 *>(grad_pre_act), (size_t)rows, F);
   return check_launch("swiglu_bwd_bf16");
+}
+
+extern "C" int f3d_gelu_bwd_bf16(const void *pre_act, const void *grad_out, void *grad_pre_act, uint64_t elems, int tanh_form,
+                                 int device, void *stream) {
+  if (elems % 8) return set_error(F3D_ERR_ARG, "gelu_bwd: element count %llu must be a multiple of 8", (unsigned long long)elems);
+  if (reinterpret_cast<uintptr_t>(pre_act) % 16 || reinterpret_cast<uintptr_t>(grad_out) % 16 || reinterpret_cast<uintptr_t>(grad_pre_act) % 16)
+    return set_error(F3D_ERR_ARG, "gelu_bwd: pointers must be 16-byte aligned");
+  if (elems == 0) return F3D_OK;
+  DeviceGuard guard(device);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const size_t n = (size_t)(elems / 8);
+  if ((n + 255) / 256 > 0x7FFFFFFFull) return set_error(F3D_ERR_UNSUPPORTED, "gelu_bwd: tensor too large");
+  const unsigned grid = (unsigned)((n + 255) / 256);
+  const __nv_bfloat16 *y = static_cast<const __nv_bfloat16 *>(pre_act), *g = static_cast<const __nv_bfloat16 *>(grad_out);
+  if (tanh_form) gelu_bwd_kernel<true><<<grid, 256, 0, st>>>(y, g, static_cast<__nv_bfloat16 *>(grad_pre_act), n);
+  else gelu_bwd_kernel<false><<<grid, 256, 0, st>>>(y, g, static_cast<__nv_bfloat16 *>(grad_pre_act), n);
+  return check_launch("gelu_bwd_bf16");
 }
 
 extern "C" int f3d_colsum_bf16(const void *x, void *out, uint64_t rows, uint32_t C, int device, void *stream) {

@@ -101,8 +101,11 @@ class CoordEmbedFn(Function):
     @staticmethod
     def backward(ctx, g):
         (x,) = ctx.saved_tensors
-        gf = g.float()
-        return None, (gf.t() @ x.float()).to(ctx.dtypes[0]), gf.sum(0).to(ctx.dtypes[1])
+        gb16 = (g if g.dtype == torch.bfloat16 else g.to(torch.bfloat16)).contiguous()
+        gw = torch.empty(gb16.shape[1], 3, dtype=torch.float32, device=g.device)
+        gb = torch.empty(gb16.shape[1], dtype=torch.float32, device=g.device)
+        pshattn.coord_embed_bwd(x.contiguous(), gb16, gw, gb)
+        return None, gw.to(ctx.dtypes[0]), gb.to(ctx.dtypes[1])
 
 
 # Largest weight (elements) whose gradient goes to the native kernel: above it the output tiles outnumber the SMs, the
@@ -187,10 +190,12 @@ class LinearFn(Function):
             pshattn.swiglu_bwd_bf16(y, g if g.dtype == torch.bfloat16 else g.to(torch.bfloat16), gy)
             g = gy
         elif epilogue == pshattn.EPI_GELU:
-            y = (torch.addmm(bias.to(wb.dtype), xb, wb.t()) if bias is not None else xb @ wb.t()).float().requires_grad_(True)
-            with torch.enable_grad():
-                z = torch.nn.functional.gelu(y, approximate="tanh")
-            g = torch.autograd.grad(z, y, g.float())[0].to(wb.dtype)
+            # the same for the tanh-form GELU epilogue
+            y = torch.empty(xb.shape[0], wb.shape[0], dtype=torch.bfloat16, device=xb.device)
+            pshattn.linear_bf16(xb, wb, _fp32_bias(bias), y)
+            gy = torch.empty_like(y)
+            pshattn.gelu_bwd_bf16(y, g if g.dtype == torch.bfloat16 else g.to(torch.bfloat16), gy, tanh_form=True)
+            g = gy
         # gx = g W: the native GEMM computes A B^T, so W^T ([in, out], a small matrix) is materialised
         gx = torch.empty(g.shape[0], wb.shape[1], dtype=torch.bfloat16, device=g.device)
         pshattn.linear_bf16(g, wb.t().contiguous(), None, gx)
@@ -240,7 +245,9 @@ class LayerNormFn(Function):
             if gelu:
                 y = torch.empty_like(xb)
                 pshattn.layernorm_bf16(xb, weight.detach().float().contiguous(), bias.detach().float().contiguous(), y, eps, False)
-                gb16 = torch.ops.aten.gelu_backward(gb16, y, approximate="none")
+                gy = torch.empty_like(y)
+                pshattn.gelu_bwd_bf16(y, gb16, gy, tanh_form=False)
+                gb16 = gy
             gx = torch.empty_like(xb)
             gw = torch.empty(xb.shape[1], dtype=torch.float32, device=xb.device)
             gb = torch.empty_like(gw)

@@ -49,6 +49,8 @@ PROTOTYPES = {
     "f3d_layernorm_bwd_bf16": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _f32, _int, _vp]),
     "f3d_swiglu_bwd_bf16": (_int, [_vp, _vp, _vp, c_uint64, _u32, _int, _vp]),
     "f3d_colsum_bf16": (_int, [_vp, _vp, c_uint64, _u32, _int, _vp]),
+    "f3d_gelu_bwd_bf16": (_int, [_vp, _vp, _vp, c_uint64, _int, _int, _vp]),
+    "f3d_coord_embed_bwd": (_int, [_vp, _vp, _vp, _vp, _u32, _u32, _int, _vp]),
     "f3d_linear_wgrad_bf16": (_int, [_vp, _vp, _vp, _vp, _int, _int, _int, _int, _vp]),
     "f3d_linear_ksplit_bf16": (_int, [_vp, _vp, _vp, _vp, _vp, _int, _int, _int, _int, _int, _vp]),
     "f3d_collate_points_f32": (_int, [_vp, _vp, _vp, c_uint64, _u32, _int, _vp]),

@@ -524,6 +524,17 @@ def swiglu_bwd_bf16(pre_act, grad_out, grad_pre_act) -> None:
     _cabi.check(st, "swiglu_bwd_bf16")
 
 
+def gelu_bwd_bf16(pre_act, grad_out, grad_pre_act, tanh_form: bool = False) -> None:
+    """grad_pre_act = grad_out * gelu'(pre_act), all bf16 of one shape: the exact (error function) form, or the tanh form
+    of the GEMM's GELU epilogue.  Not part of the reference's operator module (its GELU backward is torch autograd's)."""
+    dev = _check_tensors([pre_act, grad_out, grad_pre_act], ["pre_act", "grad_out", "grad_pre_act"])
+    _check_dtype([pre_act, grad_out, grad_pre_act], ["pre_act", "grad_out", "grad_pre_act"], torch.bfloat16)
+    _require(pre_act.shape == grad_out.shape == grad_pre_act.shape, "pre_act, grad_out and grad_pre_act must have one shape")
+    st = _cabi.load().f3d_gelu_bwd_bf16(_ptr(pre_act), _ptr(grad_out), _ptr(grad_pre_act), pre_act.numel(), int(bool(tanh_form)),
+                                        _dev_index(dev), _stream(dev))
+    _cabi.check(st, "gelu_bwd_bf16")
+
+
 def colsum_bf16(x, out) -> None:
     """out fp32 [C] = sum over the rows of x bf16 [rows, C] (the bias gradient of a projection), in a fixed order."""
     dev = _check_tensors([x, out], ["x", "out"])
@@ -547,6 +558,23 @@ def coord_embed_bf16(coords, weight, bias, out) -> None:
     st = _cabi.load().f3d_coord_embed_bf16(_ptr(coords), _ptr(weight), _ptr(bias), _ptr(out), coords.shape[0], weight.shape[0],
                                            _dev_index(dev), _stream(dev))
     _cabi.check(st, "coord_embed_bf16")
+
+
+def coord_embed_bwd(coords, grad_out, grad_weight, grad_bias=None) -> None:
+    """grad_weight fp32 [C, 3] = grad_out^T coords, grad_bias fp32 [C] = column sums of grad_out, for fp16 coords [rows, 3]
+    and bf16 grad_out [rows, C]; fixed summation order.  Not part of the reference's operator module."""
+    ts = [coords, grad_out, grad_weight] + ([grad_bias] if grad_bias is not None else [])
+    dev = _check_tensors(ts, ["coords", "grad_out", "grad_weight", "grad_bias"][:len(ts)])
+    _check_dtype([coords], ["coords"], torch.float16)
+    _check_dtype([grad_out], ["grad_out"], torch.bfloat16)
+    _check_dtype(ts[2:], ["grad_weight", "grad_bias"][:len(ts) - 2], torch.float32)
+    _require(coords.dim() == 2 and coords.shape[1] == 3 and grad_out.dim() == 2 and grad_out.shape[0] == coords.shape[0],
+             "coords must be [rows, 3] and grad_out [rows, C]")
+    _require(tuple(grad_weight.shape) == (grad_out.shape[1], 3), "grad_weight must be [C, 3]")
+    _require(grad_bias is None or grad_bias.numel() == grad_out.shape[1], "grad_bias must be [C]")
+    st = _cabi.load().f3d_coord_embed_bwd(_ptr(coords), _ptr(grad_out), _ptr(grad_weight), _ptr(grad_bias) if grad_bias is not None else None,
+                                          coords.shape[0], grad_out.shape[1], _dev_index(dev), _stream(dev))
+    _cabi.check(st, "coord_embed_bwd")
 
 
 def collate_points_f32(records, coords, extra=None) -> None:

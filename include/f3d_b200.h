@@ -277,6 +277,13 @@ int f3d_layernorm_bwd_bf16(const void *x, const void *grad_out, const void *weig
 int f3d_swiglu_bwd_bf16(const void *pre_act, const void *grad_out, void *grad_pre_act, uint64_t rows, uint32_t F, int device,
                         void *stream);
 
+/* Backward of out = gelu(y): grad_pre_act = grad_out * gelu'(pre_act), all bf16 with `elems` elements (a multiple of 8).
+ * tanh_form = 0: the exact form (error function) of the LayerNorm + GELU in the reference's pooling / unpooling wrappers
+ * (flash3dxfmr/layers/hourglass.py:101-103, 181-185), whose backward the reference takes from torch autograd;
+ * tanh_form = 1: the tanh form that the GELU epilogue of f3d_linear_bf16 computes. */
+int f3d_gelu_bwd_bf16(const void *pre_act, const void *grad_out, void *grad_pre_act, uint64_t elems, int tanh_form, int device,
+                      void *stream);
+
 /* Bias gradient: out fp32 [C] = column sums of x bf16 [rows, C], added in a fixed order.  C a multiple of 8. */
 int f3d_colsum_bf16(const void *x, void *out, uint64_t rows, uint32_t C, int device, void *stream);
 
@@ -285,6 +292,12 @@ int f3d_colsum_bf16(const void *x, void *out, uint64_t rows, uint32_t C, int dev
  * of 8, <= 2048. */
 int f3d_coord_embed_bf16(const void *coords, const void *weight, const void *bias, void *out, uint32_t rows, uint32_t C,
                          int device, void *stream);
+
+/* Parameter gradients of the coordinate embedding: grad_weight fp32 [C, 3] = grad_out^T coords and grad_bias fp32 [C]
+ * (may be NULL) = column sums of grad_out, for fp16 coords [rows, 3] and bf16 grad_out [rows, C]; sums added in a fixed
+ * order.  The reference gets them from te.Linear's backward (flash3dxfmr/layers/psh_ops.py:62,77). */
+int f3d_coord_embed_bwd(const void *coords, const void *grad_out, void *grad_weight, void *grad_bias, uint32_t rows, uint32_t C,
+                        int device, void *stream);
 
 /* Weight and bias gradient of a projection y = x W^T + b: grad_weight fp32 [N, K] = grad_out^T x and, when grad_bias is
  * not NULL, grad_bias fp32 [N] = column sums of grad_out, for grad_out bf16 [M, N] and x bf16 [M, K] (both dense).  One

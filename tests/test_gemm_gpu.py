@@ -148,6 +148,68 @@ def test_swiglu_backward(cuda_device, rows, f):
     assert ((out.float() - ref).abs() <= ref.abs() * 2.0 ** -7 + 1e-3).all()
 
 
+@pytest.mark.parametrize("rows,c,tanh_form", [(1, 8, False), (1000, 128, False), (4097, 256, True), (333, 2048, True), (70001, 32, False)])
+def test_gelu_backward(cuda_device, rows, c, tanh_form):
+    """Gradient of gelu(y) (exact and tanh form) against fp32 autograd; the output is one bf16 rounding away."""
+    from flash3dtransformer_b200.lib import pshattn
+    g = torch.Generator(cuda_device).manual_seed(rows + c)
+    y = (torch.randn(rows, c, device=cuda_device, generator=g) * 2).bfloat16()
+    go = torch.randn(rows, c, device=cuda_device, generator=g).bfloat16()
+    out = torch.full_like(y, float("nan"))
+    pshattn.gelu_bwd_bf16(y, go, out, tanh_form=tanh_form)
+    yf = y.float().requires_grad_(True)
+    z = torch.nn.functional.gelu(yf, approximate="tanh" if tanh_form else "none")
+    ref, = torch.autograd.grad(z, yf, go.float())
+    assert torch.isfinite(out.float()).all()
+    assert ((out.float() - ref).abs() <= ref.abs() * 2.0 ** -7 + 1e-3).all()
+
+
+@pytest.mark.parametrize("rows,c", [(1, 32), (1000, 32), (70001, 64), (4096, 512), (513, 2048), (300000, 32)])
+def test_coord_embed_backward(cuda_device, rows, c):
+    """Parameter gradients of the 3 -> C embedding against float64 sums; same bits on a second run; and through autograd
+    of the layer function."""
+    from flash3dtransformer_b200.lib import pshattn
+    from flash3dtransformer_b200.layers.functional import CoordEmbedFn
+    g = torch.Generator(cuda_device).manual_seed(rows + c)
+    x = (torch.randn(rows, 3, device=cuda_device, generator=g) * 20).half()
+    go = torch.randn(rows, c, device=cuda_device, generator=g).bfloat16()
+    gw = torch.full((c, 3), float("nan"), device=cuda_device)
+    gb = torch.full((c,), float("nan"), device=cuda_device)
+    pshattn.coord_embed_bwd(x, go, gw, gb)
+    ref_w = go.double().t() @ x.double()
+    ref_b = go.double().sum(0)
+    scale_w = (go.float().abs().t() @ x.float().abs()).max().item()
+    assert (gw.double() - ref_w).abs().max().item() <= 1e-5 * scale_w + 1e-6
+    assert (gb.double() - ref_b).abs().max().item() <= 1e-5 * go.float().abs().sum(0).max().item() + 1e-6
+    gw2, gb2 = torch.empty_like(gw), torch.empty_like(gb)
+    pshattn.coord_embed_bwd(x, go, gw2, gb2)
+    assert torch.equal(gw, gw2) and torch.equal(gb, gb2)
+    w = (torch.randn(c, 3, device=cuda_device, generator=g) * 0.5).requires_grad_(True)
+    b = torch.randn(c, device=cuda_device, generator=g).requires_grad_(True)
+    CoordEmbedFn.apply(x, w, b).backward(go)
+    assert torch.equal(w.grad, gw) and torch.equal(b.grad, gb)
+
+
+def test_gelu_linear_gradients(cuda_device):
+    """LinearFn with the GELU epilogue: input, weight and bias gradients against fp32 autograd."""
+    from flash3dtransformer_b200.layers.functional import LinearFn
+    from flash3dtransformer_b200.lib import pshattn
+    g = torch.Generator(cuda_device).manual_seed(23)
+    x = torch.randn(2048, 64, device=cuda_device, generator=g).bfloat16().requires_grad_(True)
+    w = (torch.randn(128, 64, device=cuda_device, generator=g) / 8).requires_grad_(True)
+    b = (torch.randn(128, device=cuda_device, generator=g) * 0.1).requires_grad_(True)
+    y = LinearFn.apply(x, w, b, None, 1, pshattn.EPI_GELU)
+    gy = torch.randn(2048, 128, device=cuda_device, generator=g).bfloat16()
+    y.backward(gy)
+    xr = x.detach().float().requires_grad_(True)
+    wr = w.detach().bfloat16().float().requires_grad_(True)
+    br = b.detach().clone().requires_grad_(True)
+    torch.nn.functional.gelu(xr @ wr.t() + br, approximate="tanh").backward(gy.float())
+    _check(x.grad, xr.grad)
+    assert (w.grad - wr.grad).abs().max().item() <= 2e-2 * wr.grad.abs().max().item() + 1e-2
+    assert (b.grad - br.grad).abs().max().item() <= 2e-2 * br.grad.abs().max().item() + 1e-2
+
+
 @pytest.mark.parametrize("rows,c", [(1, 8), (1000, 96), (70001, 32), (5000, 2048), (63, 512), (3000, 4096), (777, 2056)])
 def test_colsum(cuda_device, rows, c):
     from flash3dtransformer_b200.lib import pshattn

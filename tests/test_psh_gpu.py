@@ -147,6 +147,41 @@ def test_full_size_properties(cuda_device):
     _compare(out, _oracle(c16, seps, nb, div, 512, 2, pad_to))
 
 
+def test_pooling_bench_configuration_bit_exact(cuda_device):
+    """The PSH + pooling configuration at its full size: 8 heavy-tailed scenes of 1,000,000 points, bucket 2048,
+    Z-order hash.  Every PSH output equals the CPU oracle bit for bit (about a minute of oracle time), then the
+    sub-bucket build and a stride-2 sum pooling of fp32 features on the scattered coordinates equal the pooling oracle."""
+    from oracle import pool_oracle as pl
+    from flash3dtransformer_b200.lib import pshattn
+    from flash3dtransformer_b200.psh import subbuck as sbm
+    sizes = [1_000_000] * 8
+    coords32, seps = synthetic.batch(synthetic.zipf_voxels, sizes, seed=0)
+    c16 = coords32.astype(np.float16)
+    n = c16.shape[0]
+    nb, div, out = _gpu_scatter(cuda_device, c16, seps, 2048, 1, n)
+    assert nb == 512
+    _compare(out, _oracle(c16, seps, nb, div, 2048, 1, n))
+    po.scoreboard_check(out["bucket_id"], out["bucket_cntr"], out["bucket_offs"], seps, nb)
+    sc16 = out["scattered_coord"]
+    C = 32
+    feat32 = np.random.default_rng(1).normal(size=(n, C)).astype(np.float32)
+    coords = torch.from_numpy(sc16).to(cuda_device)
+    feat = torch.from_numpy(feat32).to(cuda_device)
+    sp = torch.from_numpy(np.asarray(seps, dtype=np.uint32)).to(cuda_device)
+    sb = sbm.SubbuckBuffers.create_subbuck_buff(coords, feat, sp, 2)
+    pshattn.batch_subbuck_reduce(coords, feat, sp, max(sizes), 2, 0xFFFF, sb.bbox_min, sb.bbox_max, sb.subbuck_id,
+                                 sb.subbuck_off, sb.reduced_sep, sb.reduced_coord, sb.reduced_feat, sb.unpool_ind, 1, 1)
+    torch.cuda.synchronize()
+    sid, soff, unpool, rcoord, red_sep = pl.subbuck_build(sc16, seps, 2, red_rows_aligned=sb.reduced_coord.shape[0])
+    assert np.array_equal(sb.reduced_sep.cpu().numpy().astype(np.int64), red_sep)
+    assert np.array_equal(sb.subbuck_id.cpu().numpy(), sid)
+    assert np.array_equal(sb.subbuck_off.cpu().numpy(), soff)
+    assert np.array_equal(sb.unpool_ind.cpu().numpy(), unpool)
+    assert np.array_equal(sb.reduced_coord.cpu().numpy().view(np.uint16), rcoord.view(np.uint16))
+    exp = pl.pool_reduce(feat32, unpool, n, 1, sb.reduced_feat.shape[0], "fp32")
+    assert np.array_equal(sb.reduced_feat.cpu().numpy(), exp)
+
+
 def test_scene_sharded_run_reproduces_full_batch(cuda_device):
     """Two 'ranks' (run one after the other on this GPU) that get the global bounding box, mean scene size and the
     global index of their first scene produce, scene by scene, the bits of the unsharded run."""
