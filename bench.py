@@ -443,10 +443,51 @@ def run_extras(args, rank: int, world: int, local_rank: int):
         pp.steps, pp.warmup, pp.points = 5, 3, POINTS_PER_SCENE
         res["psh_pool"] = psh_pool_measure(pp)
         torch.cuda.empty_cache()
+        res["graphed_forward"] = graphed_forward_measure(local_rank)
+        torch.cuda.empty_cache()
     if world > 1:
         dist.barrier()
     res["seconds"] = time.perf_counter() - t0
     return res if rank == 0 else None
+
+
+def graphed_forward_measure(local_rank: int):
+    """The backbone forward of ONE 20,000-point scan (the size of the CPU-runnable configuration), issued kernel by kernel
+    and replayed as one CUDA graph (flash3dtransformer_b200.graph.GraphedForward): at this size the host's launches take
+    longer than the kernels.  Latency per forward, device-timed, coordinates already on the device."""
+    from flash3dtransformer_b200 import graph
+    from flash3dtransformer_b200.psh import batching
+    dev = torch.device(f"cuda:{local_rank}")
+    model = build_model(dev)
+    c16, seps = make_batch(0, 1, 20_000)
+    coords = torch.from_numpy(c16).to(dev)
+    host = torch.from_numpy(seps)
+    seps_dev = batching.attach_host_seps(host.to(dev), host)
+
+    def eager():
+        with torch.no_grad():
+            return model(coords, None, seps_dev)
+
+    def timed(fn, n=30, warm=3):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    ms_eager = timed(eager)
+    ref = eager().clone()
+    gf = graph.GraphedForward(model, coords, seps_dev)
+    ms_graph = timed(lambda: gf(coords))
+    same = bool(torch.equal(gf(coords), ref))
+    torch.cuda.synchronize()
+    return {"workload": "backbone forward, 1 scan x 20,000 points", "ms_per_forward_eager": ms_eager,
+            "ms_per_forward_graph": ms_graph, "points_per_s_graph": 20_000 / (ms_graph * 1e-3), "same_bits": same}
 
 
 def strong_scaling_measure(args, rank: int, world: int, local_rank: int):

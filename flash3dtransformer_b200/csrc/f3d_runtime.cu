@@ -7,6 +7,7 @@
 #include <mutex>
 #include <map>
 #include <atomic>
+#include <vector>
 
 namespace f3d {
 
@@ -33,7 +34,7 @@ int set_error(int code, const char *fmt, ...) {
 bool sync_flag() { return g_sync.load() != 0; }
 uint64_t seed() { return g_seed.load(); }
 
-struct Slot { void *ptr = nullptr; size_t bytes = 0; unsigned long long last_use = 0; };
+struct Slot { void *ptr = nullptr; size_t bytes = 0; unsigned long long last_use = 0; bool in_graph = false; };
 struct SlotKey {
   int device, slot;
   cudaStream_t stream;
@@ -46,6 +47,8 @@ struct SlotKey {
 static std::mutex g_ws_mu;
 static std::map<SlotKey, Slot> g_ws;
 static unsigned long long g_ws_clock = 0;
+// blocks that a captured CUDA graph refers to and that were later outgrown: kept until f3d_release_workspaces
+static std::vector<std::pair<int, void *>> g_ws_retired;
 // blocks kept per (device, slot) before the least recently used one is given back: streams come and go, and a
 // handle value may belong to a stream that no longer exists
 constexpr int kMaxStreamsPerSlot = 8;
@@ -53,14 +56,28 @@ constexpr int kMaxStreamsPerSlot = 8;
 int workspace(int device, int slot, size_t bytes, cudaStream_t stream, void **out) {
   std::lock_guard<std::mutex> lk(g_ws_mu);
   const SlotKey key{device, slot, stream};
+  // A call recorded into a CUDA graph bakes the block's address into the graph: the block must exist already (nothing
+  // may be allocated while a stream is capturing) and is from then on neither evicted nor freed when outgrown.
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (stream != nullptr) F3D_CUDA_TRY(cudaStreamIsCapturing(stream, &cap));
+  const bool capturing = cap != cudaStreamCaptureStatusNone;
   auto it = g_ws.find(key);
+  if (capturing) {
+    if (it == g_ws.end() || it->second.bytes < bytes)
+      return set_error(F3D_ERR_UNSUPPORTED, "scratch block %d would have to be allocated while the stream is capturing: run the same "
+                       "calls once on this stream before the capture", slot);
+    it->second.in_graph = true;
+    it->second.last_use = ++g_ws_clock;
+    *out = it->second.ptr;
+    return F3D_OK;
+  }
   if (it == g_ws.end()) {
     // a new stream for this slot: evict the least recently used block when the slot holds too many.  Its stream may
     // be gone, so nothing stream-specific is called on it; cudaFree waits for all work of the device by itself.
     int held = 0;
     auto lru = g_ws.end();
     for (auto jt = g_ws.begin(); jt != g_ws.end(); ++jt)
-      if (jt->first.device == device && jt->first.slot == slot) {
+      if (jt->first.device == device && jt->first.slot == slot && !jt->second.in_graph) {
         ++held;
         if (lru == g_ws.end() || jt->second.last_use < lru->second.last_use) lru = jt;
       }
@@ -75,7 +92,10 @@ int workspace(int device, int slot, size_t bytes, cudaStream_t stream, void **ou
   if (s.bytes < bytes) {
     // round up so that slowly growing requests do not reallocate every call
     size_t want = bytes + bytes / 4 + 4096;
-    if (s.ptr) {
+    if (s.ptr && s.in_graph) {
+      g_ws_retired.emplace_back(device, s.ptr);          // a graph may still be replayed with this address
+      s.ptr = nullptr; s.bytes = 0; s.in_graph = false;
+    } else if (s.ptr) {
       // only kernels queued on this stream can still be using the old block
       F3D_CUDA_TRY(cudaStreamSynchronize(stream));
       F3D_CUDA_TRY(cudaFree(s.ptr));
@@ -140,6 +160,8 @@ void workspace_release_all() {
     if (kv.second.ptr) { cudaSetDevice(kv.first.device); cudaFree(kv.second.ptr); }
   }
   g_ws.clear();
+  for (auto &r : g_ws_retired) { cudaSetDevice(r.first); cudaFree(r.second); }
+  g_ws_retired.clear();
   if (prev >= 0) cudaSetDevice(prev);
 }
 

@@ -13,7 +13,11 @@
  *    it from a grow-only workspace that the library keeps per (device, stream): calls on different streams use
  *    different blocks and may overlap; calls on one stream are ordered by the stream.  As for any CUDA stream, two host
  *    threads must not issue calls on the same stream concurrently.  A block that has to grow waits for its own stream
- *    only and calls cudaFree / cudaMalloc; f3d_release_workspaces frees every block (call it with the device idle);
+ *    only and calls cudaFree / cudaMalloc; f3d_release_workspaces frees every block (call it with the device idle).
+ *    Stream capture: a call made while its stream is capturing a CUDA graph uses the stream's existing block (its
+ *    address goes into the graph) and fails if that block is missing or too small, because nothing may be allocated
+ *    during capture: run the same calls once on that stream first.  A block recorded in a graph is kept until
+ *    f3d_release_workspaces, so the graph stays valid when later calls outgrow it;
  *  - return value 0 = ok, < 0 = error; the message is available from f3d_last_error() on the calling thread.
  *    The reference throws std::runtime_error for argument errors (src/common/runtime.h:36-86) and calls exit()
  *    on CUDA errors (src/common/runtime.h:29-34); this library returns in both cases.
