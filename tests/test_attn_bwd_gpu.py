@@ -139,3 +139,60 @@ def test_partial_scope_table_with_poisoned_outputs(cuda_device, bucket, l):
     _check_grad("dQ", dq.float().cpu(), rq)
     _check_grad("dK", dk.float().cpu(), rk)
     _check_grad("dV", dv.float().cpu(), rv)
+
+
+@pytest.mark.parametrize("k", [1, 8])
+def test_full_size_layer_sampled_scopes_and_properties(cuda_device, k):
+    """The attention-layer configuration at its full size (8 x 120,000 points padded to 960,000 tokens + tail, 8 heads x
+    32, bucket 512, scope of 1 and of 8 buckets), forward and backward.  The CPU oracle cannot run 10^6 tokens in a test,
+    so (a) a sample of scopes is cut out and compared with the oracle at the usual bars, and (b) size-independent
+    properties are checked on the whole tensors: Delta = sum(dO * O) everywhere, V = 1 gives O = 1 and dQ = dK = 0,
+    buckets that no scope lists keep what they held, and the result does not depend on what other scopes hold."""
+    from flash3dtransformer_b200.lib import pshattn
+    dev = cuda_device
+    bucket, h, d = 512, 8, 32
+    nb = 1880                                            # 962,560 tokens: 8 x 120,000 points and the padded tail
+    l = nb * bucket
+    g = torch.Generator(dev).manual_seed(k)
+    q, kk, v, do = (torch.randn(1, l, h, d, device=dev, generator=g).bfloat16() for _ in range(4))
+    listed = (nb // k) * k - 2 * k                       # the last buckets are listed by no scope
+    sc = torch.arange(listed, dtype=torch.int64).reshape(-1, k)
+    scd = sc.to(torch.uint32).to(dev)
+    o = torch.full_like(q, 7.0); lse = torch.full((1, l, h), 7.0, device=dev); delta = torch.zeros(1, l, h, device=dev)
+    dq, dk, dv = (torch.full_like(q, 7.0) for _ in range(3))
+    pshattn.buck_swin_fwd(q, kk, v, o, lse, scd, bucket)
+    pshattn.buck_swin_bwd(q, kk, v, o, do, lse, delta, dq, dk, dv, scd, bucket)
+    pshattn.device_status()
+    n_listed = listed * bucket
+    assert torch.isfinite(o.float()).all() and torch.isfinite(dq.float()).all()
+    # unlisted buckets: O, LSE, dK, dV untouched, dQ cleared (the documented contract of the backward)
+    assert torch.all(o[:, n_listed:] == 7.0) and torch.all(lse[:, n_listed:] == 7.0)
+    assert torch.all(dk[:, n_listed:] == 7.0) and torch.all(dv[:, n_listed:] == 7.0) and torch.all(dq[:, n_listed:] == 0)
+    exp_delta = (do[:, :n_listed].float() * o[:, :n_listed].float()).sum(-1)
+    assert torch.allclose(delta[:, :n_listed], exp_delta, atol=1e-3, rtol=1e-3)
+    # sampled scopes against the oracle (a scope's result depends on its own tokens only)
+    for s in (0, sc.shape[0] // 3, sc.shape[0] - 1):
+        t0, t1 = int(sc[s, 0]) * bucket, (int(sc[s, -1]) + 1) * bucket
+        cut = [t[:, t0:t1].cpu() for t in (q, kk, v, do)]
+        local = torch.arange(k, dtype=torch.int64).reshape(1, k)
+        ro, rlse = ao.buck_swin_fwd(cut[0], cut[1], cut[2], local, bucket)
+        rq, rk, rv, _ = ao.buck_swin_bwd(cut[0], cut[1], cut[2], cut[3], local, bucket)
+        err = (o[:, t0:t1].float().cpu() - ro).abs()
+        floor = ((ro.bfloat16().float() - ro).abs().mean() / ro.abs().mean()).item()
+        assert err.max().item() <= 2e-2 and (err.mean() / ro.abs().mean()).item() <= floor + 1e-3
+        assert (lse[:, t0:t1].cpu() - rlse).abs().max().item() <= 2e-3
+        _check_grad("dQ", dq[:, t0:t1].float().cpu(), rq)
+        _check_grad("dK", dk[:, t0:t1].float().cpu(), rk)
+        _check_grad("dV", dv[:, t0:t1].float().cpu(), rv)
+    # V = 1: every output row is a convex combination of ones; its gradient with respect to the scores vanishes
+    ones = torch.ones_like(v)
+    o1 = torch.empty_like(q); lse1 = torch.empty_like(lse)
+    pshattn.buck_swin_fwd(q, kk, ones, o1, lse1, scd, bucket)
+    assert (o1[:, :n_listed].float() - 1).abs().max().item() <= 1e-2
+    assert torch.equal(lse1[:, :n_listed], lse[:, :n_listed])          # the normaliser does not depend on V
+    dq1, dk1, dv1 = (torch.empty_like(q) for _ in range(3))
+    pshattn.buck_swin_bwd(q, kk, ones, o1, do, lse1, delta, dq1, dk1, dv1, scd, bucket)
+    # dP = dO 1^T is constant along a row and Delta = sum(dO * O) is within rounding of it: dS ~ 0
+    scale = do.float().abs().mean().item()
+    assert dq1[:, :n_listed].float().abs().max().item() <= 0.05 * scale * 8
+    assert dk1[:, :n_listed].float().abs().max().item() <= 0.05 * scale * 8
