@@ -49,8 +49,10 @@ constexpr int kPshThreads = 256;
 constexpr int kPshWarps = kPshThreads / 32;
 constexpr uint32_t kGroup = 256;            // points one warp stages at a time
 constexpr uint32_t kStageHalves = kGroup * 3 + 16;   // staged halves + room for the 16-byte alignment skew
-constexpr uint32_t kMinTile = 2048;
+constexpr uint32_t kDefaultTile = 2048;     // points per tile (one CTA)
+constexpr uint32_t kMinTile = 256;          // a warp's slice of a tile is at least 32 points
 constexpr uint32_t kMaxTile = 16384;
+constexpr size_t kFewTiles = 148;           // batches with fewer tiles than this take smaller tiles
 
 // Jump constants of the probe streams, s_n = A^n s_0 + C_n (mod 2^32) for the linear congruential step
 // s <- 1664525 s + 1013904223: entry n - 1 holds (A^n, C_n), n = 1 .. 128, evaluated at compile time.
@@ -782,19 +784,29 @@ static size_t psh_scratch_words(uint32_t batch, uint32_t tiles_max, uint32_t nbp
   return 3 * rows * nbp + 5 * (size_t)batch * nbp + 2 * rows + ((size_t)total_n + 1) / 2;
 }
 
-// Tiles of 2048 points; when `max_words` is given (the fixed scratch of the allocation-free entry point) the tile
-// doubles, up to 16384 points, until the tables fit.
+// Tiles of 2048 points.  A batch that gives fewer tiles than the GPU has SMs (a single small scan) takes smaller tiles,
+// down to 256 points, so that the probe walks of its points spread over more CTAs; when `max_words` is given (the fixed
+// scratch of the allocation-free entry point) the tile doubles, up to 16384 points, until the tables fit.  The outputs do
+// not depend on the tile size.
 static PshPlan psh_plan(uint32_t batch, uint32_t max_n, uint32_t nb, uint32_t total_n, size_t max_words = 0) {
   PshPlan p;
   p.nbp = nb + 1;
-  uint32_t tile = kMinTile;
-  for (;;) {
+  auto set = [&](uint32_t tile) {
     p.tile = tile;
     p.tiles_max = max_n ? (max_n + tile - 1) / tile : 1;
     if (p.tiles_max == 0) p.tiles_max = 1;
     p.scratch_words = psh_scratch_words(batch, p.tiles_max, p.nbp, total_n);
-    if (max_words == 0 || p.scratch_words <= max_words || tile >= kMaxTile) break;
+  };
+  uint32_t tile = kDefaultTile;
+  set(tile);
+  while (tile > kMinTile && (size_t)batch * p.tiles_max < kFewTiles) {
+    set(tile / 2);
+    if (max_words != 0 && p.scratch_words > max_words) { set(tile); break; }
+    tile /= 2;
+  }
+  while (max_words != 0 && p.scratch_words > max_words && tile < kMaxTile) {
     tile *= 2;
+    set(tile);
   }
   p.smem_hist = tile_smem_bytes(p.nbp, 0);
   p.smem_rank = tile_smem_bytes(p.nbp, p.tile);

@@ -95,7 +95,8 @@ int f3d_batch_psh_scatter_pad_hash(
  * fixed 4 MiB device array inside the library (held on every GPU that loads it); the call performs no cudaMalloc,
  * cudaFree or other allocating call.  Limits: the batch must satisfy
  *     3*B*T*(NB+1) + 5*B*(NB+1) + 2*B*T + ceil(total_N / 2) <= 1,048,576   with B = batch_size, NB = num_bucket,
- *     T = ceil(instance_max_N / tile), tile = 2048, doubled (up to 16384) while the sum does not fit,
+ *     T = ceil(instance_max_N / tile), tile = 2048, doubled (up to 16384) while the sum does not fit (batches of
+ *     fewer than 148 tiles take tiles down to 256 points while the sum still fits),
  * otherwise F3D_STATUS_UNSUPPORTED is returned (8 scans of 120,000 points with 256 buckets need 855k words at
  * tile 2048; the last term holds one 16-bit key per point).
  * The first call on a device looks up the array's device address (cudaGetSymbolAddress) and sets a kernel attribute;
