@@ -76,7 +76,16 @@ __device__ __forceinline__ uint64_t bmul2(uint64_t a, uint64_t b) {
 }
 
 template <int D> struct BwdCfg {
-  static constexpr int BQ = D == 128 ? 64 : 128;                 // queries per inner tile
+  // D = 32 (the backbone's head size) runs as TWO CTAs per SM: tiles of 64 queries, eight compute warps and 256
+  // tensor-memory columns per CTA.  A CTA's tile is a chain of hand-offs (score products -> compute warps -> gradient
+  // products -> dQ read-out) in which the compute warps, the busiest part, work less than half of the time; with two
+  // CTAs on the SM one computes while the other waits.
+  static constexpr bool kTwo = D == 32;
+  static constexpr int kMinCtas = kTwo ? 2 : 1;
+  static constexpr int kCW = kTwo ? 8 : kBwdComputeWarps;        // compute warps: kCW / 4 per tensor-memory lane quadrant
+  static constexpr int BQ = (D == 128 || kTwo) ? 64 : 128;       // queries per inner tile
+  static constexpr int QCOLS = BQ / (kCW / 4);                   // query columns per compute thread
+  static constexpr int kChunk = kTwo ? 16 : QCOLS;               // of which are held in registers at a time
   static constexpr int DCH = D < 64 ? D : 64;
   static constexpr int NDCH = D / DCH;
   static constexpr int RB = DCH * 2;
@@ -91,6 +100,9 @@ template <int D> struct BwdCfg {
   // their A operand from there and only dS^T, which dQ = dS K reads transposed, goes through shared memory.  That
   // halves the shared-memory traffic per tile, which was what bounded the kernel.
   static constexpr bool kTS = D <= 32;
+  // dS^T goes through shared memory in any case (dQ = dS K reads it transposed).  With 512 columns it is also kept in
+  // tensor memory for dK; with 256 columns per CTA dK reads the shared-memory tile.
+  static constexpr bool kDsT = kTS && !kTwo;
   static constexpr int kBufBytes = kTS ? kPBytes : 2 * kPBytes;  // per buffer: dS^T (| P^T)
   static constexpr int kLsdBytes = 2 /*stages*/ * 2 * BQ * 4;
   // D = 32: the dQ tile (128 rows of 128 bytes) leaves through shared memory and ONE add-reduce of the copy engine
@@ -98,16 +110,17 @@ template <int D> struct BwdCfg {
   static constexpr bool kTmaDq = D == 32;
   static constexpr int kDqStageBytes = kTmaDq ? BQ * D * 4 : 0;
   static constexpr int kSmem = 2 * kKVBytes + QS * kQStage + PB * kBufBytes + 2 * kDqStageBytes + kLsdBytes + 256 + 1024;
-  static constexpr int kThreads = kBwdThreads + (kTmaDq ? 32 : 0);    // + one warp that feeds the copy engine
+  static constexpr int kThreads = 64 + 32 * kCW + (kTmaDq ? 32 : 0);  // producer, MMA, compute warps (+ one warp that feeds the copy engine)
   static_assert(kSmem <= 227 * 1024, "shared memory budget");
   // tensor-memory columns: S^T, dP^T, (P^T, dS^T as bf16 pairs), dV, dK, dQ
   static constexpr uint32_t kSCol = 0, kDpCol = BQ, kPtCol = 2 * BQ, kDsCol = 2 * BQ + BQ / 2;
-  static constexpr uint32_t kDvCol = kTS ? 3 * BQ : 2 * BQ, kDkCol = kDvCol + D, kDqCol = kDkCol + D;
-  static_assert(kDqCol + D <= 512, "tensor-memory budget");
+  static constexpr uint32_t kDvCol = kTS ? (kDsT ? 3 * BQ : 2 * BQ + BQ / 2) : 2 * BQ, kDkCol = kDvCol + D, kDqCol = kDkCol + D;
+  static constexpr uint32_t kTmemCols = kTwo ? 256 : 512;
+  static_assert(kDqCol + D <= kTmemCols, "tensor-memory budget");
 };
 
 template <int D>
-__global__ void __launch_bounds__(BwdCfg<D>::kThreads, 1)
+__global__ void __launch_bounds__(BwdCfg<D>::kThreads, BwdCfg<D>::kMinCtas)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                 const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                 const __grid_constant__ CUtensorMap map_dq, AttnBwdArgs a) {
@@ -145,15 +158,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   if (threadIdx.x == 0) {
     tc::mbar_init(kv_full, 1);
     for (int s = 0; s < QS; ++s) { tc::mbar_init(&qdo_full[s], 1); tc::mbar_init(&qdo_empty[s], 1); }
-    tc::mbar_init(s_full, 1); tc::mbar_init(dp_full, 1); tc::mbar_init(pds_full, 32 * kBwdComputeWarps);
+    tc::mbar_init(s_full, 1); tc::mbar_init(dp_full, 1); tc::mbar_init(pds_full, 32 * C::kCW);
     for (int b = 0; b < PB; ++b) tc::mbar_init(&pds_empty[b], 1);
-    tc::mbar_init(dq_full, 1); tc::mbar_init(dq_read, 32 * kBwdComputeWarps); tc::mbar_init(dkv_full, 1);
+    tc::mbar_init(dq_full, 1); tc::mbar_init(dq_read, 32 * C::kCW); tc::mbar_init(dkv_full, 1);
     tc::mbar_init(dqs_written, 256); tc::mbar_init(&dqs_free[0], 1); tc::mbar_init(&dqs_free[1], 1);
     tc::mbar_init(&lsd_full[0], BQ); tc::mbar_init(&lsd_full[1], BQ); tc::mbar_init(pt_free, 1);
     *abort_flag = 0;
     tc::mbar_fence_init();
   }
-  if (warp == 1) { tc::tmem_alloc(tmem_slot, 512); tc::tmem_relinquish(); }
+  if (warp == 1) { tc::tmem_alloc(tmem_slot, C::kTmemCols); tc::tmem_relinquish(); }
   tc::tc_fence_before_sync();
   __syncthreads();
   tc::tc_fence_after_sync();
@@ -234,9 +247,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             const uint32_t b_off = c * BQ * C::RB + qk * 16 * C::RB;
             const uint64_t b_do = tc::make_smem_desc(do_addr + b_off, 16, 8 * C::RB, C::SWZ);
             const uint64_t b_q = tc::make_smem_desc(q_addr + b_off, 16, 8 * C::RB, C::SWZ);
-            if (C::kTS) {
+            if (C::kDsT) {
               tc::mma_f16_ts(tmem_base + C::kDvCol + c * C::DCH, tmem_base + C::kPtCol + qk * 8, b_do, idesc_kv_ts, (i | qk) != 0);
               tc::mma_f16_ts(tmem_base + C::kDkCol + c * C::DCH, tmem_base + C::kDsCol + qk * 8, b_q, idesc_kv_ts, (i | qk) != 0);
+            } else if (C::kTS) {
+              const uint32_t a_off = (qk / 4) * (kBK * 128) + (qk % 4) * 32;
+              tc::mma_f16_ts(tmem_base + C::kDvCol + c * C::DCH, tmem_base + C::kPtCol + qk * 8, b_do, idesc_kv_ts, (i | qk) != 0);
+              tc::mma_f16_ss(tmem_base + C::kDkCol + c * C::DCH, tc::make_smem_desc(ds_addr + a_off, 16, 1024, tc::kSwizzle128), b_q, idesc_kv, (i | qk) != 0);
             } else {
               const uint32_t a_off = (qk / 4) * (kBK * 128) + (qk % 4) * 32;
               tc::mma_f16_ss(tmem_base + C::kDvCol + c * C::DCH, tc::make_smem_desc(pt_addr + a_off, 16, 1024, tc::kSwizzle128), b_do, idesc_kv, (i | qk) != 0);
@@ -261,17 +278,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         if (i + 1 == num_qtiles) tc::mma_commit(dkv_full);
       }
     }
-  } else if (warp < 2 + kBwdComputeWarps) {
-    // Compute warps: four per tensor-memory lane quadrant; a thread owns one key row and, per query tile, the
+  } else if (warp < 2 + C::kCW) {
+    // Compute warps: kCW / 4 per tensor-memory lane quadrant; a thread owns one key row and, per query tile, the
     // BQ / 4 query columns of its warp.  After publishing tile i the warps read out dQ of tile i - 1 (queries on
     // the lanes) and add it to the fp32 scratch with vector reductions.
-    const int cw = warp - 2;                          // 0..15
+    const int cw = warp - 2;                          // 0..kCW-1
     const int q4 = warp & 3;                          // tensor-memory lane quadrant of this warp
-    const int cidx = cw >> 2;                         // which quarter of the query columns
-    const int ctid = cw * 32 + lane;                  // 0..511
+    const int cidx = cw >> 2;                         // which part of the query columns
+    const int ctid = cw * 32 + lane;                  // 0..32*kCW-1
     const int row = q4 * 32 + lane;                   // key row (S^T, dP^T, dK, dV) or query row (dQ)
     const uint32_t lane_off = (uint32_t)(q4 * 32) << 16;
-    constexpr int QCOLS = BQ / 4;                     // query columns per compute thread (32 or 16)
+    constexpr int QCOLS = C::QCOLS;                   // query columns per compute thread (32 or 16)
+    constexpr int CH = C::kChunk;                     // of which one tensor-memory load brings in
     const int col0 = cidx * QCOLS;
     const uint64_t c2 = bpack2(a.scale_log2, a.scale_log2);
     bool ok = true;
@@ -303,8 +321,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           if (use > 0 && !tc::mbar_wait(&dqs_free[buf], (uint32_t)(use - 1) & 1u, wc, 313)) return false;
           __syncwarp();
           const uint32_t stg = tc::smem_u32(sdq + buf * C::kDqStageBytes) + (uint32_t)row * 128u;
+          // with 64-query tiles the lanes of quadrants 2 and 3 hold no query (the dQ product has M = 128 rows)
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
+          for (int h = 0; h < 2 && q4 * 32 < BQ; ++h) {
             uint32_t o[8];
             asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
                          : "=r"(o[0]), "=r"(o[1]), "=r"(o[2]), "=r"(o[3]), "=r"(o[4]), "=r"(o[5]), "=r"(o[6]), "=r"(o[7])
@@ -357,64 +376,70 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       if (i >= PB && !tc::mbar_wait(&pds_empty[pb], (uint32_t)(i / PB - 1) & 1u, wc, 309)) { ok = false; break; }
       tc::tc_fence_after_sync();
       const uint32_t sds = tc::smem_u32(spds + pb * C::kBufBytes), spt = sds + C::kPBytes;
-      uint32_t sr[QCOLS], dr[QCOLS];
-      if (QCOLS == 32) {
-        tc::tmem_ld_32x32b_x32(tmem_base + lane_off + C::kSCol + col0, reinterpret_cast<uint32_t (&)[32]>(sr));
-        tc::tmem_ld_32x32b_x32(tmem_base + lane_off + C::kDpCol + col0, reinterpret_cast<uint32_t (&)[32]>(dr));
-      } else {
-        tc::tmem_ld_32x32b_x16(tmem_base + lane_off + C::kSCol + col0, reinterpret_cast<uint32_t (&)[16]>(sr));
-        tc::tmem_ld_32x32b_x16(tmem_base + lane_off + C::kDpCol + col0, reinterpret_cast<uint32_t (&)[16]>(dr));
-      }
-      // -lse2 and -delta of the first 8 queries (the same for every key row: broadcast reads); the next group's are
-      // fetched while the current one is worked on
-      uint64_t nl[4], nd[4];
-      tc::lds64x2(nlse2 + col0 * 4, nl[0], nl[1]);
-      tc::lds64x2(nlse2 + (col0 + 4) * 4, nl[2], nl[3]);
-      tc::lds64x2(ndl + col0 * 4, nd[0], nd[1]);
-      tc::lds64x2(ndl + (col0 + 4) * 4, nd[2], nd[3]);
-      tc::tmem_ld_wait();
-      if (C::kTS && i > 0) {
-        // the previous tile's dV / dK MMAs must have consumed the tensor-memory copies of P^T and dS^T
-        if (!tc::mbar_wait(pt_free, (uint32_t)(i - 1) & 1u, wc, 313)) { ok = false; break; }
-        tc::tc_fence_after_sync();
-      }
       const uint32_t prow = spt + (col0 / 64) * (kBK * 128) + row * 128;
       const uint32_t drow = sds + (col0 / 64) * (kBK * 128) + row * 128;
+      // CH of the thread's QCOLS columns at a time (all of them, or 16 where two CTAs share the register file)
 #pragma unroll
-      for (int v8 = 0; v8 < QCOLS / 8; ++v8) {
-        uint64_t nl_next[4] = {0, 0, 0, 0}, nd_next[4] = {0, 0, 0, 0};
-        if (v8 + 1 < QCOLS / 8) {
-          tc::lds64x2(nlse2 + (col0 + v8 * 8 + 8) * 4, nl_next[0], nl_next[1]);
-          tc::lds64x2(nlse2 + (col0 + v8 * 8 + 12) * 4, nl_next[2], nl_next[3]);
-          tc::lds64x2(ndl + (col0 + v8 * 8 + 8) * 4, nd_next[0], nd_next[1]);
-          tc::lds64x2(ndl + (col0 + v8 * 8 + 12) * 4, nd_next[2], nd_next[3]);
-        }
-        uint4 pw, dw;
-        uint32_t *pw32 = reinterpret_cast<uint32_t *>(&pw), *dw32 = reinterpret_cast<uint32_t *>(&dw);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          // p = 2^(s c - lse2), ds = p (dp - delta), two queries per instruction
-          float x0, x1;
-          bunpack2(bfma2(bpack2(__uint_as_float(sr[v8 * 8 + 2 * e]), __uint_as_float(sr[v8 * 8 + 2 * e + 1])), c2, nl[e]), x0, x1);
-          const float p0 = bwd_exp2(x0), p1 = bwd_exp2(x1);
-          const uint64_t t = badd2(bpack2(__uint_as_float(dr[v8 * 8 + 2 * e]), __uint_as_float(dr[v8 * 8 + 2 * e + 1])), nd[e]);
-          float g0, g1;
-          bunpack2(bmul2(bpack2(p0, p1), t), g0, g1);
-          const __nv_bfloat162 ph = __floats2bfloat162_rn(p0, p1), gh = __floats2bfloat162_rn(g0, g1);
-          pw32[e] = *reinterpret_cast<const uint32_t *>(&ph);
-          dw32[e] = *reinterpret_cast<const uint32_t *>(&gh);
-        }
-        const int chunk16 = ((col0 % 64) / 8 + v8) ^ (row & 7);
-        tc::sts128(drow + chunk16 * 16, dw);
-        if (C::kTS) {
-          tc::tmem_st_32x32b_x4(tmem_base + lane_off + C::kPtCol + col0 / 2 + v8 * 4, pw.x, pw.y, pw.z, pw.w);
-          tc::tmem_st_32x32b_x4(tmem_base + lane_off + C::kDsCol + col0 / 2 + v8 * 4, dw.x, dw.y, dw.z, dw.w);
+      for (int h0 = 0; h0 < QCOLS; h0 += CH) {
+        const int colh = col0 + h0;
+        uint32_t sr[CH], dr[CH];
+        if (CH == 32) {
+          tc::tmem_ld_32x32b_x32(tmem_base + lane_off + C::kSCol + colh, reinterpret_cast<uint32_t (&)[32]>(sr));
+          tc::tmem_ld_32x32b_x32(tmem_base + lane_off + C::kDpCol + colh, reinterpret_cast<uint32_t (&)[32]>(dr));
         } else {
-          tc::sts128(prow + chunk16 * 16, pw);
+          tc::tmem_ld_32x32b_x16(tmem_base + lane_off + C::kSCol + colh, reinterpret_cast<uint32_t (&)[16]>(sr));
+          tc::tmem_ld_32x32b_x16(tmem_base + lane_off + C::kDpCol + colh, reinterpret_cast<uint32_t (&)[16]>(dr));
+        }
+        // -lse2 and -delta of the first 8 queries (the same for every key row: broadcast reads); the next group's are
+        // fetched while the current one is worked on
+        uint64_t nl[4], nd[4];
+        tc::lds64x2(nlse2 + colh * 4, nl[0], nl[1]);
+        tc::lds64x2(nlse2 + (colh + 4) * 4, nl[2], nl[3]);
+        tc::lds64x2(ndl + colh * 4, nd[0], nd[1]);
+        tc::lds64x2(ndl + (colh + 4) * 4, nd[2], nd[3]);
+        tc::tmem_ld_wait();
+        if (C::kTS && i > 0 && h0 == 0) {
+          // the previous tile's dV / dK MMAs must have consumed the tensor-memory copies of P^T and dS^T
+          if (!tc::mbar_wait(pt_free, (uint32_t)(i - 1) & 1u, wc, 313)) { ok = false; break; }
+          tc::tc_fence_after_sync();
         }
 #pragma unroll
-        for (int e = 0; e < 4; ++e) { nl[e] = nl_next[e]; nd[e] = nd_next[e]; }
+        for (int v8 = 0; v8 < CH / 8; ++v8) {
+          uint64_t nl_next[4] = {0, 0, 0, 0}, nd_next[4] = {0, 0, 0, 0};
+          if (v8 + 1 < CH / 8) {
+            tc::lds64x2(nlse2 + (colh + v8 * 8 + 8) * 4, nl_next[0], nl_next[1]);
+            tc::lds64x2(nlse2 + (colh + v8 * 8 + 12) * 4, nl_next[2], nl_next[3]);
+            tc::lds64x2(ndl + (colh + v8 * 8 + 8) * 4, nd_next[0], nd_next[1]);
+            tc::lds64x2(ndl + (colh + v8 * 8 + 12) * 4, nd_next[2], nd_next[3]);
+          }
+          uint4 pw, dw;
+          uint32_t *pw32 = reinterpret_cast<uint32_t *>(&pw), *dw32 = reinterpret_cast<uint32_t *>(&dw);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            // p = 2^(s c - lse2), ds = p (dp - delta), two queries per instruction
+            float x0, x1;
+            bunpack2(bfma2(bpack2(__uint_as_float(sr[v8 * 8 + 2 * e]), __uint_as_float(sr[v8 * 8 + 2 * e + 1])), c2, nl[e]), x0, x1);
+            const float p0 = bwd_exp2(x0), p1 = bwd_exp2(x1);
+            const uint64_t t = badd2(bpack2(__uint_as_float(dr[v8 * 8 + 2 * e]), __uint_as_float(dr[v8 * 8 + 2 * e + 1])), nd[e]);
+            float g0, g1;
+            bunpack2(bmul2(bpack2(p0, p1), t), g0, g1);
+            const __nv_bfloat162 ph = __floats2bfloat162_rn(p0, p1), gh = __floats2bfloat162_rn(g0, g1);
+            pw32[e] = *reinterpret_cast<const uint32_t *>(&ph);
+            dw32[e] = *reinterpret_cast<const uint32_t *>(&gh);
+          }
+          const int chunk16 = ((colh % 64) / 8 + v8) ^ (row & 7);
+          tc::sts128(drow + chunk16 * 16, dw);
+          if (C::kTS) {
+            tc::tmem_st_32x32b_x4(tmem_base + lane_off + C::kPtCol + colh / 2 + v8 * 4, pw.x, pw.y, pw.z, pw.w);
+            if (C::kDsT) tc::tmem_st_32x32b_x4(tmem_base + lane_off + C::kDsCol + colh / 2 + v8 * 4, dw.x, dw.y, dw.z, dw.w);
+          } else {
+            tc::sts128(prow + chunk16 * 16, pw);
+          }
+#pragma unroll
+          for (int e = 0; e < 4; ++e) { nl[e] = nl_next[e]; nd[e] = nd_next[e]; }
+        }
       }
+      if (!ok) break;
       if (C::kTS) tc::tmem_st_wait();
       // the other stage was last read in tile i - 1, which every thread has left (S^T of tile i was issued only
       // after all of them had signalled pds_full for tile i - 1)
@@ -474,7 +499,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
     __syncthreads();
   }
-  if (warp == 1) { tc::tc_fence_after_sync(); tc::tmem_dealloc(tmem_base, 512); }
+  if (warp == 1) { tc::tc_fence_after_sync(); tc::tmem_dealloc(tmem_base, C::kTmemCols); }
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -624,10 +649,10 @@ attn_bwd_window_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
     }
   } else {
-    const int cw = warp - 2;                          // 0..15
+    const int cw = warp - 2;                          // 0..kCW-1
     const int q4 = warp & 3;                          // tensor-memory lane quadrant of this warp
-    const int cidx = cw >> 2;                         // which quarter of the query columns
-    const int ctid = cw * 32 + lane;                  // 0..511
+    const int cidx = cw >> 2;                         // which part of the query columns
+    const int ctid = cw * 32 + lane;                  // 0..32*kCW-1
     const int row = q4 * 32 + lane;                   // key row (S^T, dP^T, dK, dV) or query row (dQ)
     const uint32_t lane_off = (uint32_t)(q4 * 32) << 16;
     const int col0 = cidx * 32;
