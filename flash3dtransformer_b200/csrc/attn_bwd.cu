@@ -43,7 +43,7 @@ constexpr int kBK = 128;               // keys per CTA (tensor-memory lanes)
 struct AttnBwdArgs {
   const float *lse; const float *delta; float *dq_acc; __nv_bfloat16 *dK; __nv_bfloat16 *dV; const uint32_t *scopes;
   int B, L, H, num_scopes, k, bucket, kblocks_per_bucket;
-  float scale_log2, scale;
+  float scale_log2, scale, inv_scale;       // log2(e) / sqrt(D), 1 / sqrt(D), sqrt(D)
   int *status;
 };
 
@@ -104,12 +104,22 @@ template <int D> struct BwdCfg {
   // tensor memory for dK; with 256 columns per CTA dK reads the shared-memory tile.
   static constexpr bool kDsT = kTS && !kTwo;
   static constexpr int kBufBytes = kTS ? kPBytes : 2 * kPBytes;  // per buffer: dS^T (| P^T)
-  static constexpr int kLsdBytes = 2 /*stages*/ * 2 * BQ * 4;
+  // kFold: -lse and -delta enter the score products themselves.  S^T = K Q^T gets one more k-step of 16 whose K side is
+  // a constant tile of ones and whose Q side holds -lse * sqrt(D) of each query as three bf16 terms (hi + mid + lo, exact
+  // to 2^-24), so the product comes out as s - lse / scale; dP^T = V dO^T likewise comes out as dp - delta.  Otherwise
+  // every compute thread has to fetch both per-query constants for each of its columns from shared memory: broadcast
+  // loads that cost a wavefront per value and warp and were a third of all shared-memory traffic of a kernel whose
+  // shared-memory pipe (those loads, the dS^T stores, the tensor cores' operand reads) was saturated.
+  static constexpr bool kFold = kTwo;
+  static constexpr int kOnesBytes = kFold ? kBK * 32 : 0;          // [128 keys][16] bf16, ones in three columns of each half
+  static constexpr int kXBytes = kFold ? BQ * 32 : 0;              // [BQ queries][16] bf16: the three terms, then zeros
+  static constexpr int kLsdBytes = kFold ? 0 : 2 /*stages*/ * 2 * BQ * 4;
   // D = 32: the dQ tile (128 rows of 128 bytes) leaves through shared memory and ONE add-reduce of the copy engine
   // instead of 1024 vector reductions issued by the compute warps; two staging buffers
   static constexpr bool kTmaDq = D == 32;
   static constexpr int kDqStageBytes = kTmaDq ? BQ * D * 4 : 0;
-  static constexpr int kSmem = 2 * kKVBytes + QS * kQStage + PB * kBufBytes + 2 * kDqStageBytes + kLsdBytes + 256 + 1024;
+  static constexpr int kSmem = 2 * kKVBytes + QS * kQStage + PB * kBufBytes + 2 * kDqStageBytes + kOnesBytes + QS * 2 * kXBytes +
+                               kLsdBytes + 256 + 1024;
   static constexpr int kThreads = 64 + 32 * kCW + (kTmaDq ? 32 : 0);  // producer, MMA, compute warps (+ one warp that feeds the copy engine)
   static_assert(kSmem <= 227 * 1024, "shared memory budget");
   // tensor-memory columns: S^T, dP^T, (P^T, dS^T as bf16 pairs), dV, dK, dQ
@@ -134,14 +144,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   // dS^T tile, which then falls inside the P^T tile of the same buffer (rows 64..127 of that product are never used)
   unsigned char *spds = sqdo + QS * C::kQStage;                   // [PB buffers][dS^T | P^T]
   unsigned char *sdq = spds + PB * C::kBufBytes;                  // [2][BQ rows of 128 bytes] dQ staging (1 KB aligned)
-  float *slsd = reinterpret_cast<float *>(sdq + 2 * C::kDqStageBytes);    // [stage][-lse2 | -delta][BQ]
+  unsigned char *sones = sdq + 2 * C::kDqStageBytes;             // kFold: the constant k-step of K and V
+  unsigned char *sx = sones + C::kOnesBytes;                     // kFold: [QS stages][Q side | dO side] of that k-step
+  float *slsd = reinterpret_cast<float *>(sx + QS * 2 * C::kXBytes);      // else: [stage][-lse2 | -delta][BQ]
   uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<unsigned char *>(slsd) + C::kLsdBytes);
   uint64_t *kv_full = bars, *qdo_full = bars + 1, *qdo_empty = qdo_full + QS, *s_full = qdo_empty + QS, *dp_full = s_full + 1;
   uint64_t *pds_full = dp_full + 1, *pds_empty = pds_full + 1 /*[PB]*/, *dq_full = pds_empty + PB, *dq_read = dq_full + 1;
   uint64_t *dkv_full = dq_read + 1, *lsd_full = dkv_full + 1 /*[2]*/;
   uint64_t *pt_free = lsd_full + 2;
   uint64_t *dqs_written = pt_free + 1, *dqs_free = dqs_written + 1 /*[2]*/;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(dqs_free + 2);
+  uint64_t *x_full = dqs_free + 2 /*[QS]*/;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(x_full + QS);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -163,8 +176,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     tc::mbar_init(dq_full, 1); tc::mbar_init(dq_read, 32 * C::kCW); tc::mbar_init(dkv_full, 1);
     tc::mbar_init(dqs_written, 256); tc::mbar_init(&dqs_free[0], 1); tc::mbar_init(&dqs_free[1], 1);
     tc::mbar_init(&lsd_full[0], BQ); tc::mbar_init(&lsd_full[1], BQ); tc::mbar_init(pt_free, 1);
+    for (int s = 0; s < QS; ++s) tc::mbar_init(&x_full[s], BQ);
     *abort_flag = 0;
     tc::mbar_fence_init();
+  }
+  if (C::kFold) {
+    // the constant k-step: every 16-byte half of every row is (1, 1, 1, 0, 0, 0, 0, 0), so that the product with a row
+    // that carries its three terms in one half and zeros in the other does not depend on where the swizzle puts the
+    // halves; the query-side rows start as zeros and only their first half is rewritten per tile
+    for (int c = threadIdx.x; c < C::kOnesBytes / 16; c += C::kThreads)
+      tc::sts128(tc::smem_u32(sones) + c * 16, make_uint4(0x3F803F80u, 0x00003F80u, 0u, 0u));
+    for (int c = threadIdx.x; c < QS * 2 * C::kXBytes / 16; c += C::kThreads)
+      tc::sts128(tc::smem_u32(sx) + c * 16, make_uint4(0u, 0u, 0u, 0u));
+    tc::fence_proxy_async();
   }
   if (warp == 1) { tc::tmem_alloc(tmem_slot, C::kTmemCols); tc::tmem_relinquish(); }
   tc::tc_fence_before_sync();
@@ -207,14 +231,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       auto issue_s_dp = [&](int i) -> bool {
         const int s = i % QS;
         if (!tc::mbar_wait(&qdo_full[s], (uint32_t)(i / QS) & 1u, wc, 303)) return false;
+        if (C::kFold && !tc::mbar_wait(&x_full[s], (uint32_t)(i / QS) & 1u, wc, 315)) return false;
         tc::tc_fence_after_sync();
         const uint32_t q_addr = tc::smem_u32(sqdo + s * C::kQStage), do_addr = q_addr + C::kQBytes;
+        const uint32_t ones_addr = tc::smem_u32(sones), qx_addr = tc::smem_u32(sx + s * 2 * C::kXBytes), dox_addr = qx_addr + C::kXBytes;
 #pragma unroll
         for (int c = 0; c < C::NDCH; ++c)
 #pragma unroll
           for (int kk = 0; kk < C::DCH / 16; ++kk)
             tc::mma_f16_ss(tmem_base + C::kSCol, tc::make_smem_desc(k_addr + c * kBK * C::RB + kk * 32, 16, 8 * C::RB, C::SWZ),
                            tc::make_smem_desc(q_addr + c * BQ * C::RB + kk * 32, 16, 8 * C::RB, C::SWZ), idesc_s, (c | kk) != 0);
+        if (C::kFold)      // + 1 * (-lse * sqrt(D)) in three terms
+          tc::mma_f16_ss(tmem_base + C::kSCol, tc::make_smem_desc(ones_addr, 16, 256, tc::kSwizzle32),
+                         tc::make_smem_desc(qx_addr, 16, 256, tc::kSwizzle32), idesc_s, 1u);
         tc::mma_commit(s_full);
 #pragma unroll
         for (int c = 0; c < C::NDCH; ++c)
@@ -222,6 +251,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           for (int kk = 0; kk < C::DCH / 16; ++kk)
             tc::mma_f16_ss(tmem_base + C::kDpCol, tc::make_smem_desc(v_addr + c * kBK * C::RB + kk * 32, 16, 8 * C::RB, C::SWZ),
                            tc::make_smem_desc(do_addr + c * BQ * C::RB + kk * 32, 16, 8 * C::RB, C::SWZ), idesc_s, (c | kk) != 0);
+        if (C::kFold)      // + 1 * (-delta) in three terms
+          tc::mma_f16_ss(tmem_base + C::kDpCol, tc::make_smem_desc(ones_addr, 16, 256, tc::kSwizzle32),
+                         tc::make_smem_desc(dox_addr, 16, 256, tc::kSwizzle32), idesc_s, 1u);
         tc::mma_commit(dp_full);
         return true;
       };
@@ -299,11 +331,34 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const int q_tok = (int)my_scope[i / qtiles_per_bucket] * a.bucket + (i % qtiles_per_bucket) * BQ;
       return ((size_t)brow * a.L + q_tok + ctid) * a.H + head;
     };
+    // v as three bf16 terms whose sum is v to 2^-24: (hi | mid << 16, lo)
+    auto split3 = [](float v, uint32_t &w0, uint32_t &w1) {
+      const __nv_bfloat16 h0 = __float2bfloat16_rn(v);
+      const float r1 = v - __bfloat162float(h0);
+      const __nv_bfloat16 h1 = __float2bfloat16_rn(r1);
+      const __nv_bfloat16 h2 = __float2bfloat16_rn(r1 - __bfloat162float(h1));
+      w0 = (uint32_t)__bfloat16_as_ushort(h0) | ((uint32_t)__bfloat16_as_ushort(h1) << 16);
+      w1 = (uint32_t)__bfloat16_as_ushort(h2);
+    };
     auto lsd_publish = [&](int i, float l, float d) {
-      const uint32_t base = tc::smem_u32(slsd + (i & 1) * 2 * BQ);
-      tc::sts32(base + ctid * 4, l * -1.4426950408889634f);
-      tc::sts32(base + BQ * 4 + ctid * 4, -d);
-      tc::mbar_arrive(&lsd_full[i & 1]);
+      if constexpr (C::kFold) {
+        // query ctid of tile i: the first half of its row of the extra k-step, for S^T and for dP^T.  The stage last held
+        // tile i - QS, whose score products finished before this thread's previous tile began.
+        const int s = i % QS;
+        const uint32_t base = tc::smem_u32(sx + s * 2 * C::kXBytes) + (uint32_t)ctid * 32u;
+        uint32_t w0, w1;
+        split3(-l * a.inv_scale, w0, w1);
+        tc::sts128(base, make_uint4(w0, w1, 0u, 0u));
+        split3(-d, w0, w1);
+        tc::sts128(base + C::kXBytes, make_uint4(w0, w1, 0u, 0u));
+        tc::fence_proxy_async();
+        tc::mbar_arrive(&x_full[s]);
+      } else {
+        const uint32_t base = tc::smem_u32(slsd + (i & 1) * 2 * BQ);
+        tc::sts32(base + ctid * 4, l * -1.4426950408889634f);
+        tc::sts32(base + BQ * 4 + ctid * 4, -d);
+        tc::mbar_arrive(&lsd_full[i & 1]);
+      }
     };
     // dQ of tile i: two warps per quadrant take half of the D columns each
     auto read_out_dq = [&](int i) -> bool {
@@ -370,7 +425,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       float next_l = 0.f, next_d = 0.f;
       const bool prefetch = ctid < BQ && i + 1 < num_qtiles;
       if (prefetch) { const size_t idx = lsd_index(i + 1); next_l = a.lse[idx]; next_d = a.delta[idx]; }
-      if (!tc::mbar_wait(&lsd_full[s2], (uint32_t)(i >> 1) & 1u, wc, 312)) { ok = false; break; }
+      if (!C::kFold && !tc::mbar_wait(&lsd_full[s2], (uint32_t)(i >> 1) & 1u, wc, 312)) { ok = false; break; }
       if (!tc::mbar_wait(s_full, (uint32_t)i & 1u, wc, 307) || !tc::mbar_wait(dp_full, (uint32_t)i & 1u, wc, 308)) { ok = false; break; }
       // the MMAs that read this shared-memory buffer (tile i - PB) must have finished
       if (i >= PB && !tc::mbar_wait(&pds_empty[pb], (uint32_t)(i / PB - 1) & 1u, wc, 309)) { ok = false; break; }
@@ -392,11 +447,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
         // -lse2 and -delta of the first 8 queries (the same for every key row: broadcast reads); the next group's are
         // fetched while the current one is worked on
-        uint64_t nl[4], nd[4];
-        tc::lds64x2(nlse2 + colh * 4, nl[0], nl[1]);
-        tc::lds64x2(nlse2 + (colh + 4) * 4, nl[2], nl[3]);
-        tc::lds64x2(ndl + colh * 4, nd[0], nd[1]);
-        tc::lds64x2(ndl + (colh + 4) * 4, nd[2], nd[3]);
+        uint64_t nl[4] = {0, 0, 0, 0}, nd[4] = {0, 0, 0, 0};
+        if (!C::kFold) {
+          tc::lds64x2(nlse2 + colh * 4, nl[0], nl[1]);
+          tc::lds64x2(nlse2 + (colh + 4) * 4, nl[2], nl[3]);
+          tc::lds64x2(ndl + colh * 4, nd[0], nd[1]);
+          tc::lds64x2(ndl + (colh + 4) * 4, nd[2], nd[3]);
+        }
         tc::tmem_ld_wait();
         if (C::kTS && i > 0 && h0 == 0) {
           // the previous tile's dV / dK MMAs must have consumed the tensor-memory copies of P^T and dS^T
@@ -406,7 +463,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 #pragma unroll
         for (int v8 = 0; v8 < CH / 8; ++v8) {
           uint64_t nl_next[4] = {0, 0, 0, 0}, nd_next[4] = {0, 0, 0, 0};
-          if (v8 + 1 < CH / 8) {
+          if (!C::kFold && v8 + 1 < CH / 8) {
             tc::lds64x2(nlse2 + (colh + v8 * 8 + 8) * 4, nl_next[0], nl_next[1]);
             tc::lds64x2(nlse2 + (colh + v8 * 8 + 12) * 4, nl_next[2], nl_next[3]);
             tc::lds64x2(ndl + (colh + v8 * 8 + 8) * 4, nd_next[0], nd_next[1]);
@@ -418,9 +475,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           for (int e = 0; e < 4; ++e) {
             // p = 2^(s c - lse2), ds = p (dp - delta), two queries per instruction
             float x0, x1;
-            bunpack2(bfma2(bpack2(__uint_as_float(sr[v8 * 8 + 2 * e]), __uint_as_float(sr[v8 * 8 + 2 * e + 1])), c2, nl[e]), x0, x1);
+            const uint64_t s2v = bpack2(__uint_as_float(sr[v8 * 8 + 2 * e]), __uint_as_float(sr[v8 * 8 + 2 * e + 1]));
+            const uint64_t d2v = bpack2(__uint_as_float(dr[v8 * 8 + 2 * e]), __uint_as_float(dr[v8 * 8 + 2 * e + 1]));
+            // kFold: the products already hold s - lse / scale and dp - delta
+            bunpack2(C::kFold ? bmul2(s2v, c2) : bfma2(s2v, c2, nl[e]), x0, x1);
             const float p0 = bwd_exp2(x0), p1 = bwd_exp2(x1);
-            const uint64_t t = badd2(bpack2(__uint_as_float(dr[v8 * 8 + 2 * e]), __uint_as_float(dr[v8 * 8 + 2 * e + 1])), nd[e]);
+            const uint64_t t = C::kFold ? d2v : badd2(d2v, nd[e]);
             float g0, g1;
             bunpack2(bmul2(bpack2(p0, p1), t), g0, g1);
             const __nv_bfloat162 ph = __floats2bfloat162_rn(p0, p1), gh = __floats2bfloat162_rn(g0, g1);
@@ -890,7 +950,7 @@ extern "C" int f3d_buck_swin_bwd(const void *Q, const void *K, const void *V, co
     const float scale = 1.f / sqrtf((float)D);
     AttnBwdArgs a{static_cast<const float *>(LSE), static_cast<const float *>(Delta), nullptr,
                   static_cast<__nv_bfloat16 *>(dK), static_cast<__nv_bfloat16 *>(dV), static_cast<const uint32_t *>(scope_buckets),
-                  B, L, H, num_scopes, scope_size, (int)bucket_size, (int)bucket_size / kBK, 1.4426950408889634f * scale, scale,
+                  B, L, H, num_scopes, scope_size, (int)bucket_size, (int)bucket_size / kBK, 1.4426950408889634f * scale, scale, sqrtf((float)D),
                   status_word(device)};
     if (!a.status) return F3D_ERR_CUDA;
     // this kernel writes dQ only for the tokens of listed buckets; the general path below writes every row (zero where
@@ -907,7 +967,7 @@ extern "C" int f3d_buck_swin_bwd(const void *Q, const void *K, const void *V, co
   const float scale = 1.f / sqrtf((float)D);
   AttnBwdArgs a{static_cast<const float *>(LSE), static_cast<const float *>(Delta), static_cast<float *>(acc),
                 static_cast<__nv_bfloat16 *>(dK), static_cast<__nv_bfloat16 *>(dV), static_cast<const uint32_t *>(scope_buckets),
-                B, L, H, num_scopes, scope_size, (int)bucket_size, (int)bucket_size / kBK, 1.4426950408889634f * scale, scale,
+                B, L, H, num_scopes, scope_size, (int)bucket_size, (int)bucket_size / kBK, 1.4426950408889634f * scale, scale, sqrtf((float)D),
                 status_word(device)};
   if (!a.status) return F3D_ERR_CUDA;
   int rc;
