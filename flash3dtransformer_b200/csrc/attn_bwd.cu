@@ -9,20 +9,27 @@
 //
 // Kernels:
 //   attn_bwd_delta_kernel   Delta = rowsum(dO o O), one thread per (token, head)
-//   attn_bwd_kernel<D>      one CTA (576 threads, 608 at D = 32) per (scope, 128-key block, head, batch row); it loops over the
-//                           query tiles of the scope and keeps dK, dV for its keys in tensor memory
+//   attn_bwd_kernel<D>      one CTA per (scope, 128-key block, head, batch row); it loops over the query tiles of the
+//                           scope and keeps dK, dV for its keys in tensor memory.  D = 16 / 64 / 128: 576 threads, one
+//                           CTA per SM, 512 tensor-memory columns.  D = 32 (the backbone's head size): 352 threads, TWO
+//                           CTAs per SM with 256 columns each and 64-query tiles, so that one CTA computes while the
+//                           other waits for its products
 //       warp 0      TMA producer: K_j, V_j once; Q_i, dO_i through a 2- or 3-stage ring
 //       warp 1      issues S^T = K Q^T and dP^T = V dO^T into tensor memory (keys on the lanes); once the compute
 //                   warps have published P^T and dS^T it first issues the NEXT tile's S^T / dP^T, then dV += P^T dO
-//                   and dK += dS^T Q (A from tensor memory at D <= 32, else K-major shared-memory tiles) and
-//                   dQ_i = dS K (the dS^T shared-memory tile read as an MN-major A operand)
-//       warps 2-17  compute: a thread owns one key row and a quarter of the query columns; p = exp2(s*c - lse),
-//                   ds = p*(dp - delta) in packed fp32 pairs, with -lse / -delta of the tile staged in shared memory
-//                   one tile ahead; afterwards they read dQ of the previous tile from tensor memory (queries on the
-//                   lanes) and add it to an fp32 scratch: with vector reductions, or at D = 32 by staging the tile in
-//                   shared memory for
-//       warp 18     (D = 32) one thread hands each staged dQ tile to the copy engine as a single add-reduce
+//                   and dK += dS^T Q (A from tensor memory where the columns allow it, else K-major shared-memory
+//                   tiles) and dQ_i = dS K (the dS^T shared-memory tile read as an MN-major A operand)
+//       compute     16 warps (8 at D = 32): a thread owns one key row and a share of the query columns;
+//                   p = exp2(s*c - lse), ds = p*(dp - delta) in packed fp32 pairs.  At D = 32 the score products
+//                   deliver s - lse/scale and dp - delta themselves (an extra k-step carries the per-query constants,
+//                   BwdCfg::kFold); otherwise -lse / -delta of the tile are staged in shared memory one tile ahead
+//                   and fetched per column.  Afterwards the warps read dQ of the previous tile from tensor memory
+//                   (queries on the lanes) and add it to an fp32 scratch: with vector reductions, or at D = 32 by
+//                   staging the tile in shared memory for
+//       drain warp  (D = 32) one thread hands each staged dQ tile to the copy engine as a single add-reduce
 //                   (cp.reduce.async.bulk.tensor) and recycles the two staging buffers
+// What bounds the kernel at D = 32 is the shared-memory pipe: dS^T stores, the tensor cores' operand reads and, before
+// the constants moved into the products, one broadcast load per query constant and warp (a third of all wavefronts).
 //   attn_bwd_dq_convert     dQ = bf16(scratch / sqrt(D))
 // dQ needs the scratch because every key block of a scope contributes to every query; dK and dV are written once.
 //   attn_bwd_window_kernel<D>   windows of at most 512 tokens at D <= 32: one CTA per (scope, head) walks key blocks
@@ -577,9 +584,12 @@ template <int D> struct BwdWinCfg {
   static constexpr int kQStage = 2 * kQBytes;
   static constexpr int QS = 3;
   static constexpr int kPBytes = kBK * BQ * 2;                  // dS^T tile
-  static constexpr int kLsdBytes = 2 * 2 * BQ * 4;
-  static constexpr int kSmem = 2 * 2 * kKVBytes + QS * kQStage + 2 * kPBytes + kLsdBytes + 256 + 1024;
   static constexpr int kMaxTiles = 4;                           // query tiles (and key blocks) per scope
+  // -lse / scale and -delta of every query of the scope enter the score products as an extra k-step of 16 (three bf16
+  // terms per query against a tile of ones, see BwdCfg::kFold): written once per CTA, one row pair per query
+  static constexpr int kOnesBytes = kBK * 32;
+  static constexpr int kXBytes = BQ * 32;                       // per query tile and side (Q side | dO side)
+  static constexpr int kSmem = 2 * 2 * kKVBytes + QS * kQStage + 2 * kPBytes + kOnesBytes + kMaxTiles * 2 * kXBytes + 256 + 1024;
   static constexpr uint32_t kSCol = 0, kDpCol = 128, kPtCol = 256, kDvCol = 320, kDkCol = 352, kDqCol = 384;
   static_assert(D <= 32 && kDqCol + kMaxTiles * D <= 512, "tensor-memory budget");
 };
@@ -596,12 +606,13 @@ attn_bwd_window_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   unsigned char *skv = smem;                                      // [2 buffers][K | V]
   unsigned char *sqdo = skv + 2 * 2 * C::kKVBytes;                // [QS stages][Q | dO]
   unsigned char *sdsb = sqdo + QS * C::kQStage;                   // [2 buffers] dS^T
-  float *slsd = reinterpret_cast<float *>(sdsb + 2 * C::kPBytes); // [stage][-lse2 | -delta][BQ]
-  uint64_t *bars = reinterpret_cast<uint64_t *>(reinterpret_cast<unsigned char *>(slsd) + C::kLsdBytes);
+  unsigned char *sones = sdsb + 2 * C::kPBytes;                   // the constant k-step of K and V
+  unsigned char *sx = sones + C::kOnesBytes;                      // [query tile][Q side | dO side] of that k-step
+  uint64_t *bars = reinterpret_cast<uint64_t *>(sx + C::kMaxTiles * 2 * C::kXBytes);
   uint64_t *kv_full = bars /*[2]*/, *kv_empty = bars + 2 /*[2]*/, *qdo_full = bars + 4, *qdo_empty = qdo_full + QS;
   uint64_t *s_full = qdo_empty + QS, *dp_full = s_full + 1, *pds_full = dp_full + 1, *pds_empty = pds_full + 1 /*[2]*/;
-  uint64_t *pt_free = pds_empty + 2, *dkv_full = pt_free + 1, *dkv_read = dkv_full + 1, *lsd_full = dkv_read + 1 /*[2]*/;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(lsd_full + 2);
+  uint64_t *pt_free = pds_empty + 2, *dkv_full = pt_free + 1, *dkv_read = dkv_full + 1, *x_full = dkv_read + 1;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(x_full + 1);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -617,10 +628,15 @@ attn_bwd_window_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     for (int s = 0; s < QS; ++s) { tc::mbar_init(&qdo_full[s], 1); tc::mbar_init(&qdo_empty[s], 1); }
     tc::mbar_init(s_full, 1); tc::mbar_init(dp_full, 1); tc::mbar_init(pds_full, 32 * kBwdComputeWarps);
     tc::mbar_init(pt_free, 1); tc::mbar_init(dkv_full, 1); tc::mbar_init(dkv_read, 32 * kBwdComputeWarps);
-    tc::mbar_init(&lsd_full[0], BQ); tc::mbar_init(&lsd_full[1], BQ);
+    tc::mbar_init(x_full, 32 * kBwdComputeWarps);
     *abort_flag = 0;
     tc::mbar_fence_init();
   }
+  // every 16-byte half of every row of the constant tile is (1, 1, 1, 0, ...): the product with a row that carries its
+  // three terms in one half and zeros in the other does not depend on where the swizzle puts the halves
+  for (int c = threadIdx.x; c < C::kOnesBytes / 16; c += kBwdThreads)
+    tc::sts128(tc::smem_u32(sones) + c * 16, make_uint4(0x3F803F80u, 0x00003F80u, 0u, 0u));
+  tc::fence_proxy_async();
   if (warp == 1) { tc::tmem_alloc(tmem_slot, 512); tc::tmem_relinquish(); }
   tc::tc_fence_before_sync();
   __syncthreads();
@@ -665,19 +681,24 @@ attn_bwd_window_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         tc::tc_fence_after_sync();
         const uint32_t k_addr = tc::smem_u32(skv + (j & 1) * 2 * C::kKVBytes), v_addr = k_addr + C::kKVBytes;
         const uint32_t q_addr = tc::smem_u32(sqdo + s * C::kQStage), do_addr = q_addr + C::kQBytes;
+        const uint32_t ones_addr = tc::smem_u32(sones), qx_addr = tc::smem_u32(sx + i * 2 * C::kXBytes), dox_addr = qx_addr + C::kXBytes;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
           tc::mma_f16_ss(tmem_base + C::kSCol, tc::make_smem_desc(k_addr + kk * 32, 16, 8 * C::RB, C::SWZ),
                          tc::make_smem_desc(q_addr + kk * 32, 16, 8 * C::RB, C::SWZ), idesc_s, kk != 0);
+        tc::mma_f16_ss(tmem_base + C::kSCol, tc::make_smem_desc(ones_addr, 16, 256, tc::kSwizzle32),
+                       tc::make_smem_desc(qx_addr, 16, 256, tc::kSwizzle32), idesc_s, 1u);          // - lse / scale
         tc::mma_commit(s_full);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
           tc::mma_f16_ss(tmem_base + C::kDpCol, tc::make_smem_desc(v_addr + kk * 32, 16, 8 * C::RB, C::SWZ),
                          tc::make_smem_desc(do_addr + kk * 32, 16, 8 * C::RB, C::SWZ), idesc_s, kk != 0);
+        tc::mma_f16_ss(tmem_base + C::kDpCol, tc::make_smem_desc(ones_addr, 16, 256, tc::kSwizzle32),
+                       tc::make_smem_desc(dox_addr, 16, 256, tc::kSwizzle32), idesc_s, 1u);         // - delta
         tc::mma_commit(dp_full);
         return true;
       };
-      bool ok = issue_s_dp(0);
+      bool ok = tc::mbar_wait(x_full, 0, wc, 327) && issue_s_dp(0);
       for (int t = 0; t < total && ok; ++t) {
         const int j = t / nt, i = t % nt, s = t % QS, pb = t & 1;
         // P^T (tensor memory) and dS^T (shared memory) of iteration t are published, S^T / dP^T have been read
@@ -718,21 +739,33 @@ attn_bwd_window_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int col0 = cidx * 32;
     const uint64_t c2 = bpack2(a.scale_log2, a.scale_log2);
     bool ok = true;
-    auto lsd_index = [&](int t) { return ((size_t)brow * a.L + tile_tok(t % nt) + ctid) * a.H + head; };
-    auto lsd_publish = [&](int t, float l, float d) {
-      const uint32_t base = tc::smem_u32(slsd + (t & 1) * 2 * BQ);
-      tc::sts32(base + ctid * 4, l * -1.4426950408889634f);
-      tc::sts32(base + BQ * 4 + ctid * 4, -d);
-      tc::mbar_arrive(&lsd_full[t & 1]);
-    };
-    if (ctid < BQ) { const size_t idx = lsd_index(0); lsd_publish(0, a.lse[idx], a.delta[idx]); }
+    {
+      // thread ctid owns query ctid of the scope (tile ctid / 128): its row pair of the extra k-step, written once
+      const int xt = ctid / BQ, xr = ctid % BQ;
+      uint4 qrow = make_uint4(0u, 0u, 0u, 0u), drow4 = qrow;
+      if (xt < nt) {
+        const size_t idx = ((size_t)brow * a.L + tile_tok(xt) + xr) * a.H + head;
+        auto split3 = [](float v, uint32_t &w0, uint32_t &w1) {
+          const __nv_bfloat16 h0 = __float2bfloat16_rn(v);
+          const float r1 = v - __bfloat162float(h0);
+          const __nv_bfloat16 h1 = __float2bfloat16_rn(r1);
+          const __nv_bfloat16 h2 = __float2bfloat16_rn(r1 - __bfloat162float(h1));
+          w0 = (uint32_t)__bfloat16_as_ushort(h0) | ((uint32_t)__bfloat16_as_ushort(h1) << 16);
+          w1 = (uint32_t)__bfloat16_as_ushort(h2);
+        };
+        split3(-a.lse[idx] * a.inv_scale, qrow.x, qrow.y);
+        split3(-a.delta[idx], drow4.x, drow4.y);
+      }
+      const uint32_t base = tc::smem_u32(sx + xt * 2 * C::kXBytes) + (uint32_t)xr * 32u;
+      tc::sts128(base, qrow);
+      tc::sts128(base + 16, make_uint4(0u, 0u, 0u, 0u));
+      tc::sts128(base + C::kXBytes, drow4);
+      tc::sts128(base + C::kXBytes + 16, make_uint4(0u, 0u, 0u, 0u));
+      tc::fence_proxy_async();
+      tc::mbar_arrive(x_full);
+    }
     for (int t = 0; t < total && ok; ++t) {
       const int j = t / nt, i = t % nt, pb = t & 1;
-      const uint32_t nlse2 = tc::smem_u32(slsd + (t & 1) * 2 * BQ), ndl = nlse2 + BQ * 4;
-      float next_l = 0.f, next_d = 0.f;
-      const bool prefetch = ctid < BQ && t + 1 < total;
-      if (prefetch) { const size_t idx = lsd_index(t + 1); next_l = a.lse[idx]; next_d = a.delta[idx]; }
-      if (!tc::mbar_wait(&lsd_full[t & 1], (uint32_t)(t >> 1) & 1u, wc, 327)) { ok = false; break; }
       if (!tc::mbar_wait(s_full, (uint32_t)t & 1u, wc, 328) || !tc::mbar_wait(dp_full, (uint32_t)t & 1u, wc, 329)) { ok = false; break; }
       // the dQ MMA that read this shared-memory buffer (iteration t - 2) must have finished
       if (t >= 2 && !tc::mbar_wait(&pds_empty[pb], (uint32_t)(t / 2 - 1) & 1u, wc, 330)) { ok = false; break; }
@@ -740,11 +773,6 @@ attn_bwd_window_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       uint32_t sr[32], dr[32];
       tc::tmem_ld_32x32b_x32(tmem_base + lane_off + C::kSCol + col0, sr);
       tc::tmem_ld_32x32b_x32(tmem_base + lane_off + C::kDpCol + col0, dr);
-      uint64_t nl[4], nd[4];
-      tc::lds64x2(nlse2 + col0 * 4, nl[0], nl[1]);
-      tc::lds64x2(nlse2 + (col0 + 4) * 4, nl[2], nl[3]);
-      tc::lds64x2(ndl + col0 * 4, nd[0], nd[1]);
-      tc::lds64x2(ndl + (col0 + 4) * 4, nd[2], nd[3]);
       tc::tmem_ld_wait();
       if (t > 0) {
         // the previous iteration's dV MMAs must have consumed the tensor-memory copy of P^T
@@ -754,21 +782,15 @@ attn_bwd_window_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const uint32_t drow = tc::smem_u32(sdsb + pb * C::kPBytes) + (col0 / 64) * (kBK * 128) + row * 128;
 #pragma unroll
       for (int v8 = 0; v8 < 4; ++v8) {
-        uint64_t nl_next[4] = {0, 0, 0, 0}, nd_next[4] = {0, 0, 0, 0};
-        if (v8 + 1 < 4) {
-          tc::lds64x2(nlse2 + (col0 + v8 * 8 + 8) * 4, nl_next[0], nl_next[1]);
-          tc::lds64x2(nlse2 + (col0 + v8 * 8 + 12) * 4, nl_next[2], nl_next[3]);
-          tc::lds64x2(ndl + (col0 + v8 * 8 + 8) * 4, nd_next[0], nd_next[1]);
-          tc::lds64x2(ndl + (col0 + v8 * 8 + 12) * 4, nd_next[2], nd_next[3]);
-        }
         uint4 pw, dw;
         uint32_t *pw32 = reinterpret_cast<uint32_t *>(&pw), *dw32 = reinterpret_cast<uint32_t *>(&dw);
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
+          // the products hold s - lse / scale and dp - delta: p = 2^(c s'), ds = p dp'
           float x0, x1;
-          bunpack2(bfma2(bpack2(__uint_as_float(sr[v8 * 8 + 2 * e]), __uint_as_float(sr[v8 * 8 + 2 * e + 1])), c2, nl[e]), x0, x1);
+          bunpack2(bmul2(bpack2(__uint_as_float(sr[v8 * 8 + 2 * e]), __uint_as_float(sr[v8 * 8 + 2 * e + 1])), c2), x0, x1);
           const float p0 = bwd_exp2(x0), p1 = bwd_exp2(x1);
-          const uint64_t tt = badd2(bpack2(__uint_as_float(dr[v8 * 8 + 2 * e]), __uint_as_float(dr[v8 * 8 + 2 * e + 1])), nd[e]);
+          const uint64_t tt = bpack2(__uint_as_float(dr[v8 * 8 + 2 * e]), __uint_as_float(dr[v8 * 8 + 2 * e + 1]));
           float g0, g1;
           bunpack2(bmul2(bpack2(p0, p1), tt), g0, g1);
           const __nv_bfloat162 ph = __floats2bfloat162_rn(p0, p1), gh = __floats2bfloat162_rn(g0, g1);
@@ -778,11 +800,8 @@ attn_bwd_window_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int chunk16 = ((col0 % 64) / 8 + v8) ^ (row & 7);
         tc::sts128(drow + chunk16 * 16, dw);
         tc::tmem_st_32x32b_x4(tmem_base + lane_off + C::kPtCol + col0 / 2 + v8 * 4, pw.x, pw.y, pw.z, pw.w);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) { nl[e] = nl_next[e]; nd[e] = nd_next[e]; }
       }
       tc::tmem_st_wait();
-      if (prefetch) lsd_publish(t + 1, next_l, next_d);
       tc::fence_proxy_async();
       tc::tc_fence_before_sync();
       tc::mbar_arrive(pds_full);
