@@ -72,7 +72,10 @@ template <int BN> struct GemmSmem {
   static constexpr int kBarBytes = 256;
   // partial row sums of the epilogue warps: [accumulator][quadrant][warp of the quadrant][32 rows] pairs + counters
   static constexpr int kStatBytes = kAcc * 4 * (kEpiWarps / 4) * 32 * 8 + kAcc * 4 * 4;
-  static constexpr int kTotal = kStages * kStageBytes + kOutBytes + kBarBytes + kStatBytes + 1024 /*alignment slack*/;
+  // bias inside the product: one more k-step of 16 whose A side is a tile of ones [BM][16] and whose W side holds every
+  // column's bias as three 16-bit terms [BN][16] (single column tile only, where the W side never changes)
+  static constexpr int kFoldBytes = (BM + BN) * 32;
+  static constexpr int kTotal = kStages * kStageBytes + kOutBytes + kBarBytes + kStatBytes + kFoldBytes + 1024 /*alignment slack*/;
 };
 
 __device__ __forceinline__ float gelu_tanh(float x) {
@@ -142,11 +145,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char *stage_base = smem;
   unsigned char *out_base = smem + kStages * S::kStageBytes;
-  uint64_t *bars = reinterpret_cast<uint64_t *>(out_base + S::kOutBytes);
+  unsigned char *fold_base = out_base + S::kOutBytes;             // [BM][16] ones, then [BN][16] bias terms (1 KB aligned)
+  uint64_t *bars = reinterpret_cast<uint64_t *>(fold_base + S::kFoldBytes);
   uint64_t *full = bars, *empty = bars + kStages, *acc_full = bars + 2 * kStages, *acc_empty = bars + 2 * kStages + kAcc;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 2 * kAcc);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
-  float2 *stat_slots = reinterpret_cast<float2 *>(out_base + S::kOutBytes + S::kBarBytes);
+  float2 *stat_slots = reinterpret_cast<float2 *>(fold_base + S::kFoldBytes + S::kBarBytes);
   int *stat_cnt = reinterpret_cast<int *>(stat_slots + kAcc * 4 * (kEpiWarps / 4) * 32);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -154,6 +158,42 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   const int num_tiles = m_tiles * n_tiles;
   const int kb_per_split = (g.K + BK - 1) / BK;
   const int kb_count = kb_per_split * g.ksplit;
+  // The bias enters the product itself when the kernel has one column tile: the tile of ones times the columns' bias
+  // terms (hi + mid + lo in the element type, exact to 2^-24) adds b[n] to every accumulator in fp32, and the epilogue
+  // neither loads nor adds it.  Every 16-byte half of the ones rows is (1, 1, 1, 0, ...), the bias rows carry their terms
+  // in the first half and zeros in the second, so the sum does not depend on where the 32-byte swizzle puts the halves.
+  const bool fold_bias = g.bias != nullptr && g.ln_stats == nullptr && n_tiles == 1 && g.ksplit == 1;
+  if (fold_bias) {
+    const uint32_t one2 = F16 ? 0x3C003C00u : 0x3F803F80u, one1 = F16 ? 0x00003C00u : 0x00003F80u;
+    for (int c = threadIdx.x; c < BM * 2; c += kGemmThreads) tc::sts128(tc::smem_u32(fold_base) + c * 16, make_uint4(one2, one1, 0u, 0u));
+    for (int r = threadIdx.x; r < BN; r += kGemmThreads) {
+      // row r of the W tile is output column r, or for SwiGLU gate column r | up column r - BN / 2
+      int col = r;
+      if (g.epilogue == EPI_SWIGLU) col = r < BN / 2 ? r : g.N / 2 + (r - BN / 2);
+      const bool live = g.epilogue == EPI_SWIGLU ? (r < BN / 2 ? r < g.N / 2 : r - BN / 2 < g.N / 2) : r < g.N;
+      const float b = live ? __ldg(g.bias + col) : 0.f;
+      uint32_t w0, w1;
+      if (F16) {
+        const __half h0 = __float2half_rn(b);
+        const float r1 = b - __half2float(h0);
+        const __half h1 = __float2half_rn(r1);
+        const __half h2 = __float2half_rn(r1 - __half2float(h1));
+        w0 = (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
+        w1 = (uint32_t)__half_as_ushort(h2);
+      } else {
+        const __nv_bfloat16 h0 = __float2bfloat16_rn(b);
+        const float r1 = b - __bfloat162float(h0);
+        const __nv_bfloat16 h1 = __float2bfloat16_rn(r1);
+        const __nv_bfloat16 h2 = __float2bfloat16_rn(r1 - __bfloat162float(h1));
+        w0 = (uint32_t)__bfloat16_as_ushort(h0) | ((uint32_t)__bfloat16_as_ushort(h1) << 16);
+        w1 = (uint32_t)__bfloat16_as_ushort(h2);
+      }
+      const uint32_t base = tc::smem_u32(fold_base) + BM * 32 + r * 32;
+      tc::sts128(base, make_uint4(w0, w1, 0u, 0u));
+      tc::sts128(base + 16, make_uint4(0u, 0u, 0u, 0u));
+    }
+    tc::fence_proxy_async();
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { tc::mbar_init(&full[s], 1); tc::mbar_init(&empty[s], 1); }
@@ -234,6 +274,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             tc::mma_f16_ss(d_tmem, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
           tc::mma_commit(&empty[s]);
         }
+        if (ok && fold_bias)
+          tc::mma_f16_ss(d_tmem, tc::make_smem_desc(tc::smem_u32(fold_base), 16, 256, tc::kSwizzle32),
+                         tc::make_smem_desc(tc::smem_u32(fold_base) + BM * 32, 16, 256, tc::kSwizzle32), idesc, 1u);
         if (ok) tc::mma_commit(&acc_full[acc]);
       }
     }
@@ -291,7 +334,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                           gfma2(gpack2(__uint_as_float(u[4 * j + 2]), __uint_as_float(u[4 * j + 3])), rstd2, gfma2(gpack2(d4.z, d4.w), nmr2, gpack2(b4.z, b4.w))),
                           v[4 * j + 2], v[4 * j + 3]);
             }
-          } else if (g.bias) {
+          } else if (g.bias && !fold_bias) {
             const float4 *pg = reinterpret_cast<const float4 *>(g.bias + oc0);
             const float4 *pu = reinterpret_cast<const float4 *>(g.bias + g.N / 2 + oc0);
 #pragma unroll
@@ -325,7 +368,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 gunpack2(gfma2(gpack2(v[4 * j + 2], v[4 * j + 3]), rstd2, gfma2(gpack2(c4.z, c4.w), nmr2, gpack2(b4.z, b4.w))), v[4 * j + 2], v[4 * j + 3]);
               }
             }
-          } else if (g.bias) {
+          } else if (g.bias && !fold_bias) {
             const float4 *bp = reinterpret_cast<const float4 *>(g.bias + oc0);
             if (oc0 + 32 <= g.N) {                               // common case: no guards inside the loop
 #pragma unroll
