@@ -290,7 +290,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     unsigned char *my_out = out_base + (warp - 2) * 2 * 32 * 64;
     uint32_t t_local = 0, obuf = 0, task = 0;
     bool ok = true;
-    const int out_cols = g.epilogue == EPI_SWIGLU ? BN / 2 : BN;     // output columns produced per tile
+    const int tile_cols = g.epilogue == EPI_SWIGLU ? BN / 2 : BN;    // output columns a tile can produce
+    const int total_cols = g.epilogue == EPI_SWIGLU ? g.N / 2 : g.N; // output columns there are
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t_local) {
       const uint32_t acc = t_local % kAcc, aph = (t_local / kAcc) & 1u;
       const int mt = n_tiles == 1 ? tile : tile / n_tiles;
@@ -311,6 +312,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       const uint64_t rstd2 = gpack2(ln_rstd, ln_rstd), nmr2 = gpack2(ln_nmr, ln_nmr);
       uint64_t tile_sum2 = gpack2(0.f, 0.f), tile_sq2 = gpack2(0.f, 0.f);     // row sums over this warp's tasks of the tile
       // this warp's tasks of the tile: numbers congruent to `sub` modulo kSub, `task` being the tile's first
+      // tasks of this tile: only the 32-column groups that hold output columns (N = 96 fills three of a 128-column
+      // tile's four groups; the fourth would be computed and then clipped by the store)
+      const int first_col = g.epilogue == EPI_SWIGLU ? n0 / 2 : n0;
+      const int out_cols = min(tile_cols, (total_cols - first_col + 31) & ~31);
       for (int c0 = (int)((sub + kSub - task % kSub) % kSub) * 32; c0 < out_cols; c0 += 32 * (int)kSub) {
         float v[32];
         const int oc0 = (g.epilogue == EPI_SWIGLU ? n0 / 2 : n0) + c0;      // first output column of the task
