@@ -20,7 +20,7 @@
 //                   and dK += dS^T Q (A from tensor memory where the columns allow it, else K-major shared-memory
 //                   tiles) and dQ_i = dS K (the dS^T shared-memory tile read as an MN-major A operand)
 //       compute     16 warps (8 at D = 32): a thread owns one key row and a share of the query columns;
-//                   p = exp2(s*c - lse), ds = p*(dp - delta) in packed fp32 pairs.  At D = 32 the score products
+//                   p = exp2(s*c - lse), ds = p*(dp - delta) in packed fp32 pairs.  Except at D = 64 the score products
 //                   deliver s - lse/scale and dp - delta themselves (an extra k-step carries the per-query constants,
 //                   BwdCfg::kFold); otherwise -lse / -delta of the tile are staged in shared memory one tile ahead
 //                   and fetched per column.  Afterwards the warps read dQ of the previous tile from tensor memory
@@ -117,7 +117,9 @@ template <int D> struct BwdCfg {
   // every compute thread has to fetch both per-query constants for each of its columns from shared memory: broadcast
   // loads that cost a wavefront per value and warp and were a third of all shared-memory traffic of a kernel whose
   // shared-memory pipe (those loads, the dS^T stores, the tensor cores' operand reads) was saturated.
-  static constexpr bool kFold = kTwo;
+  // (measured per head size: D = 16 200 -> 243, D = 32 426 -> 485-512, D = 128 579-600 -> 618 TFLOP/s; D = 64, whose
+  // compute threads are short of registers, 549 -> 509, so it keeps the per-column loads)
+  static constexpr bool kFold = D != 64;
   static constexpr int kOnesBytes = kFold ? kBK * 32 : 0;          // [128 keys][16] bf16, ones in three columns of each half
   static constexpr int kXBytes = kFold ? BQ * 32 : 0;              // [BQ queries][16] bf16: the three terms, then zeros
   static constexpr int kLsdBytes = kFold ? 0 : 2 /*stages*/ * 2 * BQ * 4;
