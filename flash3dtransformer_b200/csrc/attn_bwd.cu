@@ -10,16 +10,16 @@
 // Kernels:
 //   attn_bwd_delta_kernel   Delta = rowsum(dO o O), one thread per (token, head)
 //   attn_bwd_kernel<D>      one CTA per (scope, 128-key block, head, batch row); it loops over the query tiles of the
-//                           scope and keeps dK, dV for its keys in tensor memory.  D = 16 / 64 / 128: 576 threads, one
-//                           CTA per SM, 512 tensor-memory columns.  D = 32 (the backbone's head size): 352 threads, TWO
-//                           CTAs per SM with 256 columns each and 64-query tiles, so that one CTA computes while the
+//                           scope and keeps dK, dV for its keys in tensor memory.  D = 64 / 128: 576 threads, one CTA
+//                           per SM, 512 tensor-memory columns.  D <= 32 (32 is the backbone's head size): 320-352 threads,
+//                           TWO CTAs per SM with 256 columns each and 64-query tiles, so that one CTA computes while the
 //                           other waits for its products
 //       warp 0      TMA producer: K_j, V_j once; Q_i, dO_i through a 2- or 3-stage ring
 //       warp 1      issues S^T = K Q^T and dP^T = V dO^T into tensor memory (keys on the lanes); once the compute
 //                   warps have published P^T and dS^T it first issues the NEXT tile's S^T / dP^T, then dV += P^T dO
 //                   and dK += dS^T Q (A from tensor memory where the columns allow it, else K-major shared-memory
 //                   tiles) and dQ_i = dS K (the dS^T shared-memory tile read as an MN-major A operand)
-//       compute     16 warps (8 at D = 32): a thread owns one key row and a share of the query columns;
+//       compute     16 warps (8 at D <= 32): a thread owns one key row and a share of the query columns;
 //                   p = exp2(s*c - lse), ds = p*(dp - delta) in packed fp32 pairs.  Except at D = 64 the score products
 //                   deliver s - lse/scale and dp - delta themselves (an extra k-step carries the per-query constants,
 //                   BwdCfg::kFold); otherwise -lse / -delta of the tile are staged in shared memory one tile ahead
@@ -83,11 +83,11 @@ __device__ __forceinline__ uint64_t bmul2(uint64_t a, uint64_t b) {
 }
 
 template <int D> struct BwdCfg {
-  // D = 32 (the backbone's head size) runs as TWO CTAs per SM: tiles of 64 queries, eight compute warps and 256
+  // D <= 32 (32 is the backbone's head size) runs as TWO CTAs per SM: tiles of 64 queries, eight compute warps and 256
   // tensor-memory columns per CTA.  A CTA's tile is a chain of hand-offs (score products -> compute warps -> gradient
   // products -> dQ read-out) in which the compute warps, the busiest part, work less than half of the time; with two
   // CTAs on the SM one computes while the other waits.
-  static constexpr bool kTwo = D == 32;
+  static constexpr bool kTwo = D <= 32;
   static constexpr int kMinCtas = kTwo ? 2 : 1;
   static constexpr int kCW = kTwo ? 8 : kBwdComputeWarps;        // compute warps: kCW / 4 per tensor-memory lane quadrant
   static constexpr int BQ = (D == 128 || kTwo) ? 64 : 128;       // queries per inner tile
@@ -117,7 +117,7 @@ template <int D> struct BwdCfg {
   // every compute thread has to fetch both per-query constants for each of its columns from shared memory: broadcast
   // loads that cost a wavefront per value and warp and were a third of all shared-memory traffic of a kernel whose
   // shared-memory pipe (those loads, the dS^T stores, the tensor cores' operand reads) was saturated.
-  // (measured per head size: D = 16 200 -> 243, D = 32 426 -> 485-512, D = 128 579-600 -> 618 TFLOP/s; D = 64, whose
+  // (measured per head size: D = 16 200 -> 243 (264 with two CTAs per SM), D = 32 426 -> 485-512, D = 128 579-600 -> 618 TFLOP/s; D = 64, whose
   // compute threads are short of registers, 549 -> 509, so it keeps the per-column loads)
   static constexpr bool kFold = D != 64;
   static constexpr int kOnesBytes = kFold ? kBK * 32 : 0;          // [128 keys][16] bf16, ones in three columns of each half
