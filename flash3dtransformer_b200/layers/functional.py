@@ -30,6 +30,12 @@ def bf16_weight(p: torch.Tensor) -> torch.Tensor:
     return w
 
 
+def _fp32_param(p: torch.Tensor) -> torch.Tensor:
+    """fp32 contiguous view of a parameter (the parameter itself when it already is one)."""
+    d = p.detach()
+    return d if d.dtype == torch.float32 and d.is_contiguous() else d.float().contiguous()
+
+
 def _fp32_bias(b: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
     if b is None:
         return None
@@ -220,6 +226,9 @@ LinearFn._backward_split = staticmethod(_split_backward)
 
 
 def linear(x, weight, bias=None, residual=None, nsplit=1, epilogue=pshattn.EPI_NONE):
+    if not torch.is_grad_enabled() and x.dtype == torch.bfloat16 and x.is_contiguous():
+        # inference: the same GEMM without the autograd bookkeeping of a Function call
+        return linear_inference(x, weight, bias, None if residual is None else residual.contiguous(), nsplit, epilogue)
     return LinearFn.apply(x, weight, bias, residual, nsplit, epilogue)
 
 
@@ -265,6 +274,10 @@ class LayerNormFn(Function):
 
 
 def layer_norm(x, weight, bias, eps=1e-5, gelu=False):
+    if not torch.is_grad_enabled() and x.dtype == torch.bfloat16 and x.is_contiguous():
+        out = torch.empty_like(x)
+        pshattn.layernorm_bf16(x, _fp32_param(weight), _fp32_param(bias), out, eps, gelu)
+        return out
     return LayerNormFn.apply(x, weight, bias, eps, gelu)
 
 

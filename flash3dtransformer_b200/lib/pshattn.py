@@ -27,29 +27,41 @@ def _require(cond: bool, msg: str) -> None:
 
 
 def _check_tensors(tensors, names) -> torch.device:
-    """assert_contiguous + assert_same_device of src/common/runtime.h:36-70."""
+    """assert_contiguous + assert_same_device of src/common/runtime.h:36-70.  (The checks run on every operator call of
+    a forward pass, so the passing case is kept to plain comparisons; the messages are built only on failure.)"""
     dev = None
     for t, n in zip(tensors, names):
-        _require(isinstance(t, torch.Tensor), f"{n} must be a torch.Tensor")
-        _require(t.is_contiguous(), f"Tensor {n} is not contiguous")
-        _require(t.is_cuda, f"Tensor {n} is not on a CUDA device (there is no CPU path)")
+        if not isinstance(t, torch.Tensor):
+            raise RuntimeError(f"{n} must be a torch.Tensor")
+        if not t.is_contiguous():
+            raise RuntimeError(f"Tensor {n} is not contiguous")
+        if not t.is_cuda:
+            raise RuntimeError(f"Tensor {n} is not on a CUDA device (there is no CPU path)")
         if dev is None:
             dev = t.device
-        _require(t.device == dev, f"Tensor {n} is on {t.device}, expected {dev}")
+        elif t.device != dev:
+            raise RuntimeError(f"Tensor {n} is on {t.device}, expected {dev}")
     return dev
 
 
 def _check_dtype(tensors, names, dtype) -> None:
     """assert_dtype of src/common/runtime.h:72-86."""
     for t, n in zip(tensors, names):
-        _require(t.dtype == dtype, f"Tensor {n} has dtype {t.dtype}, expected {dtype}")
+        if t.dtype != dtype:
+            raise RuntimeError(f"Tensor {n} has dtype {t.dtype}, expected {dtype}")
 
 
 def _ptr(t: torch.Tensor) -> ctypes.c_void_p:
     return ctypes.c_void_p(t.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream(dev: torch.device) -> ctypes.c_void_p:
+    """cudaStream_t of torch's current stream on the device."""
+    if _raw_stream is not None:
+        return ctypes.c_void_p(_raw_stream(dev.index if dev.index is not None else torch.cuda.current_device()))
     return ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
 
 
