@@ -36,8 +36,12 @@ namespace f3d {
 // Three epilogue warps per tensor-memory lane quadrant: with 16 the register file caps a thread at 96 registers and the
 // epilogue spills; 12 warps get 128 registers, spill nothing and execute fewer control instructions per tile (the
 // epilogue is bound by instruction issue): 16.4 ms for the backbone's GEMM mix against 17.3 (16 warps) and 17.9 (8).
-constexpr int kEpiWarps = 12;
-constexpr int kGemmThreads = 64 + 32 * kEpiWarps;     // TMA warp, MMA warp, epilogue warps
+// The kernel comes in two builds.  The general one (LEAN = false) has every epilogue (SwiGLU, GELU, folded LayerNorm, row
+// sums, direct stores) and 12 epilogue warps.  The lean one serves the plain projections (bias, residual, column splits):
+// without the other epilogues' code a thread needs fewer registers, so 16 epilogue warps fit, and the epilogue, a chain
+// of latencies per 32-column task, is what bounds those projections.
+constexpr int epi_warps(bool lean) { return lean ? 16 : 12; }
+constexpr int gemm_threads(bool lean) { return 64 + 32 * epi_warps(lean); }     // TMA warp, MMA warp, epilogue warps
 constexpr int BM = 128;
 constexpr int BK = 64;
 
@@ -62,7 +66,8 @@ struct GemmArgs {
   float2 *stats_out;        // [M] or null: (sum, sum of squares) of every output row, accumulated with atomic adds
 };
 
-template <int BN> struct GemmSmem {
+template <int BN, bool LEAN> struct GemmSmem {
+  static constexpr int kEpiWarps = epi_warps(LEAN);
   static constexpr int kStages = BN >= 256 ? 3 : 4;
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
@@ -71,7 +76,7 @@ template <int BN> struct GemmSmem {
   static constexpr int kAcc = BN >= 256 ? 2 : 4;        // accumulator buffers in tensor memory (kAcc * BN <= 512 columns)
   static constexpr int kBarBytes = 256;
   // partial row sums of the epilogue warps: [accumulator][quadrant][warp of the quadrant][32 rows] pairs + counters
-  static constexpr int kStatBytes = kAcc * 4 * (kEpiWarps / 4) * 32 * 8 + kAcc * 4 * 4;
+  static constexpr int kStatBytes = LEAN ? 16 : kAcc * 4 * (kEpiWarps / 4) * 32 * 8 + kAcc * 4 * 4;     // (the lean build has no row sums)
   // bias inside the product: one more k-step of 16 whose A side is a tile of ones [BM][16] and whose W side holds every
   // column's bias as three 16-bit terms [BN][16] (single column tile only, where the W side never changes)
   static constexpr int kFoldBytes = (BM + BN) * 32;
@@ -133,11 +138,12 @@ template <bool F16> __device__ __forceinline__ float unpack_in1(const __nv_bfloa
   return __bfloat162float(*p);
 }
 
-template <int BN, bool F16>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+template <int BN, bool F16, bool LEAN>
+__global__ void __launch_bounds__(gemm_threads(LEAN), 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                          const __grid_constant__ CUtensorMap map_c, GemmArgs g) {
-  using S = GemmSmem<BN>;
+  using S = GemmSmem<BN, LEAN>;
+  constexpr int kEpiWarps = S::kEpiWarps, kGemmThreads = gemm_threads(LEAN);
   constexpr int kStages = S::kStages;
   constexpr int kAcc = S::kAcc;
   constexpr uint32_t kTmemCols = kAcc * BN < 32 ? 32 : kAcc * BN;
@@ -198,7 +204,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { tc::mbar_init(&full[s], 1); tc::mbar_init(&empty[s], 1); }
     for (int a = 0; a < kAcc; ++a) { tc::mbar_init(&acc_full[a], 1); tc::mbar_init(&acc_empty[a], kEpiWarps); }
-    for (int a = 0; a < kAcc * 4; ++a) stat_cnt[a] = 0;
+    if (!LEAN) for (int a = 0; a < kAcc * 4; ++a) stat_cnt[a] = 0;
     *abort_flag = 0;
     tc::mbar_fence_init();
   }
@@ -302,7 +308,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       const int row = m0 + q * 32 + lane;
       // folded LayerNorm: this thread's row contributes rstd and -mean * rstd to every column
       float ln_rstd = 1.f, ln_nmr = 0.f;
-      if (g.ln_stats) {
+      if (!LEAN && g.ln_stats) {
         const float2 st = row < g.M ? __ldg(g.ln_stats + row) : make_float2(0.f, 0.f);
         const float mean = st.x * g.ln_inv_k;
         const float var = fmaxf(fmaf(-mean, mean, st.y * g.ln_inv_k), 0.f);
@@ -320,7 +326,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         float v[32];
         const int oc0 = (g.epilogue == EPI_SWIGLU ? n0 / 2 : n0) + c0;      // first output column of the task
         // runtime switches (bias, activation) are tested once per task, never per element
-        if (g.epilogue == EPI_SWIGLU) {
+        if (!LEAN && g.epilogue == EPI_SWIGLU) {
           uint32_t r[32], u[32];
           tc::tmem_ld_32x32b_x32(t_row + c0, r);
           tc::tmem_ld_32x32b_x32(t_row + BN / 2 + c0, u);
@@ -362,7 +368,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           tc::tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-          if (g.ln_stats) {
+          if (!LEAN && g.ln_stats) {
             // v = rstd * acc + (nmr * s + b'); columns past N are never stored, so only the loads are guarded
             const float4 *bp = reinterpret_cast<const float4 *>(g.bias + oc0), *sp4 = reinterpret_cast<const float4 *>(g.ln_colsum + oc0);
 #pragma unroll
@@ -392,7 +398,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
               }
             }
           }
-          if (g.epilogue == EPI_GELU) {
+          if (!LEAN && g.epilogue == EPI_GELU) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
           }
@@ -412,7 +418,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             for (int j = 0; j < 32; ++j) if (oc0 + j < g.N) v[j] += unpack_in1<F16>(rp + j);
           }
         }
-        if (g.stats_out) {
+        if (!LEAN && g.stats_out) {
           // row sums of this task's columns for the LayerNorm that follows (the next projection folds it in)
 #pragma unroll
           for (int j = 0; j < 32; j += 2) {
@@ -423,7 +429,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             }
           }
         }
-        if (g.direct_store) {
+        if (!LEAN && g.direct_store) {
           if (row < g.M) {
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
@@ -461,7 +467,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         obuf ^= 1u;
       }
       task += (uint32_t)(out_cols / 32);
-      if (g.stats_out) {
+      if (!LEAN && g.stats_out) {
         // leave this warp's partial sums in its slot; the last warp of the quadrant to get here adds the slots in a
         // fixed order.  The slots of an accumulator are free again before its next tile: every epilogue warp arrives
         // on acc_empty only after this block.
@@ -510,15 +516,24 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 
 int *status_word(int device);   // device word, zero until a kernel reports an abandoned wait
 
+template <int BN, bool F16, bool LEAN>
+static int launch_gemm_build(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mc, const GemmArgs &g, int device,
+                             cudaStream_t st) {
+  auto kern = gemm_bf16_tcgen05_kernel<BN, F16, LEAN>;
+  F3D_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(kern), device, GemmSmem<BN, LEAN>::kTotal));
+  int tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN);
+  int grid = tiles < sm_count(device) ? tiles : sm_count(device);
+  kern<<<grid, gemm_threads(LEAN), GemmSmem<BN, LEAN>::kTotal, st>>>(ma, mb, mc, g);
+  return check_launch("gemm_bf16_tcgen05");
+}
+
 template <int BN, bool F16>
 static int launch_gemm(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mc, const GemmArgs &g, int device,
                        cudaStream_t st) {
-  auto kern = gemm_bf16_tcgen05_kernel<BN, F16>;
-  F3D_TRY(ensure_dynamic_smem(reinterpret_cast<const void *>(kern), device, GemmSmem<BN>::kTotal));
-  int tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN);
-  int grid = tiles < sm_count(device) ? tiles : sm_count(device);
-  kern<<<grid, kGemmThreads, GemmSmem<BN>::kTotal, st>>>(ma, mb, mc, g);
-  return check_launch("gemm_bf16_tcgen05");
+  // the plain projections (bias, residual, column splits, TMA stores) take the lean build
+  const bool lean = g.epilogue == EPI_NONE && !g.ln_stats && !g.stats_out && !g.direct_store;
+  if (lean) return launch_gemm_build<BN, F16, true>(ma, mb, mc, g, device, st);
+  return launch_gemm_build<BN, F16, false>(ma, mb, mc, g, device, st);
 }
 
 struct LinearFusion {
