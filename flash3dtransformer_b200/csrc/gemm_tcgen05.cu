@@ -37,7 +37,8 @@ namespace f3d {
 // epilogue spills; 12 warps get 128 registers, spill nothing and execute fewer control instructions per tile (the
 // epilogue is bound by instruction issue): 16.4 ms for the backbone's GEMM mix against 17.3 (16 warps) and 17.9 (8).
 // The kernel comes in two builds.  The general one (LEAN = false) has every epilogue (SwiGLU, GELU, folded LayerNorm, row
-// sums, direct stores) and 12 epilogue warps.  The lean one serves the plain projections (bias, residual, column splits):
+// sums, direct stores) and 12 epilogue warps.  The lean one serves the plain projections (bias, residual, column splits)
+// and SwiGLU without a folded LayerNorm:
 // without the other epilogues' code a thread needs fewer registers, so 16 epilogue warps fit, and the epilogue, a chain
 // of latencies per 32-column task, is what bounds those projections.
 constexpr int epi_warps(bool lean) { return lean ? 16 : 12; }
@@ -326,7 +327,36 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         float v[32];
         const int oc0 = (g.epilogue == EPI_SWIGLU ? n0 / 2 : n0) + c0;      // first output column of the task
         // runtime switches (bias, activation) are tested once per task, never per element
-        if (!LEAN && g.epilogue == EPI_SWIGLU) {
+        if (LEAN && g.epilogue == EPI_SWIGLU) {
+          // lean build: gate and up accumulators of 16 output columns at a time, so that a thread stays within the
+          // registers that 16 epilogue warps leave it
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            uint32_t r[16], u[16];
+            tc::tmem_ld_32x32b_x16(t_row + c0 + hh * 16, r);
+            tc::tmem_ld_32x32b_x16(t_row + BN / 2 + c0 + hh * 16, u);
+            tc::tmem_ld_wait();
+            if (g.bias && !fold_bias) {
+              const float4 *pg = reinterpret_cast<const float4 *>(g.bias + oc0 + hh * 16);
+              const float4 *pu = reinterpret_cast<const float4 *>(g.bias + g.N / 2 + oc0 + hh * 16);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float4 a4 = __ldg(pg + j), b4 = __ldg(pu + j);
+                swiglu_pair(gadd2(gpack2(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1])), gpack2(a4.x, a4.y)),
+                            gadd2(gpack2(__uint_as_float(u[4 * j]), __uint_as_float(u[4 * j + 1])), gpack2(b4.x, b4.y)),
+                            v[hh * 16 + 4 * j], v[hh * 16 + 4 * j + 1]);
+                swiglu_pair(gadd2(gpack2(__uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])), gpack2(a4.z, a4.w)),
+                            gadd2(gpack2(__uint_as_float(u[4 * j + 2]), __uint_as_float(u[4 * j + 3])), gpack2(b4.z, b4.w)),
+                            v[hh * 16 + 4 * j + 2], v[hh * 16 + 4 * j + 3]);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                swiglu_pair(gpack2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1])),
+                            gpack2(__uint_as_float(u[2 * j]), __uint_as_float(u[2 * j + 1])), v[hh * 16 + 2 * j], v[hh * 16 + 2 * j + 1]);
+            }
+          }
+        } else if (!LEAN && g.epilogue == EPI_SWIGLU) {
           uint32_t r[32], u[32];
           tc::tmem_ld_32x32b_x32(t_row + c0, r);
           tc::tmem_ld_32x32b_x32(t_row + BN / 2 + c0, u);
@@ -531,7 +561,7 @@ template <int BN, bool F16>
 static int launch_gemm(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mc, const GemmArgs &g, int device,
                        cudaStream_t st) {
   // the plain projections (bias, residual, column splits, TMA stores) take the lean build
-  const bool lean = g.epilogue == EPI_NONE && !g.ln_stats && !g.stats_out && !g.direct_store;
+  const bool lean = (g.epilogue == EPI_NONE || g.epilogue == EPI_SWIGLU) && !g.ln_stats && !g.stats_out && !g.direct_store;
   if (lean) return launch_gemm_build<BN, F16, true>(ma, mb, mc, g, device, st);
   return launch_gemm_build<BN, F16, false>(ma, mb, mc, g, device, st);
 }
