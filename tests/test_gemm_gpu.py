@@ -59,7 +59,8 @@ def test_qkv_split_and_residual(cuda_device, m, c):
     _check(out, xw.float() @ ww.float().t() + bw + x.float(), max_abs=4e-2)
 
 
-@pytest.mark.parametrize("m,c,f", [(1024, 128, 256), (700, 64, 256), (2048, 256, 1024)])
+# (1000, 32, 128) and (3001, 64, 128): one column tile, where the bias rides in the product
+@pytest.mark.parametrize("m,c,f", [(1024, 128, 256), (700, 64, 256), (2048, 256, 1024), (1000, 32, 128), (3001, 64, 128), (513, 32, 64)])
 def test_swiglu_and_gelu(cuda_device, m, c, f):
     from flash3dtransformer_b200.lib import pshattn
     x, w, b = _mk(cuda_device, m, 2 * f, c, seed=3)
