@@ -25,7 +25,7 @@
 // the next key tile's Q K^T is issued as soon as the softmax threads have pulled S into registers, so the tensor pipe
 // computes S(j+1) while the warps exponentiate tile j.  At D = 32 the kernel is bound by the special-function unit
 // (one ex2 per score against 4*D = 128 tensor FLOPs) and by instruction issue of the softmax warps, not by the tensor
-// pipe; a quarter of the exponentials are therefore computed on the FMA pipe (poly_exp2_pair).
+// pipe; three of every sixteen exponentials are therefore computed on the FMA pipe (poly_exp2_pair).
 #include "f3d_common.cuh"
 #include "tc_sm100.cuh"
 #include "../../include/f3d_b200.h"
@@ -125,8 +125,10 @@ template <int D, int BKV, int NQ> struct AttnCfg {
   static_assert(kTmemCols <= 512, "tensor memory holds 512 columns");
 };
 
-// POLY8: of every eight pairs of scores, this many take their exponential from poly_exp2_pair (FMA pipe) and the rest
-// from ex2.approx (special-function unit), so that both pipes work on every row.
+// POLY8 != 0: of the sixteen pairs of scores of a half tile, pairs 4, 9 and 14 take their exponential from poly_exp2_pair
+// (FMA pipe) and the rest from ex2.approx (special-function unit), so that both pipes work on every row.  Share and
+// placement are measured choices (D = 32, W = 4096): none 439, two adjacent pairs of every eight 476, every fourth pair
+// 484, every fifth pair 497 TFLOP/s; larger shares cost more issue slots than the special-function slots they free.
 template <int D, int BKV, int NQ, int POLY8, bool F16>
 __global__ void __launch_bounds__((AttnCfg<D, BKV, NQ>::kThreads), (AttnCfg<D, BKV, NQ>::kMinCtas))
 attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -309,7 +311,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       for (int i = 0; i < 16; ++i) {
         const uint64_t xx = fma2(pack2(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1])), c2, m2);
         float e0, e1;
-        if ((i & 7) < POLY8) {
+        if (POLY8 != 0 && (i % 5) == 4) {
           poly_exp2_pair(xx, e0, e1);
         } else {
           float x0, x1;
@@ -329,7 +331,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       for (int i = 0; i < 16; ++i) {
         const uint64_t xx = fma2(pack2(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1])), c2, m2);
         float e0, e1;
-        if ((i & 7) < POLY8) {
+        if (POLY8 != 0 && (i % 5) == 4) {
           poly_exp2_pair(xx, e0, e1);
         } else {
           float x0, x1;
@@ -406,9 +408,9 @@ static int launch_attn_fwd(const void *Q, const void *K, const void *V, AttnFwdA
   return check_launch("buck_swin_fwd");
 }
 
-// Head sizes up to 32 are bound by the special-function unit: a quarter of their exponentials go to the FMA pipe
-// (measured at D = 32, window 4096: 0 / 12.5 / 25 / 37.5 / 50 % -> 439 / 448 / 462 / 446 / 413 TFLOP/s; beyond a quarter
-// the extra instructions cost more issue slots than the special-function slots they free).  One query tile per CTA:
+// Head sizes up to 32 are bound by the special-function unit: three of every sixteen exponentials go to the FMA pipe
+// (measured at D = 32, window 4096, with adjacent pairs: 0 / 12.5 / 25 / 37.5 / 50 % -> 439 / 448 / 462 / 446 / 413
+// TFLOP/s; spread out as every fifth pair, 18.75 %: 497).  One query tile per CTA:
 // two and four tiles per CTA sharing the K/V stream measured 2 % and 4 % slower (their exponential phases line up).
 template <bool F16>
 static int launch_attn_fwd_any(int D, const void *Q, const void *K, const void *V, AttnFwdArgs a, int device, cudaStream_t st) {
